@@ -1,0 +1,186 @@
+/* C ABI of libcoli_b200.so — the B200 (sm_100a) backend for the routed-expert MoE block of
+ * GriffinPilz/SpeedyColibri.
+ *
+ * The first half keeps the names, argument meaning and return convention of the reference's
+ * CUDA backend (crates/colibri-backend/cuda/backend_cuda.h; Rust declarations in
+ * crates/colibri-backend/src/cuda.rs:32-395), so the engine's expert dispatch
+ * (crates/colibri-engine/src/gpu.rs) links against it unchanged.  The second half
+ * (coli_b200_*) is the whole-block entry the reference does not have: router, top-k, permute,
+ * grouped expert FFN, weighted combine and shared expert in one device-resident call, plus
+ * the per-stage calls the expert-parallel path is assembled from.
+ *
+ * Conventions (backend_cuda.h throughout): every int-returning call returns 1 when it ran and
+ * 0 when it declined or failed.  There is no CPU fallback behind a 0 in this library; the
+ * reason is available from coli_cuda_last_error().  Matrices are row-major; a weight W[O,I]
+ * maps x[S,I] to y[S,O].  All pointers are plain host or device addresses as stated per call.
+ */
+#ifndef COLI_B200_H
+#define COLI_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define COLI_CUDA_MAX_DEVICES 16
+
+/* Weight formats.  0..6 are the reference's QTensor fmt codes
+ * (crates/colibri-core/src/quant.rs:707-746); 8 is the 128x128 block-scaled FP8 form the
+ * reference only reads in its converter (crates/colibri-engine/src/convert.rs:674-745). */
+#define COLI_FMT_F32 0
+#define COLI_FMT_E4M3_ROW 4
+#define COLI_FMT_NVFP4 5
+#define COLI_FMT_FP8_B128 8
+
+/* Opaque, persistent HBM copy of one quantised matrix (backend_cuda.h:24). */
+typedef struct ColiCudaTensor ColiCudaTensor;
+
+/* ---- lifecycle ------------------------------------------------------------------------- */
+/* backend_cuda.h:27 / backend_cuda.cu:2611-2655.  `devices` are CUDA ordinals.  Idempotent for
+ * the same set; refuses a different set while live.  Refuses a device that is not sm_100. */
+int coli_cuda_init(const int *devices, int count);
+/* backend_cuda.h:28. */
+void coli_cuda_shutdown(void);
+/* backend_cuda.h:32-33. */
+int coli_cuda_device_count(void);
+int coli_cuda_device_at(int index);
+/* backend_cuda.h:34. */
+int coli_cuda_mem_info(int device, size_t *free_bytes, size_t *total_bytes);
+/* backend_cuda.h:46. */
+int coli_cuda_device_sync(int device);
+/* backend_cuda.h:31.  Only the plain SiLU SwiGLU (oai = 0, limit = 0) is implemented; after
+ * any other setting the expert calls return 0. */
+void coli_cuda_set_activation(int oai, float alpha, float limit);
+/* backend_cuda.h:48.  Resident tensors on `device` (< 0: all devices). */
+void coli_cuda_stats(int device, size_t *tensor_count, size_t *tensor_bytes);
+/* Added: text of the most recent failure on the calling thread ("" if none).  The reference
+ * logs "[CUDA] what: msg" to stderr (backend_cuda.cu:102-106); this library does both. */
+const char *coli_cuda_last_error(void);
+
+/* ---- resident weights -------------------------------------------------------------------- */
+/* backend_cuda.h:57-59 / backend_cuda.cu:2880-2920.  Copies a host matrix into HBM.  fmt 4:
+ * `weights` = e4m3 codes [O,I], `scales` = f32 [O].  fmt 8: `weights` = e4m3 codes [O,I],
+ * `scales` = f32 [ceil(O/128), ceil(I/128)].  fmt 5 must use coli_cuda_tensor_wrap_nvfp4.
+ * If *tensor is already set, only checks fmt/I/O/device and returns (backend_cuda.cu:2892-2895). */
+int coli_cuda_tensor_upload(ColiCudaTensor **tensor, const void *weights, const float *scales, int fmt,
+                            int I, int O, int device);
+/* backend_cuda.h:80-82.  Same as upload here: B200 has no pageable zero-copy at speed, so a
+ * "wrap" copies into HBM and the handle owns that copy. */
+int coli_cuda_tensor_wrap(ColiCudaTensor **tensor, const void *weights, const float *scales, int fmt, int I,
+                          int O, int device);
+/* crates/colibri-backend/src/cuda.rs:69-77 / backend_cuda.cu:5311-5330.  `weights` = packed
+ * e2m1 nibbles [O, ceil(I/2)] (low nibble = even column), `bscale` = ue4m3 per-16 block scales
+ * [O, ceil(I/16)], `gscale` = per-tensor f32.  Host pointers; copied into HBM. */
+int coli_cuda_tensor_wrap_nvfp4(ColiCudaTensor **tensor, const void *weights, const void *bscale, float gscale,
+                                int I, int O, int device);
+/* backend_cuda.h:270-272. */
+void coli_cuda_tensor_free(ColiCudaTensor *tensor);
+size_t coli_cuda_tensor_bytes(const ColiCudaTensor *tensor);
+int coli_cuda_tensor_device(const ColiCudaTensor *tensor);
+
+/* Added: build a handle from matrices that already sit in device memory, in the same layouts
+ * as the host-pointer calls above (q = nibbles or codes, s = ue4m3 bytes or f32 scales). */
+int coli_b200_tensor_from_device(ColiCudaTensor **tensor, int fmt, const void *d_q, const void *d_s,
+                                 float gscale, int I, int O, int device);
+/* Added: copy a handle's contents back to HOST memory in the layouts of the upload calls
+ * (inverse of the HBM repack).  `gscale` may be NULL. */
+int coli_b200_tensor_export(const ColiCudaTensor *tensor, void *q_host, void *s_host, float *gscale);
+/* Added: device-side quantisers, bit-identical to the reference's
+ * (crates/colibri-engine/src/convert.rs:1107-1135 for NVFP4; the 128x128 FP8 encoder is the
+ * per-row rule of convert.rs:1042-1054 applied per block).  All pointers are device pointers,
+ * `d_w` is f32 [O,I]; nvfp4 returns the per-tensor scale through the host pointer `gscale`. */
+int coli_b200_quantize_nvfp4(int device, const float *d_w, int O, int I, void *d_nibbles, void *d_bscale,
+                             float *gscale);
+int coli_b200_quantize_fp8_b128(int device, const float *d_w, int O, int I, void *d_codes, float *d_scales);
+
+/* ---- expert FFN, reference signatures ------------------------------------------------------ */
+/* backend_cuda.h:97-99 semantics for NVFP4 (backend_cuda.cu:3668-3806): y = down(silu(gate x) * up x),
+ * x and y are HOST f32 [S, D] with D = gate->I; synchronous. */
+int coli_cuda_expert_mlp_nvfp4(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down, float *y,
+                               const float *x, int S);
+/* backend_cuda.h:104-105 (fmt 4 per-row scaled e4m3; this library also accepts fmt 8). */
+int coli_cuda_expert_mlp_fp8(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down, float *y,
+                             const float *x, int S);
+/* backend_cuda.h:134-140 / backend_cuda.cu:4410-4792: packed group of same-shaped experts; x and
+ * y hold sum(rows) consecutive [D] HOST f32 rows in call order. */
+int coli_cuda_expert_group_nvfp4(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                                 ColiCudaTensor *const *downs, const int *rows, int count, float *y,
+                                 const float *x);
+/* backend_cuda.h:89-92 restricted to fmt 0, the router GEMM the engine issues through it
+ * (crates/colibri-engine/src/gpu.rs:2219-2249): y[S,O] = x[S,I] @ W[O,I]^T with a k-ascending
+ * f32 sum per output.  HOST pointers; `tensor` caches the device copy of W as in the reference. */
+int coli_cuda_matmul(ColiCudaTensor **tensor, float *y, const float *x, const void *weights,
+                     const float *scales, int fmt, int S, int I, int O, int device);
+
+/* ---- whole block (no counterpart in the reference: its router, top-k, gather, combine and
+ * shared-expert add run on the CPU in crates/colibri-engine/src/moe.rs:1799-1895) ----------- */
+#define COLI_SCORE_SOFTMAX 0
+#define COLI_SCORE_SIGMOID 1
+
+typedef struct ColiMoeLayer {
+  int32_t H, E, k, I;      /* hidden, routed experts, top-k, expert intermediate */
+  int32_t score;           /* COLI_SCORE_* (colibri_core::RouterScore) */
+  int32_t norm_topk;       /* cfg.norm_topk */
+  float routed_scale;      /* cfg.routed_scale */
+  int32_t n_group;         /* 1 = ungrouped (the reference's only mode) */
+  int32_t topk_group;
+  int32_t fmt;             /* COLI_FMT_NVFP4 or COLI_FMT_FP8_B128, all experts alike */
+  int32_t device;
+  const void *router_w;    /* HOST bf16 [E,H]; copied at create */
+  const float *select_bias;/* HOST f32 [E] or NULL; sigmoid arm, selection only (moe.rs:1104) */
+  const float *logit_bias; /* HOST f32 [E] or NULL; extension: added to the logits */
+  ColiCudaTensor *const *gate; /* E entries; NULL entry = expert not resident on this rank */
+  ColiCudaTensor *const *up;
+  ColiCudaTensor *const *down;
+  ColiCudaTensor *sh_gate; /* shared expert or NULL (all three) */
+  ColiCudaTensor *sh_up;
+  ColiCudaTensor *sh_down;
+  int32_t ep_rank, ep_world;   /* expert-parallel placement; 0/1 = single GPU */
+  const int32_t *expert_owner; /* HOST [E] or NULL = contiguous e*world/E (sharding.rs:197-203) */
+} ColiMoeLayer;
+
+typedef struct ColiMoe ColiMoe; /* layer tables + workspace for up to max_tokens tokens */
+
+int coli_b200_moe_create(ColiMoe **moe, const ColiMoeLayer *layer, int max_tokens);
+void coli_b200_moe_destroy(ColiMoe *moe);
+/* Bytes of HBM workspace the handle owns (excludes the weights). */
+size_t coli_b200_moe_workspace_bytes(const ColiMoe *moe);
+
+/* One block call, synchronous, HOST bf16 x[T,H] -> HOST bf16 out[T,H] (host<->device copies
+ * inside).  topk_idx [T,k] int32 and topk_w [T,k] f32 are optional HOST outputs.  All experts
+ * must be resident (single GPU). */
+int coli_b200_moe_block(ColiMoe *moe, const void *x, void *out, int T, int32_t *topk_idx, float *topk_w);
+/* Same with DEVICE pointers, asynchronous on `stream` (a cudaStream_t, NULL = the handle's). */
+int coli_b200_moe_block_dev(ColiMoe *moe, const void *x_dev, void *out_dev, int T, void *stream);
+/* Copy the last call's routing to HOST (after synchronising the stream). */
+int coli_b200_moe_last_routing(ColiMoe *moe, int T, int32_t *topk_idx, float *topk_w);
+
+/* ---- stages, DEVICE pointers, asynchronous (what the expert-parallel path is built from) --- */
+/* Router GEMM + score + top-k for x_dev[T,H]; then rows are ordered by (owner rank, expert id)
+ * and gathered into rows_dev[T*k, H] (bf16).  seg_count_dev[E] receives rows per expert in that
+ * order, slot_dev[T*k] the row each (token, kk) pair went to.  Routing stays in the handle for
+ * the combine stage. */
+int coli_b200_moe_route_dev(ColiMoe *moe, const void *x_dev, int T, void *rows_dev, int32_t *seg_count_dev,
+                            int32_t *slot_dev, void *stream);
+/* Grouped SwiGLU FFN over expert-contiguous rows: segment j (j < n_seg) holds seg_count_dev[j]
+ * rows and uses resident expert first_expert + j in owner order.  rows_dev, y_dev: bf16
+ * [n_rows, H].  The device-pointer form of coli_cuda_expert_group_nvfp4. */
+int coli_b200_moe_experts_dev(ColiMoe *moe, const void *rows_dev, const int32_t *seg_count_dev, int first_seg,
+                              int n_seg, int n_rows, void *y_dev, void *stream);
+/* Shared expert over x_dev[T,H] -> y_dev[T,H] (bf16). */
+int coli_b200_moe_shared_dev(ColiMoe *moe, const void *x_dev, int T, void *y_dev, void *stream);
+/* out[t] = sum_kk w[t,kk] * y_rows[slot[t,kk]]  (+ shared_y[t] if not NULL), kk ascending, f32,
+ * rounded once to bf16 (moe.rs:1549-1553,1875-1885). */
+int coli_b200_moe_combine_dev(ColiMoe *moe, const void *y_rows_dev, const int32_t *slot_dev,
+                              const void *shared_y_dev, void *out_dev, int T, void *stream);
+
+/* FNV-1a fingerprint of an expert->rank map (crates/colibri-cluster/src/sharding.rs:251-265);
+ * `owner` NULL = contiguous.  Ranks compare it before the first exchange. */
+uint64_t coli_b200_sharding_fingerprint(uint32_t num_nodes, uint32_t n_experts, const uint32_t *owner);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* COLI_B200_H */

@@ -1,0 +1,936 @@
+// Host side of libcoli_b200.so: the extern "C" entry points declared in include/coli_b200.h.
+// Lifecycle, resident-weight handles, the whole-block call and its stages, and the reference's
+// host-pointer expert calls expressed through the same kernels.
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "internal.cuh"
+
+// ---- errors ---------------------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+void coli_set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  fprintf(stderr, "[CUDA] %s\n", g_err);  // the reference's log format, backend_cuda.cu:102-106
+}
+bool coli_cuda_check(cudaError_t e, const char *what) {
+  if (e == cudaSuccess) return true;
+  coli_set_error("%s: %s", what, cudaGetErrorString(e));
+  return false;
+}
+extern "C" const char *coli_cuda_last_error(void) { return g_err; }
+
+// ---- device contexts (backend_cuda.cu:87-129, 2594-2655) --------------------------------------
+namespace {
+struct DeviceContext {
+  int device = -1;
+  cudaStream_t stream = nullptr;
+  std::mutex mu;  // held across a whole host-pointer call, as the reference does
+  size_t tensor_count = 0, tensor_bytes = 0;
+  // scratch of the host-pointer expert calls, grown on demand
+  void *buf[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  size_t cap[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+};
+std::mutex g_init_mu;
+DeviceContext *g_ctx[COLI_CUDA_MAX_DEVICES];
+int g_ndev = 0;
+int g_act_oai = 0;
+float g_act_limit = 0.0f;
+
+DeviceContext *find_ctx(int device) {
+  for (int i = 0; i < g_ndev; ++i)
+    if (g_ctx[i] && g_ctx[i]->device == device) return g_ctx[i];
+  coli_set_error("device %d is not initialised (call coli_cuda_init)", device);
+  return nullptr;
+}
+bool select_ctx(DeviceContext *c) { return c && coli_cuda_check(cudaSetDevice(c->device), "cudaSetDevice"); }
+bool reserve(DeviceContext *c, int slot, size_t bytes) {
+  if (c->cap[slot] >= bytes) return true;
+  if (c->buf[slot]) cudaFree(c->buf[slot]);
+  c->buf[slot] = nullptr;
+  c->cap[slot] = 0;
+  if (!coli_cuda_check(cudaMalloc(&c->buf[slot], bytes), "scratch allocation")) return false;
+  c->cap[slot] = bytes;
+  return true;
+}
+}  // namespace
+
+extern "C" int coli_cuda_init(const int *devices, int count) {
+  std::lock_guard<std::mutex> lk(g_init_mu);
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || n < 1) {
+    coli_set_error("no CUDA device is visible");
+    return 0;
+  }
+  int def = 0;
+  if (!devices || count <= 0) {
+    devices = &def;
+    count = 1;
+  }
+  if (count > COLI_CUDA_MAX_DEVICES) {
+    coli_set_error("too many devices (%d)", count);
+    return 0;
+  }
+  if (g_ndev > 0) {  // idempotent for the same set only
+    bool same = g_ndev == count;
+    for (int i = 0; same && i < count; ++i) same = g_ctx[i]->device == devices[i];
+    if (!same) coli_set_error("coli_cuda_init: already initialised with a different device set");
+    return same ? 1 : 0;
+  }
+  for (int i = 0; i < count; ++i) {
+    cudaDeviceProp prop;
+    if (devices[i] < 0 || devices[i] >= n || !coli_cuda_check(cudaGetDeviceProperties(&prop, devices[i]), "device properties"))
+      return 0;
+    if (prop.major != 10) {
+      coli_set_error("device %d is sm_%d%d; this library is built for sm_100a only", devices[i], prop.major, prop.minor);
+      return 0;
+    }
+  }
+  for (int i = 0; i < count; ++i) {
+    DeviceContext *c = new DeviceContext();
+    c->device = devices[i];
+    if (!coli_cuda_check(cudaSetDevice(c->device), "cudaSetDevice") ||
+        !coli_cuda_check(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking), "stream creation")) {
+      delete c;
+      return 0;
+    }
+    g_ctx[g_ndev++] = c;
+  }
+  return 1;
+}
+
+extern "C" void coli_cuda_shutdown(void) {
+  std::lock_guard<std::mutex> lk(g_init_mu);
+  for (int i = 0; i < g_ndev; ++i) {
+    DeviceContext *c = g_ctx[i];
+    if (!c) continue;
+    cudaSetDevice(c->device);
+    cudaStreamSynchronize(c->stream);
+    for (int s = 0; s < 8; ++s)
+      if (c->buf[s]) cudaFree(c->buf[s]);
+    cudaStreamDestroy(c->stream);
+    delete c;
+    g_ctx[i] = nullptr;
+  }
+  g_ndev = 0;
+}
+extern "C" int coli_cuda_device_count(void) { return g_ndev; }
+extern "C" int coli_cuda_device_at(int index) { return (index >= 0 && index < g_ndev) ? g_ctx[index]->device : -1; }
+extern "C" int coli_cuda_mem_info(int device, size_t *free_bytes, size_t *total_bytes) {
+  DeviceContext *c = find_ctx(device);
+  if (!select_ctx(c) || !free_bytes || !total_bytes) return 0;
+  return coli_cuda_check(cudaMemGetInfo(free_bytes, total_bytes), "cudaMemGetInfo") ? 1 : 0;
+}
+extern "C" int coli_cuda_device_sync(int device) {
+  DeviceContext *c = find_ctx(device);
+  if (!select_ctx(c)) return 0;
+  return coli_cuda_check(cudaDeviceSynchronize(), "device sync") ? 1 : 0;
+}
+extern "C" void coli_cuda_set_activation(int oai, float alpha, float limit) {
+  (void)alpha;
+  g_act_oai = oai;
+  g_act_limit = limit;
+}
+extern "C" void coli_cuda_stats(int device, size_t *tensor_count, size_t *tensor_bytes) {
+  size_t n = 0, b = 0;
+  for (int i = 0; i < g_ndev; ++i)
+    if (g_ctx[i] && (device < 0 || g_ctx[i]->device == device)) {
+      n += g_ctx[i]->tensor_count;
+      b += g_ctx[i]->tensor_bytes;
+    }
+  if (tensor_count) *tensor_count = n;
+  if (tensor_bytes) *tensor_bytes = b;
+}
+static bool activation_supported() {
+  if (g_act_oai != 0 || g_act_limit > 0.0f) {
+    coli_set_error("only the plain SiLU SwiGLU activation is implemented (oai=%d limit=%g requested)", g_act_oai, g_act_limit);
+    return false;
+  }
+  return true;
+}
+
+// ---- resident weights ----------------------------------------------------------------------------
+static bool fmt_supported(int fmt) { return fmt == COLI_FMT_NVFP4 || fmt == COLI_FMT_FP8_B128 || fmt == COLI_FMT_E4M3_ROW; }
+
+static size_t src_q_bytes(int fmt, int I, int O) {
+  return fmt == COLI_FMT_NVFP4 ? (size_t)O * ((I + 1) / 2) : (size_t)O * I;
+}
+static size_t src_s_bytes(int fmt, int I, int O) {
+  if (fmt == COLI_FMT_NVFP4) return (size_t)O * ((I + 15) / 16);
+  if (fmt == COLI_FMT_FP8_B128) return sizeof(float) * (size_t)((O + 127) / 128) * ((I + 127) / 128);
+  return sizeof(float) * (size_t)O;
+}
+
+// Allocates the handle's HBM and fills it from device-resident source arrays.
+static int build_tensor(ColiCudaTensor **slot, DeviceContext *ctx, int fmt, const void *d_q, const void *d_s,
+                        float gscale, int I, int O) {
+  ColiCudaTensor *t = static_cast<ColiCudaTensor *>(calloc(1, sizeof(ColiCudaTensor)));
+  if (!t) return 0;
+  t->fmt = fmt;
+  t->I = I;
+  t->O = O;
+  t->device = ctx->device;
+  t->Kp = round_up(I, 128);
+  t->Op = round_up(O, 16);
+  t->KT = t->Kp / 128;
+  t->gscale = gscale;
+  t->q_bytes = (size_t)t->KT * t->Op * (fmt == COLI_FMT_NVFP4 ? 64 : 128);
+  t->s_bytes = fmt == COLI_FMT_NVFP4 ? (size_t)t->KT * t->Op * 8 : src_s_bytes(fmt, I, O);
+  bool ok = coli_cuda_check(cudaMalloc((void **)&t->q, t->q_bytes), "tensor allocation") &&
+            coli_cuda_check(cudaMalloc((void **)&t->s, t->s_bytes), "scale allocation");
+  if (ok) {
+    if (fmt == COLI_FMT_NVFP4) {
+      ok = colib::pack_nvfp4((const uint8_t *)d_q, (const uint8_t *)d_s, O, I, t, ctx->stream);
+    } else {
+      ok = colib::pack_fp8((const uint8_t *)d_q, O, I, t, ctx->stream) &&
+           coli_cuda_check(cudaMemcpyAsync(t->s, d_s, t->s_bytes, cudaMemcpyDeviceToDevice, ctx->stream), "scale copy");
+    }
+    ok = ok && coli_cuda_check(cudaStreamSynchronize(ctx->stream), "tensor repack");
+  }
+  if (!ok) {
+    if (t->q) cudaFree(t->q);
+    if (t->s) cudaFree(t->s);
+    free(t);
+    return 0;
+  }
+  ctx->tensor_count++;
+  ctx->tensor_bytes += t->q_bytes + t->s_bytes;
+  *slot = t;
+  return 1;
+}
+
+static int existing_matches(ColiCudaTensor *t, int fmt, int I, int O, int device) {
+  return t->fmt == fmt && t->I == I && t->O == O && t->device == device;
+}
+
+static int upload_from_host(ColiCudaTensor **tensor, const void *q, const void *s, float gscale, int fmt, int I,
+                            int O, int device) {
+  if (!tensor || !q || !s || I < 1 || O < 1) {
+    coli_set_error("tensor upload: null pointer or empty shape");
+    return 0;
+  }
+  if (!fmt_supported(fmt)) {
+    coli_set_error("tensor upload: format %d is not part of the MoE expert path (supported: 4, 5, 8)", fmt);
+    return 0;
+  }
+  if (*tensor) return existing_matches(*tensor, fmt, I, O, device);
+  DeviceContext *ctx = find_ctx(device);
+  if (!select_ctx(ctx)) return 0;
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  const size_t qb = src_q_bytes(fmt, I, O), sb = src_s_bytes(fmt, I, O);
+  void *dq = nullptr, *ds = nullptr;
+  int ok = coli_cuda_check(cudaMalloc(&dq, qb), "staging allocation") &&
+           coli_cuda_check(cudaMalloc(&ds, sb), "staging allocation") &&
+           coli_cuda_check(cudaMemcpyAsync(dq, q, qb, cudaMemcpyHostToDevice, ctx->stream), "tensor upload") &&
+           coli_cuda_check(cudaMemcpyAsync(ds, s, sb, cudaMemcpyHostToDevice, ctx->stream), "scale upload");
+  ok = ok && build_tensor(tensor, ctx, fmt, dq, ds, gscale, I, O);
+  if (dq) cudaFree(dq);
+  if (ds) cudaFree(ds);
+  return ok;
+}
+
+extern "C" int coli_cuda_tensor_upload(ColiCudaTensor **tensor, const void *weights, const float *scales, int fmt,
+                                       int I, int O, int device) {
+  if (fmt == COLI_FMT_NVFP4) {
+    coli_set_error("tensor upload: NVFP4 carries byte block scales; use coli_cuda_tensor_wrap_nvfp4");
+    return 0;
+  }
+  return upload_from_host(tensor, weights, scales, 1.0f, fmt, I, O, device);
+}
+extern "C" int coli_cuda_tensor_wrap(ColiCudaTensor **tensor, const void *weights, const float *scales, int fmt,
+                                     int I, int O, int device) {
+  return coli_cuda_tensor_upload(tensor, weights, scales, fmt, I, O, device);
+}
+extern "C" int coli_cuda_tensor_wrap_nvfp4(ColiCudaTensor **tensor, const void *weights, const void *bscale,
+                                           float gscale, int I, int O, int device) {
+  return upload_from_host(tensor, weights, bscale, gscale, COLI_FMT_NVFP4, I, O, device);
+}
+extern "C" int coli_b200_tensor_from_device(ColiCudaTensor **tensor, int fmt, const void *d_q, const void *d_s,
+                                            float gscale, int I, int O, int device) {
+  if (!tensor || !d_q || !d_s || I < 1 || O < 1 || !fmt_supported(fmt)) {
+    coli_set_error("tensor_from_device: bad argument");
+    return 0;
+  }
+  if (*tensor) return existing_matches(*tensor, fmt, I, O, device);
+  DeviceContext *ctx = find_ctx(device);
+  if (!select_ctx(ctx)) return 0;
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  // the source arrays may have been written on another stream
+  if (!coli_cuda_check(cudaDeviceSynchronize(), "tensor_from_device sync")) return 0;
+  return build_tensor(tensor, ctx, fmt, d_q, d_s, gscale, I, O);
+}
+extern "C" int coli_b200_tensor_export(const ColiCudaTensor *t, void *q_host, void *s_host, float *gscale) {
+  if (!t || !q_host || !s_host) {
+    coli_set_error("tensor_export: null pointer");
+    return 0;
+  }
+  DeviceContext *ctx = find_ctx(t->device);
+  if (!select_ctx(ctx)) return 0;
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  const size_t qb = src_q_bytes(t->fmt, t->I, t->O), sb = src_s_bytes(t->fmt, t->I, t->O);
+  void *dq = nullptr, *ds = nullptr;
+  int ok = coli_cuda_check(cudaMalloc(&dq, qb), "staging allocation") && coli_cuda_check(cudaMalloc(&ds, sb), "staging allocation");
+  if (ok) {
+    if (t->fmt == COLI_FMT_NVFP4)
+      ok = colib::unpack_nvfp4(t, (uint8_t *)dq, (uint8_t *)ds, ctx->stream);
+    else
+      ok = colib::unpack_fp8(t, (uint8_t *)dq, ctx->stream) &&
+           coli_cuda_check(cudaMemcpyAsync(ds, t->s, sb, cudaMemcpyDeviceToDevice, ctx->stream), "scale copy");
+  }
+  ok = ok && coli_cuda_check(cudaMemcpyAsync(q_host, dq, qb, cudaMemcpyDeviceToHost, ctx->stream), "tensor export") &&
+       coli_cuda_check(cudaMemcpyAsync(s_host, ds, sb, cudaMemcpyDeviceToHost, ctx->stream), "scale export") &&
+       coli_cuda_check(cudaStreamSynchronize(ctx->stream), "tensor export sync");
+  if (dq) cudaFree(dq);
+  if (ds) cudaFree(ds);
+  if (ok && gscale) *gscale = t->gscale;
+  return ok;
+}
+extern "C" void coli_cuda_tensor_free(ColiCudaTensor *t) {
+  if (!t) return;
+  for (int i = 0; i < g_ndev; ++i)
+    if (g_ctx[i] && g_ctx[i]->device == t->device) {
+      cudaSetDevice(t->device);
+      g_ctx[i]->tensor_count--;
+      g_ctx[i]->tensor_bytes -= t->q_bytes + t->s_bytes;
+    }
+  if (t->q) cudaFree(t->q);
+  if (t->s) cudaFree(t->s);
+  free(t);
+}
+extern "C" size_t coli_cuda_tensor_bytes(const ColiCudaTensor *t) { return t ? t->q_bytes + t->s_bytes : 0; }
+extern "C" int coli_cuda_tensor_device(const ColiCudaTensor *t) { return t ? t->device : -1; }
+
+extern "C" int coli_b200_quantize_nvfp4(int device, const float *d_w, int O, int I, void *d_nibbles, void *d_bscale,
+                                        float *gscale) {
+  DeviceContext *ctx = find_ctx(device);
+  if (!select_ctx(ctx) || !d_w || !d_nibbles || !d_bscale || !gscale) return 0;
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  if (!reserve(ctx, 7, 256)) return 0;
+  if (!coli_cuda_check(cudaDeviceSynchronize(), "quantise sync")) return 0;
+  return colib::quantize_nvfp4(d_w, O, I, (uint8_t *)d_nibbles, (uint8_t *)d_bscale, (float *)ctx->buf[7], gscale, ctx->stream);
+}
+extern "C" int coli_b200_quantize_fp8_b128(int device, const float *d_w, int O, int I, void *d_codes, float *d_scales) {
+  DeviceContext *ctx = find_ctx(device);
+  if (!select_ctx(ctx) || !d_w || !d_codes || !d_scales) return 0;
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  if (!coli_cuda_check(cudaDeviceSynchronize(), "quantise sync")) return 0;
+  return colib::quantize_fp8_b128(d_w, O, I, (uint8_t *)d_codes, d_scales, ctx->stream) &&
+         coli_cuda_check(cudaStreamSynchronize(ctx->stream), "fp8 quantise sync");
+}
+
+// ---- the block ------------------------------------------------------------------------------------
+struct ColiMoe {
+  ColiMoeLayer L;
+  DeviceContext *ctx;
+  int max_tokens;
+  int nseg;            // E (+1 with a shared expert)
+  bool has_shared;
+  bool all_resident;
+  std::vector<int32_t> h_expert_slot;  // expert -> segment position in (owner, id) order
+  std::vector<int32_t> h_seg_expert;   // segment position -> weight-table index
+  int first_local_seg, n_local_seg;
+  // device tables
+  __nv_bfloat16 *router_w;
+  float *select_bias, *logit_bias;
+  WeightRef *gate, *up, *down;  // [E+1], entry E = shared expert
+  int32_t *expert_slot, *seg_expert;
+  // workspace
+  float *logits, *topk_w;
+  int32_t *topk_idx, *local_rank, *chunk_cnt, *seg_count, *seg_off, *slot, *row_token;
+  int32_t *item_seg, *item_row0, *item_nrows, *n_items;
+  int item_cap;
+  __nv_bfloat16 *h, *y, *x_stage, *out_stage;
+  size_t h_rows_cap;  // rows the h scratch holds
+  size_t ws_bytes;
+  std::vector<void *> allocs;
+};
+
+template <class T>
+static bool ws_alloc(ColiMoe *m, T **p, size_t count) {
+  const size_t bytes = (count ? count : 1) * sizeof(T);
+  if (!coli_cuda_check(cudaMalloc((void **)p, bytes), "workspace allocation")) return false;
+  m->allocs.push_back(*p);
+  m->ws_bytes += bytes;
+  return true;
+}
+
+extern "C" void coli_b200_moe_destroy(ColiMoe *m) {
+  if (!m) return;
+  if (m->ctx) {
+    cudaSetDevice(m->ctx->device);
+    cudaStreamSynchronize(m->ctx->stream);
+  }
+  for (void *p : m->allocs) cudaFree(p);
+  delete m;
+}
+
+static int rows_per_item_for(const ColiMoeLayer &L, int rows, int nseg) {
+  const int avg = (rows + nseg - 1) / (nseg > 0 ? nseg : 1);
+  return avg <= 8 ? 8 : avg <= 16 ? 16 : 32;
+}
+
+extern "C" int coli_b200_moe_create(ColiMoe **out, const ColiMoeLayer *L, int max_tokens) {
+  if (!out || !L || max_tokens < 1) {
+    coli_set_error("moe_create: bad argument");
+    return 0;
+  }
+  if (L->H < 8 || L->H % 8 || L->I < 8 || L->I % 8 || L->E < 1 || L->E > 512 || L->k < 1 || L->k > 32 || L->k > L->E) {
+    coli_set_error("moe_create: unsupported shape H=%d I=%d E=%d k=%d (H, I multiples of 8; E <= 512; k <= min(32,E))", L->H, L->I, L->E, L->k);
+    return 0;
+  }
+  if (L->n_group > 1 && (L->E % L->n_group || L->n_group > 32 || L->topk_group < 1)) {
+    coli_set_error("moe_create: n_group=%d must divide E=%d and be <= 32", L->n_group, L->E);
+    return 0;
+  }
+  if (!fmt_supported(L->fmt) || !L->router_w || !L->gate || !L->up || !L->down) {
+    coli_set_error("moe_create: missing router/expert tables or unsupported format %d", L->fmt);
+    return 0;
+  }
+  if (!activation_supported()) return 0;
+  DeviceContext *ctx = find_ctx(L->device);
+  if (!select_ctx(ctx)) return 0;
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  ColiMoe *m = new ColiMoe();
+  m->L = *L;
+  m->ctx = ctx;
+  m->max_tokens = max_tokens;
+  m->ws_bytes = 0;
+  m->has_shared = L->sh_gate && L->sh_up && L->sh_down;
+  m->nseg = L->E + (m->has_shared ? 1 : 0);
+  const int E = L->E, H = L->H, I = L->I, k = L->k;
+  const int world = L->ep_world > 1 ? L->ep_world : 1;
+
+  // segment order = experts sorted by (owner rank, expert id); sharding.rs:197-203 for the default map
+  std::vector<int> owner(E);
+  for (int e = 0; e < E; ++e) {
+    owner[e] = world > 1 ? (L->expert_owner ? L->expert_owner[e] : (int)((int64_t)e * world / E)) : 0;
+    if (owner[e] < 0 || owner[e] >= world) {
+      coli_set_error("moe_create: expert %d has owner %d outside [0,%d)", e, owner[e], world);
+      delete m;
+      return 0;
+    }
+  }
+  m->h_expert_slot.assign(E, 0);
+  m->h_seg_expert.assign(E + 1, E);
+  m->first_local_seg = 0;
+  m->n_local_seg = 0;
+  {
+    int pos = 0;
+    for (int r = 0; r < world; ++r) {
+      if (r == L->ep_rank) m->first_local_seg = pos;
+      for (int e = 0; e < E; ++e)
+        if (owner[e] == r) {
+          m->h_expert_slot[e] = pos;
+          m->h_seg_expert[pos] = e;
+          ++pos;
+          if (r == L->ep_rank || world == 1) m->n_local_seg++;
+        }
+    }
+  }
+  // weight tables
+  std::vector<WeightRef> tg(E + 1), tu(E + 1), td(E + 1);
+  auto ref = [&](ColiCudaTensor *t, int wantI, int wantO, WeightRef &r, const char *name, int e) -> bool {
+    r.q = nullptr;
+    r.s = nullptr;
+    r.g = 0.0f;
+    r.pad = 0;
+    if (!t) return true;
+    if (t->fmt != L->fmt || t->I != wantI || t->O != wantO || t->device != L->device) {
+      coli_set_error("moe_create: %s of expert %d has fmt/shape/device %d/[%d,%d]/%d, expected %d/[%d,%d]/%d", name, e, t->fmt,
+                     t->O, t->I, t->device, L->fmt, wantO, wantI, L->device);
+      return false;
+    }
+    r.q = t->q;
+    r.s = t->s;
+    r.g = t->gscale;
+    return true;
+  };
+  m->all_resident = true;
+  bool ok = true;
+  for (int e = 0; e < E && ok; ++e) {
+    ok = ref(L->gate[e], H, I, tg[e], "gate", e) && ref(L->up[e], H, I, tu[e], "up", e) && ref(L->down[e], I, H, td[e], "down", e);
+    const bool have = L->gate[e] && L->up[e] && L->down[e];
+    if (!have) m->all_resident = false;
+    if (ok && !have && (world == 1 || owner[e] == L->ep_rank)) {
+      coli_set_error("moe_create: expert %d is owned by this rank but has no resident weights", e);
+      ok = false;
+    }
+  }
+  if (ok && m->has_shared)
+    ok = ref(L->sh_gate, H, I, tg[E], "shared gate", E) && ref(L->sh_up, H, I, tu[E], "shared up", E) &&
+         ref(L->sh_down, I, H, td[E], "shared down", E);
+  else if (ok)
+    ref(nullptr, 0, 0, tg[E], "", E), ref(nullptr, 0, 0, tu[E], "", E), ref(nullptr, 0, 0, td[E], "", E);
+
+  const size_t T = (size_t)max_tokens;
+  const size_t rows = T * k + T;
+  m->item_cap = (int)(rows / 8 + m->nseg + 1);
+  const int nchunk = (max_tokens + 31) / 32;
+  ok = ok && ws_alloc(m, &m->router_w, (size_t)E * H) && ws_alloc(m, &m->gate, E + 1) && ws_alloc(m, &m->up, E + 1) &&
+       ws_alloc(m, &m->down, E + 1) && ws_alloc(m, &m->expert_slot, E) && ws_alloc(m, &m->seg_expert, E + 1) &&
+       ws_alloc(m, &m->logits, T * E) && ws_alloc(m, &m->topk_w, T * k) && ws_alloc(m, &m->topk_idx, T * k) &&
+       ws_alloc(m, &m->local_rank, T * k) && ws_alloc(m, &m->chunk_cnt, (size_t)nchunk * E) &&
+       ws_alloc(m, &m->seg_count, E + 1) && ws_alloc(m, &m->seg_off, E + 2) && ws_alloc(m, &m->slot, T * k) &&
+       ws_alloc(m, &m->row_token, rows) && ws_alloc(m, &m->item_seg, m->item_cap) &&
+       ws_alloc(m, &m->item_row0, m->item_cap) && ws_alloc(m, &m->item_nrows, m->item_cap) && ws_alloc(m, &m->n_items, 1) &&
+       ws_alloc(m, &m->h, rows * I) && ws_alloc(m, &m->y, rows * H) && ws_alloc(m, &m->x_stage, T * H) &&
+       ws_alloc(m, &m->out_stage, T * H);
+  m->h_rows_cap = rows;
+  m->select_bias = nullptr;
+  m->logit_bias = nullptr;
+  if (ok && L->select_bias) ok = ws_alloc(m, &m->select_bias, E);
+  if (ok && L->logit_bias) ok = ws_alloc(m, &m->logit_bias, E);
+  cudaStream_t st = ctx->stream;
+  ok = ok && coli_cuda_check(cudaMemcpyAsync(m->router_w, L->router_w, (size_t)E * H * 2, cudaMemcpyHostToDevice, st), "router upload") &&
+       coli_cuda_check(cudaMemcpyAsync(m->gate, tg.data(), sizeof(WeightRef) * (E + 1), cudaMemcpyHostToDevice, st), "table upload") &&
+       coli_cuda_check(cudaMemcpyAsync(m->up, tu.data(), sizeof(WeightRef) * (E + 1), cudaMemcpyHostToDevice, st), "table upload") &&
+       coli_cuda_check(cudaMemcpyAsync(m->down, td.data(), sizeof(WeightRef) * (E + 1), cudaMemcpyHostToDevice, st), "table upload") &&
+       coli_cuda_check(cudaMemcpyAsync(m->expert_slot, m->h_expert_slot.data(), sizeof(int32_t) * E, cudaMemcpyHostToDevice, st), "table upload") &&
+       coli_cuda_check(cudaMemcpyAsync(m->seg_expert, m->h_seg_expert.data(), sizeof(int32_t) * (E + 1), cudaMemcpyHostToDevice, st), "table upload");
+  if (ok && L->select_bias)
+    ok = coli_cuda_check(cudaMemcpyAsync(m->select_bias, L->select_bias, sizeof(float) * E, cudaMemcpyHostToDevice, st), "bias upload");
+  if (ok && L->logit_bias)
+    ok = coli_cuda_check(cudaMemcpyAsync(m->logit_bias, L->logit_bias, sizeof(float) * E, cudaMemcpyHostToDevice, st), "bias upload");
+  ok = ok && coli_cuda_check(cudaStreamSynchronize(st), "moe_create sync");
+  // the handle keeps no host pointers
+  m->L.router_w = nullptr;
+  m->L.select_bias = nullptr;
+  m->L.logit_bias = nullptr;
+  m->L.expert_owner = nullptr;
+  m->L.gate = m->L.up = m->L.down = nullptr;
+  if (!ok) {
+    for (void *p : m->allocs) cudaFree(p);
+    delete m;
+    return 0;
+  }
+  *out = m;
+  return 1;
+}
+
+extern "C" size_t coli_b200_moe_workspace_bytes(const ColiMoe *m) { return m ? m->ws_bytes : 0; }
+
+static cudaStream_t pick_stream(ColiMoe *m, void *stream) { return stream ? (cudaStream_t)stream : m->ctx->stream; }
+
+static bool check_T(ColiMoe *m, int T, const char *who) {
+  if (!m) {
+    coli_set_error("%s: null handle", who);
+    return false;
+  }
+  if (T < 0 || T > m->max_tokens) {
+    coli_set_error("%s: T=%d outside [0,%d]", who, T, m->max_tokens);
+    return false;
+  }
+  return select_ctx(m->ctx);
+}
+
+static colib::RouteParams route_params(ColiMoe *m, const void *x_dev, int T) {
+  colib::RouteParams rp;
+  rp.T = T;
+  rp.H = m->L.H;
+  rp.E = m->L.E;
+  rp.k = m->L.k;
+  rp.score = m->L.score;
+  rp.norm_topk = m->L.norm_topk;
+  rp.routed_scale = m->L.routed_scale;
+  rp.n_group = m->L.n_group;
+  rp.topk_group = m->L.topk_group;
+  rp.x = (const __nv_bfloat16 *)x_dev;
+  rp.router_w = m->router_w;
+  rp.select_bias = m->select_bias;
+  rp.logit_bias = m->logit_bias;
+  rp.logits = m->logits;
+  rp.topk_idx = m->topk_idx;
+  rp.topk_w = m->topk_w;
+  return rp;
+}
+
+static colib::PermuteParams permute_params(ColiMoe *m, const void *x_dev, int T, bool with_shared, int rpi, void *rows_dev,
+                                           int32_t *seg_count, int32_t *slot) {
+  colib::PermuteParams pp;
+  pp.T = T;
+  pp.H = m->L.H;
+  pp.E = m->L.E;
+  pp.k = m->L.k;
+  pp.has_shared = with_shared ? 1 : 0;
+  pp.rows_per_item = rpi;
+  pp.topk_idx = m->topk_idx;
+  pp.expert_slot = m->expert_slot;
+  pp.local_rank = m->local_rank;
+  pp.chunk_cnt = m->chunk_cnt;
+  pp.seg_count = seg_count;
+  pp.seg_off = m->seg_off;
+  pp.slot = slot;
+  pp.row_token = m->row_token;
+  pp.item_seg = m->item_seg;
+  pp.item_row0 = m->item_row0;
+  pp.item_nrows = m->item_nrows;
+  pp.n_items = m->n_items;
+  pp.x = (const __nv_bfloat16 *)x_dev;
+  pp.xg = (__nv_bfloat16 *)rows_dev;
+  return pp;
+}
+
+extern "C" int coli_b200_moe_block_dev(ColiMoe *m, const void *x_dev, void *out_dev, int T, void *stream) {
+  if (!check_T(m, T, "moe_block_dev")) return 0;
+  if (!x_dev || !out_dev) {
+    coli_set_error("moe_block_dev: null pointer");
+    return 0;
+  }
+  if (!m->all_resident) {
+    coli_set_error("moe_block_dev: not every expert is resident on this rank; use the stage calls for expert parallelism");
+    return 0;
+  }
+  if (T == 0) return 1;
+  cudaStream_t st = pick_stream(m, stream);
+  const int k = m->L.k;
+  const int rows = T * k + (m->has_shared ? T : 0);
+  const int rpi = rows_per_item_for(m->L, rows, m->nseg);
+  if (!colib::launch_router(route_params(m, x_dev, T), st)) return 0;
+  if (!colib::launch_permute(permute_params(m, x_dev, T, m->has_shared, rpi, nullptr, m->seg_count, m->slot), st)) return 0;
+  colib::FfnParams fp;
+  fp.fmt = m->L.fmt;
+  fp.H = m->L.H;
+  fp.I = m->L.I;
+  fp.gate = m->gate;
+  fp.up = m->up;
+  fp.down = m->down;
+  fp.seg_expert = m->seg_expert;
+  fp.item_seg = m->item_seg;
+  fp.item_row0 = m->item_row0;
+  fp.item_nrows = m->item_nrows;
+  fp.n_items = m->n_items;
+  fp.max_items = rows / rpi + m->nseg;
+  fp.rows_per_item = rpi;
+  fp.x = (const __nv_bfloat16 *)x_dev;
+  fp.row_token = m->row_token;
+  fp.h = m->h;
+  fp.y = m->y;
+  fp.y32 = nullptr;
+  if (!colib::launch_ffn_small(fp, st)) return 0;
+  colib::CombineParams cp;
+  cp.T = T;
+  cp.H = m->L.H;
+  cp.k = k;
+  cp.has_shared = m->has_shared ? 1 : 0;
+  cp.y = m->y;
+  cp.shared_y = m->y + (size_t)T * k * m->L.H;
+  cp.slot = m->slot;
+  cp.topk_w = m->topk_w;
+  cp.out = (__nv_bfloat16 *)out_dev;
+  return colib::launch_combine(cp, st);
+}
+
+extern "C" int coli_b200_moe_last_routing(ColiMoe *m, int T, int32_t *topk_idx, float *topk_w) {
+  if (!check_T(m, T, "moe_last_routing")) return 0;
+  if (!coli_cuda_check(cudaDeviceSynchronize(), "routing read sync")) return 0;
+  const size_t n = (size_t)T * m->L.k;
+  if (topk_idx && !coli_cuda_check(cudaMemcpy(topk_idx, m->topk_idx, n * sizeof(int32_t), cudaMemcpyDeviceToHost), "routing read")) return 0;
+  if (topk_w && !coli_cuda_check(cudaMemcpy(topk_w, m->topk_w, n * sizeof(float), cudaMemcpyDeviceToHost), "routing read")) return 0;
+  return 1;
+}
+
+extern "C" int coli_b200_moe_block(ColiMoe *m, const void *x, void *out, int T, int32_t *topk_idx, float *topk_w) {
+  if (!check_T(m, T, "moe_block")) return 0;
+  if (!x || !out) {
+    coli_set_error("moe_block: null pointer");
+    return 0;
+  }
+  if (T == 0) return 1;
+  std::lock_guard<std::mutex> lk(m->ctx->mu);
+  cudaStream_t st = m->ctx->stream;
+  const size_t bytes = (size_t)T * m->L.H * sizeof(__nv_bfloat16);
+  CK(cudaMemcpyAsync(m->x_stage, x, bytes, cudaMemcpyHostToDevice, st), "moe_block input upload");
+  if (!coli_b200_moe_block_dev(m, m->x_stage, m->out_stage, T, st)) return 0;
+  CK(cudaMemcpyAsync(out, m->out_stage, bytes, cudaMemcpyDeviceToHost, st), "moe_block output download");
+  const size_t n = (size_t)T * m->L.k;
+  if (topk_idx) CK(cudaMemcpyAsync(topk_idx, m->topk_idx, n * sizeof(int32_t), cudaMemcpyDeviceToHost, st), "routing download");
+  if (topk_w) CK(cudaMemcpyAsync(topk_w, m->topk_w, n * sizeof(float), cudaMemcpyDeviceToHost, st), "routing download");
+  CK(cudaStreamSynchronize(st), "moe_block sync");
+  return 1;
+}
+
+// ---- stages ----------------------------------------------------------------------------------------
+extern "C" int coli_b200_moe_route_dev(ColiMoe *m, const void *x_dev, int T, void *rows_dev, int32_t *seg_count_dev,
+                                       int32_t *slot_dev, void *stream) {
+  if (!check_T(m, T, "moe_route_dev")) return 0;
+  if (!x_dev || !rows_dev || !seg_count_dev || !slot_dev) {
+    coli_set_error("moe_route_dev: null pointer");
+    return 0;
+  }
+  cudaStream_t st = pick_stream(m, stream);
+  if (T == 0) return coli_cuda_check(cudaMemsetAsync(seg_count_dev, 0, sizeof(int32_t) * m->L.E, st), "count clear") ? 1 : 0;
+  if (!colib::launch_router(route_params(m, x_dev, T), st)) return 0;
+  return colib::launch_permute(permute_params(m, x_dev, T, false, 32, rows_dev, seg_count_dev, slot_dev), st);
+}
+
+// h scratch for the stage calls grows on demand (synchronises the device when it does).
+static bool ensure_h(ColiMoe *m, size_t rows) {
+  if (rows <= m->h_rows_cap) return true;
+  if (!coli_cuda_check(cudaDeviceSynchronize(), "scratch regrow sync")) return false;
+  __nv_bfloat16 *nh = nullptr;
+  if (!coli_cuda_check(cudaMalloc((void **)&nh, rows * m->L.I * sizeof(__nv_bfloat16)), "scratch regrow")) return false;
+  m->allocs.push_back(nh);  // the old block is released with the handle
+  m->ws_bytes += rows * m->L.I * sizeof(__nv_bfloat16);
+  m->h = nh;
+  m->h_rows_cap = rows;
+  return true;
+}
+static bool ensure_items(ColiMoe *m, int need) {
+  if (need <= m->item_cap) return true;
+  if (!coli_cuda_check(cudaDeviceSynchronize(), "work list regrow sync")) return false;
+  m->item_cap = need;
+  return ws_alloc(m, &m->item_seg, need) && ws_alloc(m, &m->item_row0, need) && ws_alloc(m, &m->item_nrows, need);
+}
+
+static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, const WeightRef *d, const int32_t *seg_expert_dev,
+                        const void *rows_dev, const int32_t *seg_count_dev, int n_seg, int n_rows, void *y_dev,
+                        cudaStream_t st) {
+  if (n_rows == 0) return 1;
+  const int rpi = rows_per_item_for(m->L, n_rows, n_seg);
+  const int max_items = n_rows / rpi + n_seg;
+  if (!ensure_h(m, (size_t)n_rows) || !ensure_items(m, max_items)) return 0;
+  if (!colib::launch_items_from_counts(seg_count_dev, n_seg, rpi, m->seg_off, m->item_seg, m->item_row0, m->item_nrows,
+                                       m->n_items, st))
+    return 0;
+  colib::FfnParams fp;
+  fp.fmt = m->L.fmt;
+  fp.H = m->L.H;
+  fp.I = m->L.I;
+  fp.gate = g;
+  fp.up = u;
+  fp.down = d;
+  fp.seg_expert = seg_expert_dev;
+  fp.item_seg = m->item_seg;
+  fp.item_row0 = m->item_row0;
+  fp.item_nrows = m->item_nrows;
+  fp.n_items = m->n_items;
+  fp.max_items = max_items;
+  fp.rows_per_item = rpi;
+  fp.x = (const __nv_bfloat16 *)rows_dev;
+  fp.row_token = nullptr;
+  fp.h = m->h;
+  fp.y = (__nv_bfloat16 *)y_dev;
+  fp.y32 = nullptr;
+  return colib::launch_ffn_small(fp, st);
+}
+
+extern "C" int coli_b200_moe_experts_dev(ColiMoe *m, const void *rows_dev, const int32_t *seg_count_dev, int first_seg,
+                                         int n_seg, int n_rows, void *y_dev, void *stream) {
+  if (!m || !select_ctx(m->ctx)) return 0;
+  if (n_seg < 0 || first_seg < 0 || first_seg + n_seg > m->L.E || n_rows < 0 || (n_rows > 0 && (!rows_dev || !y_dev || !seg_count_dev))) {
+    coli_set_error("moe_experts_dev: bad segment range [%d,%d) or null pointer", first_seg, first_seg + n_seg);
+    return 0;
+  }
+  if (first_seg < m->first_local_seg || first_seg + n_seg > m->first_local_seg + m->n_local_seg) {
+    coli_set_error("moe_experts_dev: segments [%d,%d) are not all resident on rank %d (local range [%d,%d))", first_seg,
+                   first_seg + n_seg, m->L.ep_rank, m->first_local_seg, m->first_local_seg + m->n_local_seg);
+    return 0;
+  }
+  return run_segments(m, m->gate, m->up, m->down, m->seg_expert + first_seg, rows_dev, seg_count_dev, n_seg, n_rows, y_dev,
+                      pick_stream(m, stream));
+}
+
+extern "C" int coli_b200_moe_shared_dev(ColiMoe *m, const void *x_dev, int T, void *y_dev, void *stream) {
+  if (!check_T(m, T, "moe_shared_dev")) return 0;
+  if (!m->has_shared) {
+    coli_set_error("moe_shared_dev: the layer has no shared expert");
+    return 0;
+  }
+  if (T == 0) return 1;
+  cudaStream_t st = pick_stream(m, stream);
+  // one segment of T rows; its count lives in seg_count[E]
+  if (!coli_cuda_check(cudaMemcpyAsync(m->seg_count + m->L.E, &T, sizeof(int32_t), cudaMemcpyHostToDevice, st), "shared count"))
+    return 0;
+  return run_segments(m, m->gate + m->L.E, m->up + m->L.E, m->down + m->L.E, nullptr, x_dev, m->seg_count + m->L.E, 1, T, y_dev, st);
+}
+
+extern "C" int coli_b200_moe_combine_dev(ColiMoe *m, const void *y_rows_dev, const int32_t *slot_dev,
+                                         const void *shared_y_dev, void *out_dev, int T, void *stream) {
+  if (!check_T(m, T, "moe_combine_dev")) return 0;
+  if (T == 0) return 1;
+  if (!y_rows_dev || !slot_dev || !out_dev) {
+    coli_set_error("moe_combine_dev: null pointer");
+    return 0;
+  }
+  colib::CombineParams cp;
+  cp.T = T;
+  cp.H = m->L.H;
+  cp.k = m->L.k;
+  cp.has_shared = shared_y_dev ? 1 : 0;
+  cp.y = (const __nv_bfloat16 *)y_rows_dev;
+  cp.shared_y = (const __nv_bfloat16 *)shared_y_dev;
+  cp.slot = slot_dev;
+  cp.topk_w = m->topk_w;
+  cp.out = (__nv_bfloat16 *)out_dev;
+  return colib::launch_combine(cp, pick_stream(m, stream));
+}
+
+// sharding.rs:251-265
+extern "C" uint64_t coli_b200_sharding_fingerprint(uint32_t num_nodes, uint32_t n_experts, const uint32_t *owner) {
+  uint64_t h = 0xcbf29ce484222325ull;
+  auto mix = [&](uint32_t v) {
+    for (int b = 0; b < 4; ++b) {
+      h ^= (uint64_t)((v >> (8 * b)) & 0xffu);
+      h *= 0x00000100000001b3ull;
+    }
+  };
+  mix(num_nodes);
+  mix(n_experts);
+  for (uint32_t e = 0; e < n_experts; ++e) mix(owner ? owner[e] : (uint32_t)((uint64_t)e * num_nodes / n_experts));
+  return h;
+}
+
+// ---- the reference's host-pointer expert calls -------------------------------------------------------
+// Same contract as backend_cuda.cu:3668-3806 / 4410-4792 (host f32 in, host f32 out, synchronous,
+// one mutex per device held across the call).  Activations are rounded to bf16 on the device
+// (the kernels are W4A16 / W8A16 with bf16 activations); outputs are written as f32.
+static int run_host_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups, ColiCudaTensor *const *downs,
+                          const int *rows, int count, float *y, const float *x, int want_fmt_a, int want_fmt_b,
+                          const char *who) {
+  if (!gates || !ups || !downs || !rows || !x || !y || count < 1 || !gates[0]) {
+    coli_set_error("%s: null pointer or empty group", who);
+    return 0;
+  }
+  if (!activation_supported()) return 0;
+  const int device = gates[0]->device, D = gates[0]->I, I = gates[0]->O, fmt = gates[0]->fmt;
+  long total = 0;
+  for (int c = 0; c < count; ++c) {
+    ColiCudaTensor *g = gates[c], *u = ups[c], *d = downs[c];
+    if (!g || !u || !d || rows[c] < 1 || g->fmt != fmt || u->fmt != fmt || d->fmt != fmt ||
+        (fmt != want_fmt_a && fmt != want_fmt_b) || g->device != device || u->device != device || d->device != device ||
+        g->I != D || g->O != I || u->I != D || u->O != I || d->I != I || d->O != D) {
+      coli_set_error("%s: expert %d has a mismatched format, shape or device", who, c);
+      return 0;
+    }
+    total += rows[c];
+  }
+  if (D % 8 || I % 8) {
+    coli_set_error("%s: D=%d and I=%d must be multiples of 8", who, D, I);
+    return 0;
+  }
+  DeviceContext *ctx = find_ctx(device);
+  if (!select_ctx(ctx)) return 0;
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  cudaStream_t st = ctx->stream;
+  const int avg = (int)((total + count - 1) / count);
+  const int rpi = avg <= 8 ? 8 : avg <= 16 ? 16 : 32;
+  const int max_items = (int)(total / rpi) + count;
+  const size_t xb = (size_t)total * D;
+  // slots: 0 x f32 / y f32, 1 x bf16, 2 h bf16, 3 tables + counts + work list
+  const size_t tbl_bytes = sizeof(WeightRef) * 3 * count + sizeof(int32_t) * (2 * count + 2 + 3 * (size_t)max_items + 1);
+  if (!reserve(ctx, 0, xb * sizeof(float)) || !reserve(ctx, 1, xb * sizeof(__nv_bfloat16)) ||
+      !reserve(ctx, 2, (size_t)total * I * sizeof(__nv_bfloat16)) || !reserve(ctx, 3, tbl_bytes))
+    return 0;
+  std::vector<WeightRef> tbl(3 * (size_t)count);
+  for (int c = 0; c < count; ++c) {
+    tbl[c] = WeightRef{gates[c]->q, gates[c]->s, gates[c]->gscale, 0};
+    tbl[count + c] = WeightRef{ups[c]->q, ups[c]->s, ups[c]->gscale, 0};
+    tbl[2 * count + c] = WeightRef{downs[c]->q, downs[c]->s, downs[c]->gscale, 0};
+  }
+  WeightRef *d_tbl = (WeightRef *)ctx->buf[3];
+  int32_t *d_cnt = (int32_t *)(d_tbl + 3 * (size_t)count);
+  int32_t *d_off = d_cnt + count;
+  int32_t *d_iseg = d_off + count + 1;
+  int32_t *d_irow = d_iseg + max_items;
+  int32_t *d_inr = d_irow + max_items;
+  int32_t *d_nit = d_inr + max_items;
+  CK(cudaMemcpyAsync(ctx->buf[0], x, xb * sizeof(float), cudaMemcpyHostToDevice, st), "expert input upload");
+  CK(cudaMemcpyAsync(d_tbl, tbl.data(), sizeof(WeightRef) * tbl.size(), cudaMemcpyHostToDevice, st), "expert table upload");
+  CK(cudaMemcpyAsync(d_cnt, rows, sizeof(int32_t) * count, cudaMemcpyHostToDevice, st), "row count upload");
+  CK(cudaStreamSynchronize(st), "expert upload sync");  // tbl is a local; rows/x belong to the caller
+  if (!colib::launch_f32_to_bf16((const float *)ctx->buf[0], (__nv_bfloat16 *)ctx->buf[1], xb, st)) return 0;
+  if (!colib::launch_items_from_counts(d_cnt, count, rpi, d_off, d_iseg, d_irow, d_inr, d_nit, st)) return 0;
+  colib::FfnParams fp;
+  fp.fmt = fmt;
+  fp.H = D;
+  fp.I = I;
+  fp.gate = d_tbl;
+  fp.up = d_tbl + count;
+  fp.down = d_tbl + 2 * count;
+  fp.seg_expert = nullptr;
+  fp.item_seg = d_iseg;
+  fp.item_row0 = d_irow;
+  fp.item_nrows = d_inr;
+  fp.n_items = d_nit;
+  fp.max_items = max_items;
+  fp.rows_per_item = rpi;
+  fp.x = (const __nv_bfloat16 *)ctx->buf[1];
+  fp.row_token = nullptr;
+  fp.h = (__nv_bfloat16 *)ctx->buf[2];
+  fp.y = nullptr;
+  fp.y32 = (float *)ctx->buf[0];  // x f32 is dead once converted
+  if (!colib::launch_ffn_small(fp, st)) return 0;
+  CK(cudaMemcpyAsync(y, ctx->buf[0], xb * sizeof(float), cudaMemcpyDeviceToHost, st), "expert output download");
+  CK(cudaStreamSynchronize(st), "expert call sync");
+  return 1;
+}
+
+extern "C" int coli_cuda_expert_group_nvfp4(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                                            ColiCudaTensor *const *downs, const int *rows, int count, float *y,
+                                            const float *x) {
+  return run_host_group(gates, ups, downs, rows, count, y, x, COLI_FMT_NVFP4, COLI_FMT_NVFP4, "expert_group_nvfp4");
+}
+extern "C" int coli_cuda_expert_mlp_nvfp4(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down, float *y,
+                                          const float *x, int S) {
+  return run_host_group(&gate, &up, &down, &S, 1, y, x, COLI_FMT_NVFP4, COLI_FMT_NVFP4, "expert_mlp_nvfp4");
+}
+extern "C" int coli_cuda_expert_mlp_fp8(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down, float *y,
+                                        const float *x, int S) {
+  return run_host_group(&gate, &up, &down, &S, 1, y, x, COLI_FMT_E4M3_ROW, COLI_FMT_FP8_B128, "expert_mlp_fp8");
+}
+
+// Router GEMM through the generic matmul entry (fmt 0 only): gpu.rs:2219-2249 -> backend_cuda.cu:3063-3075.
+extern "C" int coli_cuda_matmul(ColiCudaTensor **tensor, float *y, const float *x, const void *weights,
+                                const float *scales, int fmt, int S, int I, int O, int device) {
+  (void)scales;
+  if (fmt != COLI_FMT_F32) {
+    coli_set_error("coli_cuda_matmul: only fmt 0 (the f32 router GEMM) goes through this entry; got %d", fmt);
+    return 0;
+  }
+  if (!tensor || !y || !x || S < 1 || I < 1 || O < 1 || (!*tensor && !weights)) {
+    coli_set_error("coli_cuda_matmul: bad argument");
+    return 0;
+  }
+  DeviceContext *ctx = find_ctx(device);
+  if (!select_ctx(ctx)) return 0;
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  cudaStream_t st = ctx->stream;
+  if (*tensor) {
+    if (!existing_matches(*tensor, fmt, I, O, device)) {
+      coli_set_error("coli_cuda_matmul: cached tensor does not match fmt/I/O/device");
+      return 0;
+    }
+  } else {
+    ColiCudaTensor *t = static_cast<ColiCudaTensor *>(calloc(1, sizeof(ColiCudaTensor)));
+    if (!t) return 0;
+    t->fmt = fmt;
+    t->I = I;
+    t->O = O;
+    t->device = device;
+    t->q_bytes = sizeof(float) * (size_t)I * O;
+    if (!coli_cuda_check(cudaMalloc((void **)&t->q, t->q_bytes), "tensor allocation") ||
+        !coli_cuda_check(cudaMemcpyAsync(t->q, weights, t->q_bytes, cudaMemcpyHostToDevice, st), "tensor upload") ||
+        !coli_cuda_check(cudaStreamSynchronize(st), "tensor upload sync")) {
+      if (t->q) cudaFree(t->q);
+      free(t);
+      return 0;
+    }
+    ctx->tensor_count++;
+    ctx->tensor_bytes += t->q_bytes;
+    *tensor = t;
+  }
+  const size_t xb = sizeof(float) * (size_t)S * I, yb = sizeof(float) * (size_t)S * O;
+  if (!reserve(ctx, 0, xb) || !reserve(ctx, 1, yb)) return 0;
+  CK(cudaMemcpyAsync(ctx->buf[0], x, xb, cudaMemcpyHostToDevice, st), "matmul input upload");
+  if (!colib::launch_matmul_f32_seq((const float *)ctx->buf[0], (const float *)(*tensor)->q, (float *)ctx->buf[1], S, I, O, st))
+    return 0;
+  CK(cudaMemcpyAsync(y, ctx->buf[1], yb, cudaMemcpyDeviceToHost, st), "matmul output download");
+  CK(cudaStreamSynchronize(st), "matmul sync");
+  return 1;
+}

@@ -1,0 +1,85 @@
+// Weighted combine: out[t] = sum_kk w[t,kk] * y[slot[t,kk]] (kk ascending, f32) + shared[t],
+// rounded once to bf16 — crates/colibri-engine/src/moe.rs:1549-1553 (routed accumulate),
+// 1875-1885 (shared expert added after the routed sum).  A gather per output row instead of the
+// reference's scatter-add, so the f32 order is fixed and no atomics are needed.
+#include "internal.cuh"
+
+namespace colib {
+
+__global__ void __launch_bounds__(256) k_combine(CombineParams p, const __nv_bfloat16 *shared_y) {
+  const int t = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;  // 8-element column group
+  if (c * 8 >= p.H) return;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+  for (int kk = 0; kk < p.k; ++kk) {
+    const float w = p.topk_w[(size_t)t * p.k + kk];
+    const int row = p.slot[(size_t)t * p.k + kk];
+    const uint4 v = *reinterpret_cast<const uint4 *>(p.y + (size_t)row * p.H + c * 8);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc[2 * i] = fmaf(w, __uint_as_float(u[i] << 16), acc[2 * i]);
+      acc[2 * i + 1] = fmaf(w, __uint_as_float(u[i] & 0xffff0000u), acc[2 * i + 1]);
+    }
+  }
+  if (shared_y) {
+    const uint4 v = *reinterpret_cast<const uint4 *>(shared_y + (size_t)t * p.H + c * 8);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc[2 * i] += __uint_as_float(u[i] << 16);
+      acc[2 * i + 1] += __uint_as_float(u[i] & 0xffff0000u);
+    }
+  }
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t lo = __bfloat16_as_ushort(__float2bfloat16_rn(acc[2 * i]));
+    const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rn(acc[2 * i + 1]));
+    o[i] = lo | (hi << 16);
+  }
+  *reinterpret_cast<uint4 *>(p.out + (size_t)t * p.H + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+int launch_combine(const CombineParams &p, cudaStream_t st) {
+  if (p.T <= 0) return 1;
+  if (p.H % 8) {
+    coli_set_error("combine: H=%d must be a multiple of 8", p.H);
+    return 0;
+  }
+  const __nv_bfloat16 *shared_y = p.has_shared ? p.shared_y : nullptr;
+  dim3 grid((p.H / 8 + 255) / 256, p.T);
+  k_combine<<<grid, 256, 0, st>>>(p, shared_y);
+  return coli_cuda_check(cudaGetLastError(), "combine launch") ? 1 : 0;
+}
+
+__global__ void k_f32_to_bf16(const float *src, __nv_bfloat16 *dst, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    dst[i] = __float2bfloat16_rn(src[i]);
+}
+int launch_f32_to_bf16(const float *src, __nv_bfloat16 *dst, size_t n, cudaStream_t st) {
+  if (n == 0) return 1;
+  const size_t blocks = (n + 255) / 256;
+  k_f32_to_bf16<<<(unsigned)(blocks > 4736 ? 4736 : blocks), 256, 0, st>>>(src, dst, n);
+  return coli_cuda_check(cudaGetLastError(), "f32->bf16 launch") ? 1 : 0;
+}
+
+__global__ void k_matmul_f32_seq(const float *x, const float *w, float *y, int S, int I, int O) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)S * O) return;
+  const int s = (int)(idx / O), o = (int)(idx % O);
+  const float *xr = x + (size_t)s * I, *wr = w + (size_t)o * I;
+  float acc = 0.0f;
+  for (int k = 0; k < I; ++k) acc = __fadd_rn(acc, __fmul_rn(xr[k], wr[k]));
+  y[idx] = acc;
+}
+int launch_matmul_f32_seq(const float *x, const float *w, float *y, int S, int I, int O, cudaStream_t st) {
+  const size_t n = (size_t)S * O;
+  if (n == 0) return 1;
+  k_matmul_f32_seq<<<(unsigned)((n + 127) / 128), 128, 0, st>>>(x, w, y, S, I, O);
+  return coli_cuda_check(cudaGetLastError(), "f32 matmul launch") ? 1 : 0;
+}
+
+}  // namespace colib

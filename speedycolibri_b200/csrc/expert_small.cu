@@ -1,0 +1,351 @@
+// Expert FFN for decode-sized segments: a weight-streaming dequant-GEMV/GEMM in which every
+// weight byte is read from HBM exactly once per work item with 128-bit loads, decoded to
+// bf16 in registers, and contracted against up to 32 token rows with warp-level bf16 MMA
+// (m16n8k16, f32 accumulate).  The path is HBM-bound: the MMA only takes the multiply-adds
+// off the CUDA cores so that the decode arithmetic (about 2.5 integer/half2 operations per
+// FP4 weight) is all the SM has to issue per byte streamed.
+//
+// It replaces the reference's per-expert launch trios nvfp4_gemv / nvfp4_wsmm / fp8a16_gemv
+// (crates/colibri-backend/cuda/backend_cuda.cu:707-1110,1436-1510,468-496, dispatched from
+// 4738-4783) with two launches for ALL experts of a layer: gate+up with SiLU*mul fused
+// (the reference runs `silu_mul` as a separate launch, backend_cuda.cu:3785-3787), then down.
+//
+// Numerics (W4A16 as in crates/colibri-engine/src/linear.rs:110-133): activations stay bf16
+// (exact), a decoded weight E2M1*ue4m3 has at most 6 significant bits and is exact in bf16, so
+// each product is exact and only the f32 summation order differs from the CPU sum.  The
+// per-tensor scale is applied once per output, as the reference does.  The intermediate
+// h = silu(g)*u is rounded to bf16 before the down projection.
+//
+// Work decomposition: grid = (row tiles of 16 outputs, work items); an item is at most 8*NB
+// consecutive rows of one expert segment.  The W warps of a CTA split the K axis (k-tile kt
+// goes to warp kt % W) so that even a single-token decode exposes thousands of warps, and
+// reduce through shared memory.
+#include "internal.cuh"
+
+namespace colib {
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t hmul2_bf16(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;\n" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint4 ldg_nc_v4(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// A NVFP4 word holds 8 consecutive k: even elements in nibble slots 0..3, odd in slots 4..7.
+// Placing the three magnitude bits e,e,m of a nibble at bf16 bits 8..6 yields the E2M1 value
+// times 2^-126 (a bf16 subnormal for 0.5); `mult` = ue4m3 scale * 2^110 in both halves brings
+// the pair to weight * 2^-16 exactly.  Pair p = elements (2p, 2p+1).
+template <int P>
+__device__ __forceinline__ uint32_t fp4_pair(uint32_t w, uint32_t mult) {
+  uint32_t mag, sgn;
+  if (P == 0) {
+    mag = (w << 6) & 0x01C001C0u;
+    sgn = (w << 12) & 0x80008000u;
+  } else if (P == 1) {
+    mag = (w << 2) & 0x01C001C0u;
+    sgn = (w << 8) & 0x80008000u;
+  } else if (P == 2) {
+    mag = (w >> 2) & 0x01C001C0u;
+    sgn = (w << 4) & 0x80008000u;
+  } else {
+    mag = (w >> 6) & 0x01C001C0u;
+    sgn = w & 0x80008000u;
+  }
+  return hmul2_bf16(mag | sgn, mult);
+}
+// An FP8 word holds bytes [k0, k2, k1, k3].  An e4m3 byte s.eeee.mmm placed at bf16 bits
+// 15 | 10..4 is the value times 2^-120; the multiply by 2^120 normalises it exactly.
+template <int P>
+__device__ __forceinline__ uint32_t fp8_pair(uint32_t w) {
+  uint32_t mag, sgn;
+  if (P == 0) {
+    mag = (w << 4) & 0x07F007F0u;
+    sgn = (w << 8) & 0x80008000u;
+  } else {
+    mag = (w >> 4) & 0x07F007F0u;
+    sgn = w & 0x80008000u;
+  }
+  return hmul2_bf16(mag | sgn, 0x7B807B80u);  // bf16 2^120 in both halves
+}
+
+constexpr float kFp4AccScale = 65536.0f;  // undoes the 2^-16 carried by decoded NVFP4 weights
+
+template <int FMT>
+struct AFrag {
+  // raw bytes of rows g and g+8 of one 16-row tile for one k-tile, as loaded by this lane
+  uint4 lo[FMT == COLI_FMT_NVFP4 ? 1 : 2], hi[FMT == COLI_FMT_NVFP4 ? 1 : 2];
+  uint32_t sc;  // NVFP4: two scale bytes of row g (low 16 bits) and of row g+8 (high 16 bits)
+};
+
+template <int FMT>
+__device__ __forceinline__ void load_a(AFrag<FMT> &f, const WeightRef &w, int Op, int r0, int kt, int lane) {
+  if (FMT == COLI_FMT_NVFP4) {
+    const uint8_t *slab = w.q + ((size_t)kt * Op + r0) * 64;
+    f.lo[0] = ldg_nc_v4(slab + lane * 16);
+    f.hi[0] = ldg_nc_v4(slab + 512 + lane * 16);
+    const uint8_t *ss = w.s + ((size_t)kt * Op + r0) * 8;
+    const uint32_t s0 = *reinterpret_cast<const uint16_t *>(ss + lane * 2);
+    const uint32_t s1 = *reinterpret_cast<const uint16_t *>(ss + 64 + lane * 2);
+    f.sc = s0 | (s1 << 16);
+  } else {
+    const uint8_t *slab = w.q + ((size_t)kt * Op + r0) * 128;
+    f.lo[0] = ldg_nc_v4(slab + lane * 32);
+    f.lo[1] = ldg_nc_v4(slab + lane * 32 + 16);
+    f.hi[0] = ldg_nc_v4(slab + 1024 + lane * 32);
+    f.hi[1] = ldg_nc_v4(slab + 1024 + lane * 32 + 16);
+    f.sc = 0;
+  }
+}
+
+// Decode the fragment of MMA step m (0..7) of a k-tile: a[0],a[2] = row g pairs, a[1],a[3] = row g+8.
+template <int FMT>
+__device__ __forceinline__ void decode_a(const AFrag<FMT> &f, int m, const uint32_t *lut, uint32_t (&a)[4]) {
+  if (FMT == COLI_FMT_NVFP4) {
+    const uint32_t wl = (&f.lo[0].x)[m >> 1], wh = (&f.hi[0].x)[m >> 1];
+    const uint32_t ml = lut[(f.sc >> ((m >> 2) * 8)) & 0xffu];
+    const uint32_t mh = lut[(f.sc >> (16 + (m >> 2) * 8)) & 0xffu];
+    if (m & 1) {
+      a[0] = fp4_pair<2>(wl, ml);
+      a[2] = fp4_pair<3>(wl, ml);
+      a[1] = fp4_pair<2>(wh, mh);
+      a[3] = fp4_pair<3>(wh, mh);
+    } else {
+      a[0] = fp4_pair<0>(wl, ml);
+      a[2] = fp4_pair<1>(wl, ml);
+      a[1] = fp4_pair<0>(wh, mh);
+      a[3] = fp4_pair<1>(wh, mh);
+    }
+  } else {
+    const uint32_t wl = (&f.lo[m >> 2].x)[m & 3], wh = (&f.hi[m >> 2].x)[m & 3];
+    a[0] = fp8_pair<0>(wl);
+    a[2] = fp8_pair<1>(wl);
+    a[1] = fp8_pair<0>(wh);
+    a[3] = fp8_pair<1>(wh);
+  }
+}
+
+// GATED: two matrices (gate, up) -> h = silu(g)*u;  otherwise one matrix (down) -> y.
+template <int FMT, int NB, bool GATED>
+__global__ void __launch_bounds__(256) k_ffn_mm(FfnParams p) {
+  constexpr int MATS = GATED ? 2 : 1;
+  extern __shared__ __align__(16) float red[];  // [W][MATS*NB*4][32]
+  __shared__ uint32_t lut[256];
+  const int item = blockIdx.y;
+  if (item >= *p.n_items) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int K = GATED ? p.H : p.I;     // contraction length
+  const int Oout = GATED ? p.I : p.H;  // output features
+  const int Kp = (K + 127) & ~127, KT = Kp >> 7, Op = (Oout + 15) & ~15;
+  const int r0 = blockIdx.x * 16;
+  const int seg = p.item_seg[item], row0 = p.item_row0[item], nrows = p.item_nrows[item];
+  const int ex = p.seg_expert ? p.seg_expert[seg] : seg;
+  const WeightRef w0 = GATED ? p.gate[ex] : p.down[ex];
+  const WeightRef w1 = GATED ? p.up[ex] : w0;
+
+  if (FMT == COLI_FMT_NVFP4) {
+    for (int b = threadIdx.x; b < 256; b += blockDim.x) {
+      const float s = coli_e4m3_to_f32((uint8_t)b) * 1.2980742146337069e33f;  // * 2^110
+      const uint32_t h = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(s));
+      lut[b] = h | (h << 16);
+    }
+    __syncthreads();
+  }
+
+  // source row of token column g of each 8-token block (nullptr = column beyond the item)
+  const __nv_bfloat16 *src = GATED ? p.x : p.h;
+  const __nv_bfloat16 *xrow[NB];
+#pragma unroll
+  for (int j = 0; j < NB; ++j) {
+    const int r = 8 * j + g;
+    if (r < nrows) {
+      const int row = row0 + r;
+      const size_t sidx = (GATED && p.row_token) ? (size_t)p.row_token[row] : (size_t)row;
+      xrow[j] = src + sidx * K;
+    } else {
+      xrow[j] = nullptr;
+    }
+  }
+
+  float acc[MATS][NB][4];
+#pragma unroll
+  for (int mtx = 0; mtx < MATS; ++mtx)
+#pragma unroll
+    for (int j = 0; j < NB; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[mtx][j][c] = 0.0f;
+
+  AFrag<FMT> cur[MATS], nxt[MATS];
+  int kt = warp;
+  if (kt < KT) {
+    load_a<FMT>(cur[0], w0, Op, r0, kt, lane);
+    if (GATED) load_a<FMT>(cur[MATS - 1], w1, Op, r0, kt, lane);
+  }
+  for (; kt < KT; kt += W) {
+    const int ktn = kt + W;
+    if (ktn < KT) {
+      load_a<FMT>(nxt[0], w0, Op, r0, ktn, lane);
+      if (GATED) load_a<FMT>(nxt[MATS - 1], w1, Op, r0, ktn, lane);
+    }
+    // token fragments of this k-tile: lane (g,t) reads x[token g][kt*128 + 32t .. +31], 16 bytes
+    // (two MMA steps) at a time
+    const int kbase = kt * 128 + t * 32;
+    float part[MATS][NB][4];
+    if (FMT == COLI_FMT_FP8_B128) {
+#pragma unroll
+      for (int mtx = 0; mtx < MATS; ++mtx)
+#pragma unroll
+        for (int j = 0; j < NB; ++j)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) part[mtx][j][c] = 0.0f;
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint4 xb[NB];
+#pragma unroll
+      for (int j = 0; j < NB; ++j) {
+        xb[j] = make_uint4(0, 0, 0, 0);
+        if (xrow[j] != nullptr && kbase + c * 8 + 8 <= K)
+          xb[j] = *reinterpret_cast<const uint4 *>(xrow[j] + kbase + c * 8);
+      }
+#pragma unroll
+      for (int mm = 0; mm < 2; ++mm) {
+        const int m = 2 * c + mm;
+#pragma unroll
+        for (int mtx = 0; mtx < MATS; ++mtx) {
+          uint32_t a[4];
+          decode_a<FMT>(cur[mtx], m, lut, a);
+#pragma unroll
+          for (int j = 0; j < NB; ++j) {
+            const uint32_t b0 = mm ? xb[j].z : xb[j].x, b1 = mm ? xb[j].w : xb[j].y;
+            if (FMT == COLI_FMT_FP8_B128)
+              mma_bf16_16816(part[mtx][j], a, b0, b1);
+            else
+              mma_bf16_16816(acc[mtx][j], a, b0, b1);
+          }
+        }
+      }
+    }
+    if (FMT == COLI_FMT_FP8_B128) {
+      // one f32 scale per (128-row block, k-tile): convert.rs:731-741
+#pragma unroll
+      for (int mtx = 0; mtx < MATS; ++mtx) {
+        const float *sc = reinterpret_cast<const float *>(mtx == 0 ? w0.s : w1.s);
+        const float s = sc[(size_t)(r0 >> 7) * KT + kt];
+#pragma unroll
+        for (int j = 0; j < NB; ++j)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) acc[mtx][j][c] = fmaf(s, part[mtx][j][c], acc[mtx][j][c]);
+      }
+    }
+#pragma unroll
+    for (int mtx = 0; mtx < MATS; ++mtx) cur[mtx] = nxt[mtx];
+  }
+
+  // cross-warp (split-K) reduction
+  constexpr int NV = MATS * NB * 4;
+#pragma unroll
+  for (int mtx = 0; mtx < MATS; ++mtx)
+#pragma unroll
+    for (int j = 0; j < NB; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) red[((size_t)warp * NV + (mtx * NB + j) * 4 + c) * 32 + lane] = acc[mtx][j][c];
+  __syncthreads();
+
+  for (int j = warp; j < NB; j += W) {
+    float v[MATS][4];
+#pragma unroll
+    for (int mtx = 0; mtx < MATS; ++mtx)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float s = 0.0f;
+        for (int w = 0; w < W; ++w) s += red[((size_t)w * NV + (mtx * NB + j) * 4 + c) * 32 + lane];
+        v[mtx][c] = s;
+      }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int orow = r0 + g + ((c & 2) ? 8 : 0);  // output feature
+      const int col = 8 * j + 2 * t + (c & 1);      // token within the item
+      if (orow >= Oout || col >= nrows) continue;
+      float s0 = 1.0f, s1 = 1.0f;
+      if (FMT == COLI_FMT_NVFP4) {
+        s0 = w0.g * kFp4AccScale;
+        s1 = w1.g * kFp4AccScale;
+      } else if (FMT == COLI_FMT_E4M3_ROW) {
+        s0 = reinterpret_cast<const float *>(w0.s)[orow];
+        s1 = reinterpret_cast<const float *>(w1.s)[orow];
+      }
+      const size_t row = (size_t)(row0 + col);
+      if (GATED) {
+        const float gv = v[0][c] * s0, uv = v[MATS - 1][c] * s1;
+        const float hv = gv / (1.0f + __expf(-gv)) * uv;
+        p.h[row * p.I + orow] = __float2bfloat16_rn(hv);
+      } else {
+        if (p.y32)
+          p.y32[row * p.H + orow] = v[0][c] * s0;
+        else
+          p.y[row * p.H + orow] = __float2bfloat16_rn(v[0][c] * s0);
+      }
+    }
+  }
+}
+
+template <int FMT, int NB>
+static int launch_pair(const FfnParams &p, cudaStream_t st) {
+  auto pick_w = [](int KT) { return KT >= 8 ? 8 : KT >= 4 ? 4 : KT >= 2 ? 2 : 1; };
+  {
+    const int KT = (p.H + 127) / 128, W = pick_w(KT);
+    dim3 grid((p.I + 15) / 16, p.max_items);
+    const size_t sm = (size_t)W * 2 * NB * 4 * 32 * sizeof(float);
+    k_ffn_mm<FMT, NB, true><<<grid, W * 32, sm, st>>>(p);
+  }
+  {
+    const int KT = (p.I + 127) / 128, W = pick_w(KT);
+    dim3 grid((p.H + 15) / 16, p.max_items);
+    const size_t sm = (size_t)W * 1 * NB * 4 * 32 * sizeof(float);
+    k_ffn_mm<FMT, NB, false><<<grid, W * 32, sm, st>>>(p);
+  }
+  return coli_cuda_check(cudaGetLastError(), "expert ffn launch") ? 1 : 0;
+}
+
+// rows_per_item the caller cut the work list with selects NB (8 * NB >= rows per item).
+int launch_ffn_small(const FfnParams &p, cudaStream_t st) {
+  if (p.max_items <= 0) return 1;
+  if (p.H % 8 || p.I % 8) {
+    coli_set_error("expert ffn: H=%d and I=%d must be multiples of 8", p.H, p.I);
+    return 0;
+  }
+  const int nb = p.rows_per_item <= 8 ? 1 : p.rows_per_item <= 16 ? 2 : 4;
+  if (p.rows_per_item > 32) {
+    coli_set_error("expert ffn: rows_per_item=%d exceeds 32", p.rows_per_item);
+    return 0;
+  }
+#define COLI_DISPATCH(F)                                   \
+  (nb == 1 ? launch_pair<F, 1>(p, st) : nb == 2 ? launch_pair<F, 2>(p, st) : launch_pair<F, 4>(p, st))
+  switch (p.fmt) {
+    case COLI_FMT_NVFP4:
+      return COLI_DISPATCH(COLI_FMT_NVFP4);
+    case COLI_FMT_FP8_B128:
+      return COLI_DISPATCH(COLI_FMT_FP8_B128);
+    case COLI_FMT_E4M3_ROW:
+      return COLI_DISPATCH(COLI_FMT_E4M3_ROW);
+    default:
+      coli_set_error("expert ffn: unsupported weight format %d", p.fmt);
+      return 0;
+  }
+#undef COLI_DISPATCH
+}
+
+}  // namespace colib

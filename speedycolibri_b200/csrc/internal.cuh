@@ -1,0 +1,136 @@
+// Internal declarations shared by the translation units of libcoli_b200.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stddef.h>
+
+#include "../../include/coli_b200.h"
+#include "coli_math.h"
+
+// ---- resident weight handle -----------------------------------------------------------------
+// HBM layout ("k-tile major"): the K (input) axis is cut into tiles of 128; for each k-tile
+// all O rows are stored back to back, so the slab a CTA streams for (rows r0..r0+n, k-tile kt)
+// is one contiguous run of bytes.
+//   NVFP4     q: [KT][Op][64 B]   16 B chunk c of a row covers k = kt*128 + 32c .. +31; each
+//                                 32-bit word covers 8 consecutive k, even elements in nibble
+//                                 slots 0..3 and odd elements in slots 4..7 (so one shift+mask
+//                                 yields a (k, k+1) pair aligned to the halves of a bf16x2).
+//             s: [KT][Op][8 B]    the ue4m3 code of each 16-wide block, k ascending
+//   FP8_B128  q: [KT][Op][128 B]  e4m3 codes, k ascending
+//             s: f32 [ceil(O/128)][KT]   (the reference's own grid, convert.rs:731-741)
+//   E4M3_ROW  q as FP8_B128; s: f32 [O] row scales (linear.rs:93-109)
+// Op = O rounded up to 16, Kp = I rounded up to 128; padding bytes are zero (decode to 0.0).
+struct ColiCudaTensor {
+  int fmt, I, O, device;
+  int Kp, Op, KT;
+  uint8_t *q;
+  uint8_t *s;
+  float gscale;
+  size_t q_bytes, s_bytes;
+};
+
+// What a kernel needs to read one matrix.
+struct WeightRef {
+  const uint8_t *q;
+  const uint8_t *s;
+  float g;
+  int pad;
+};
+
+static inline int round_up(int a, int b) { return (a + b - 1) / b * b; }
+
+// ---- error reporting -------------------------------------------------------------------------
+void coli_set_error(const char *fmt, ...);
+bool coli_cuda_check(cudaError_t e, const char *what);
+#define CK(call, what)                          \
+  do {                                          \
+    if (!coli_cuda_check((call), (what))) return 0; \
+  } while (0)
+
+// ---- launchers (defined in the kernel translation units) ------------------------------------
+namespace colib {
+
+// layout.cu
+int pack_nvfp4(const uint8_t *d_nib, const uint8_t *d_bs, int O, int I, ColiCudaTensor *t, cudaStream_t st);
+int pack_fp8(const uint8_t *d_codes, int O, int I, ColiCudaTensor *t, cudaStream_t st);
+int unpack_nvfp4(const ColiCudaTensor *t, uint8_t *d_nib, uint8_t *d_bs, cudaStream_t st);
+int unpack_fp8(const ColiCudaTensor *t, uint8_t *d_codes, cudaStream_t st);
+int quantize_nvfp4(const float *d_w, int O, int I, uint8_t *d_nib, uint8_t *d_bs, float *d_amax_scratch,
+                   float *gscale_out, cudaStream_t st);
+int quantize_fp8_b128(const float *d_w, int O, int I, uint8_t *d_codes, float *d_scales, cudaStream_t st);
+
+// routing.cu
+struct RouteParams {
+  int T, H, E, k;
+  int score, norm_topk;
+  float routed_scale;
+  int n_group, topk_group;
+  const __nv_bfloat16 *x;         // [T,H]
+  const __nv_bfloat16 *router_w;  // [E,H]
+  const float *select_bias;       // [E] or null
+  const float *logit_bias;        // [E] or null
+  float *logits;                  // [T,E] scratch
+  int32_t *topk_idx;              // [T,k]
+  float *topk_w;                  // [T,k]
+};
+int launch_router(const RouteParams &p, cudaStream_t st);
+
+struct PermuteParams {
+  int T, H, E, k;
+  int has_shared;              // append T identity rows for the shared expert (segment index E)
+  int rows_per_item;           // token rows per work item
+  const int32_t *topk_idx;     // [T,k]
+  const int32_t *expert_slot;  // [E] segment position of each expert (null = identity)
+  int32_t *local_rank;         // [T*k] scratch
+  int32_t *chunk_cnt;          // [nchunk][E] scratch
+  int32_t *seg_count;          // [E] out: rows per segment (segment order)
+  int32_t *seg_off;            // [E+2] out: exclusive offsets (+shared)
+  int32_t *slot;               // [T*k] out: row position of (t,kk)
+  int32_t *row_token;          // [T*k (+T)] out: token of each row
+  int32_t *item_seg;           // work list out: segment (expert position) of each item
+  int32_t *item_row0;          //                first row
+  int32_t *item_nrows;         //                rows (<= rows_per_item)
+  int32_t *n_items;            // [1]
+  const __nv_bfloat16 *x;      // [T,H]  (null = do not materialise rows)
+  __nv_bfloat16 *xg;           // [T*k,H] gathered rows (null = skip)
+};
+int launch_permute(const PermuteParams &p, cudaStream_t st);
+// Work list for rows that are already expert-contiguous (counts on the device).
+int launch_items_from_counts(const int32_t *seg_count, int nseg, int rows_per_item, int32_t *seg_off,
+                             int32_t *item_seg, int32_t *item_row0, int32_t *item_nrows, int32_t *n_items,
+                             cudaStream_t st);
+
+// expert_small.cu
+struct FfnParams {
+  int fmt, H, I;
+  const WeightRef *gate, *up, *down;  // indexed by segment->expert table
+  const int32_t *seg_expert;          // [nseg] weight-table index of each segment (null = identity)
+  const int32_t *item_seg, *item_row0, *item_nrows, *n_items;
+  int max_items;
+  int rows_per_item;         // rows per work item the list was cut with (<= 32)
+  const __nv_bfloat16 *x;    // source rows
+  const int32_t *row_token;  // row -> source row index (null = identity)
+  __nv_bfloat16 *h;          // [rows, I] scratch
+  __nv_bfloat16 *y;          // [rows, H] out (bf16), or
+  float *y32;                // [rows, H] out (f32) when not null
+};
+int launch_ffn_small(const FfnParams &p, cudaStream_t st);
+
+// combine.cu
+struct CombineParams {
+  int T, H, k;
+  int has_shared;
+  const __nv_bfloat16 *y;         // routed rows [T*k, H]
+  const __nv_bfloat16 *shared_y;  // [T,H] shared-expert rows (used when has_shared)
+  const int32_t *slot;            // [T*k]
+  const float *topk_w;            // [T*k]
+  __nv_bfloat16 *out;             // [T,H]
+};
+int launch_combine(const CombineParams &p, cudaStream_t st);
+int launch_f32_to_bf16(const float *src, __nv_bfloat16 *dst, size_t n, cudaStream_t st);
+// y[S,O] = x[S,I] @ W[O,I]^T, all f32, one thread per output, multiply then add per k in order
+// (crates/colibri-engine/src/linear.rs:199-220).
+int launch_matmul_f32_seq(const float *x, const float *w, float *y, int S, int I, int O, cudaStream_t st);
+
+}  // namespace colib

@@ -1,0 +1,423 @@
+// Routing: router GEMM with a strictly k-ascending f32 sum per logit, score + top-k
+// (softmax / sigmoid+bias / group-limited), and the permutation of (token, kk) pairs into
+// expert-contiguous row segments.
+//
+// Bit-exactness contract.  The CPU restatement of crates/colibri-engine/src/moe.rs:1047-1132
+// sums each logit sequentially over k in f32 (linear.rs:199-220), scores with exp, sums the
+// softmax denominator sequentially over e, and picks k experts by a strict `>` scan from e = 0.
+// Every one of those steps is reproduced here operation for operation:
+//   * x and the router weights are bf16, so each product is exact in f32 and one fused
+//     multiply-add per k equals the reference's multiply-then-add; each logit is owned by ONE
+//     thread that walks k = 0..H-1 in order (no split-K, no tensor cores);
+//   * exp / sigmoid come from coli_math.h, compiled identically for host and device;
+//   * adds, subs, divides that the compiler could contract or reorder are spelled with the
+//     CF_* round-to-nearest intrinsics;
+//   * the arg-max of each round is the largest value with the lowest index, which is what the
+//     ascending strict-`>` scan returns; a round with no candidate above -inf returns 0.
+#include "internal.cuh"
+
+namespace colib {
+
+// ---------------------------------------------------------------------------------------------
+// Router GEMM, general shape.  Block = 16x16 threads, thread tile TM x TN, k-chunk 32 staged in
+// shared memory as f32 (transposed so the inner loop reads broadcast / consecutive words).
+// ---------------------------------------------------------------------------------------------
+template <int TM, int TN>
+__global__ void __launch_bounds__(256) k_router_gemm(RouteParams p) {
+  constexpr int BM = 16 * TM, BN = 16 * TN, BK = 32;
+  __shared__ float xs[BK][BM + 4];
+  __shared__ float ws[BK][BN + 4];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  float acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+
+  for (int k0 = 0; k0 < p.H; k0 += BK) {
+    // stage x[m0..m0+BM, k0..k0+32) and w[n0..n0+BN, k0..k0+32), zero beyond the edges
+    for (int idx = threadIdx.x; idx < BM * BK; idx += 256) {
+      const int r = idx / BK, c = idx % BK;
+      const int m = m0 + r, k = k0 + c;
+      float v = 0.0f;
+      if (m < p.T && k < p.H) v = __bfloat162float(p.x[(size_t)m * p.H + k]);
+      xs[c][r] = v;
+    }
+    for (int idx = threadIdx.x; idx < BN * BK; idx += 256) {
+      const int r = idx / BK, c = idx % BK;
+      const int n = n0 + r, k = k0 + c;
+      float v = 0.0f;
+      if (n < p.E && k < p.H) v = __bfloat162float(p.router_w[(size_t)n * p.H + k]);
+      ws[c][r] = v;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int kk = 0; kk < BK; ++kk) {
+      float a[TM], b[TN];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) a[i] = xs[kk][ty * TM + i];
+#pragma unroll
+      for (int j = 0; j < TN; ++j) b[j] = ws[kk][tx * TN + j];
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      const int m = m0 + ty * TM + i, n = n0 + tx * TN + j;
+      if (m < p.T && n < p.E) {
+        float v = acc[i][j];
+        if (p.logit_bias) v = __fadd_rn(v, p.logit_bias[n]);
+        p.logits[(size_t)m * p.E + n] = v;
+      }
+    }
+}
+
+// Decode shape (T <= 8): one thread per (token, expert) walking its own k chain; the block's 8
+// expert rows and all token rows are staged in shared memory as bf16 with coalesced 16-byte
+// loads first.  The chain of H dependent FMAs is the latency floor of bit-exact routing.
+__global__ void __launch_bounds__(256) k_router_decode(RouteParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16 *xs = reinterpret_cast<__nv_bfloat16 *>(smem_raw);  // [T][H]
+  __nv_bfloat16 *ws = xs + (size_t)p.T * p.H;                       // [8][H]
+  const int e0 = blockIdx.x * 8;
+  const int H = p.H;
+  const int vec = H / 8;  // H % 8 == 0 checked by the launcher
+  for (int idx = threadIdx.x; idx < p.T * vec; idx += blockDim.x)
+    reinterpret_cast<uint4 *>(xs)[idx] = reinterpret_cast<const uint4 *>(p.x)[idx];
+  for (int idx = threadIdx.x; idx < 8 * vec; idx += blockDim.x) {
+    const int r = idx / vec, c = idx % vec;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (e0 + r < p.E) v = reinterpret_cast<const uint4 *>(p.router_w + (size_t)(e0 + r) * H)[c];
+    reinterpret_cast<uint4 *>(ws)[idx] = v;
+  }
+  __syncthreads();
+  const int t = threadIdx.x >> 3, el = threadIdx.x & 7;
+  if (t >= p.T || e0 + el >= p.E) return;
+  const uint4 *xr = reinterpret_cast<const uint4 *>(xs + (size_t)t * H);
+  const uint4 *wr = reinterpret_cast<const uint4 *>(ws + (size_t)el * H);
+  float acc = 0.0f;
+#pragma unroll 4
+  for (int c = 0; c < vec; ++c) {
+    const uint4 xv = xr[c], wv = wr[c];
+    const uint32_t xa[4] = {xv.x, xv.y, xv.z, xv.w}, wa[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      acc = __fmaf_rn(__uint_as_float(xa[j] << 16), __uint_as_float(wa[j] << 16), acc);
+      acc = __fmaf_rn(__uint_as_float(xa[j] & 0xffff0000u), __uint_as_float(wa[j] & 0xffff0000u), acc);
+    }
+  }
+  if (p.logit_bias) acc = __fadd_rn(acc, p.logit_bias[e0 + el]);
+  p.logits[(size_t)t * p.E + e0 + el] = acc;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Score + top-k: one warp per token.  Expert e lives in lane e % 32, slot e / 32 (<= 16 slots).
+// ---------------------------------------------------------------------------------------------
+constexpr int kMaxSlots = 16;  // E <= 512
+
+// Warp arg-max with the reference's tie rule: larger value wins, equal values -> lower index.
+// `has` marks lanes that hold a candidate (value strictly above -inf).
+__device__ __forceinline__ void warp_argmax(float &v, int &i, bool &has) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, off);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, off);
+    const bool oh = __shfl_xor_sync(0xffffffffu, (int)has, off) != 0;
+    if (oh && (!has || ov > v || (ov == v && oi < i))) {
+      v = ov;
+      i = oi;
+      has = true;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(128) k_route_topk(RouteParams p) {
+  extern __shared__ float sm[];  // per warp: score[E] then choice[E]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= p.T) return;
+  const int E = p.E, k = min(p.k, p.E);
+  float *score = sm + (size_t)warp * 2 * E;
+  float *choice = score + E;
+  const float *z = p.logits + (size_t)t * E;
+  const float NEG_INF = __uint_as_float(0xff800000u);
+
+  if (p.score == COLI_SCORE_SOFTMAX) {
+    float mx = NEG_INF;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);  // max is order-independent
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    for (int e = lane; e < E; e += 32) score[e] = coli_expf(__fsub_rn(z[e], mx));
+    __syncwarp();
+    float tot = 0.0f;  // sequential over e, every lane redundantly (moe.rs:1068)
+    for (int e = 0; e < E; ++e) tot = __fadd_rn(tot, score[e]);
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) {
+      float s = score[e];
+      if (tot > 0.0f) s = __fdiv_rn(s, tot);
+      score[e] = s;
+      choice[e] = s;
+    }
+  } else {
+    for (int e = lane; e < E; e += 32) {
+      const float s = coli_sigmoidf(z[e]);
+      score[e] = s;
+      choice[e] = __fadd_rn(s, p.select_bias ? p.select_bias[e] : 0.0f);
+    }
+  }
+  __syncwarp();
+
+  // group-limited selection: allowed-group bit mask (n_group <= 32)
+  uint32_t gmask = 0xffffffffu;
+  int gs = E;
+  if (p.n_group > 1) {
+    const int G = p.n_group;
+    gs = E / G;
+    const int kg = min(p.topk_group, G);
+    float gscore = NEG_INF;
+    if (lane < G) {
+      float m1 = NEG_INF, m2 = NEG_INF;
+      for (int e = lane * gs; e < (lane + 1) * gs; ++e) {
+        const float c = choice[e];
+        if (c > m1) {
+          m2 = m1;
+          m1 = c;
+        } else if (c > m2) {
+          m2 = c;
+        }
+      }
+      gscore = __fadd_rn(m1, m2);
+    }
+    gmask = 0;
+    bool taken = false;
+    for (int j = 0; j < kg; ++j) {
+      float v = gscore;
+      int i = lane;
+      bool has = (lane < G) && !taken && (gscore > NEG_INF);
+      warp_argmax(v, i, has);
+      const int best = has ? i : 0;
+      if (lane == best) taken = true;
+      gmask |= 1u << best;
+    }
+  }
+
+  // k rounds of arg-max over the allowed, not yet chosen experts
+  uint32_t chosen = 0;  // bit s = slot s of this lane already chosen
+  int my_idx = 0;       // lane kk keeps idx[kk]
+  float my_w = 0.0f;
+  for (int kk = 0; kk < k; ++kk) {
+    float bv = NEG_INF;
+    int bi = 0;
+    bool has = false;
+#pragma unroll 4
+    for (int s = 0; s < kMaxSlots; ++s) {
+      const int e = lane + 32 * s;
+      if (e >= E) break;
+      if ((chosen >> s) & 1u) continue;
+      if (!((gmask >> (e / gs)) & 1u)) continue;
+      const float c = choice[e];
+      if (c > bv) {  // ascending e within the lane: strict > keeps the lowest index
+        bv = c;
+        bi = e;
+        has = true;
+      }
+    }
+    warp_argmax(bv, bi, has);
+    const int best = has ? bi : 0;
+    if ((best & 31) == lane) chosen |= 1u << (best >> 5);
+    if (lane == kk) {
+      my_idx = best;
+      my_w = score[best];
+    }
+  }
+  if (p.norm_topk) {
+    float smv = 0.0f;
+    for (int kk = 0; kk < k; ++kk) smv = __fadd_rn(smv, __shfl_sync(0xffffffffu, my_w, kk));
+    smv = __fadd_rn(smv, 1e-20f);
+    my_w = __fdiv_rn(my_w, smv);
+  }
+  my_w = __fmul_rn(my_w, p.routed_scale);
+  if (lane < k) {
+    p.topk_idx[(size_t)t * k + lane] = my_idx;
+    p.topk_w[(size_t)t * k + lane] = my_w;
+  }
+}
+
+int launch_router(const RouteParams &p, cudaStream_t st) {
+  if (p.T <= 0) return 1;
+  if (p.E > 32 * kMaxSlots) {
+    coli_set_error("router: E=%d exceeds the supported maximum of %d", p.E, 32 * kMaxSlots);
+    return 0;
+  }
+  if (p.k > 32 || p.n_group > 32 || (p.n_group > 1 && p.E % p.n_group != 0)) {
+    coli_set_error("router: unsupported k=%d / n_group=%d for E=%d", p.k, p.n_group, p.E);
+    return 0;
+  }
+  const size_t dec_smem = (size_t)(p.T + 8) * p.H * sizeof(__nv_bfloat16);
+  if (p.T <= 8 && p.H % 8 == 0 && dec_smem <= 200 * 1024) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaFuncSetAttribute(k_router_decode, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      attr_set = true;
+    }
+    k_router_decode<<<(p.E + 7) / 8, 64 * ((p.T * 8 + 63) / 64), dec_smem, st>>>(p);
+  } else if ((size_t)p.T * p.E >= 64 * 64 * 64) {
+    dim3 grid((p.E + 63) / 64, (p.T + 63) / 64);
+    k_router_gemm<4, 4><<<grid, 256, 0, st>>>(p);
+  } else {
+    dim3 grid((p.E + 15) / 16, (p.T + 15) / 16);
+    k_router_gemm<1, 1><<<grid, 256, 0, st>>>(p);
+  }
+  const size_t sm = (size_t)4 * 2 * p.E * sizeof(float);
+  k_route_topk<<<(p.T + 3) / 4, 128, sm, st>>>(p);
+  return coli_cuda_check(cudaGetLastError(), "router launch") ? 1 : 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Permutation into expert-contiguous segments.  Stable: rows of one expert keep ascending
+// token order (moe.rs:1373-1387), positions are a pure function of the routing.
+//   1. k_seg_count : one warp per chunk of 32 tokens walks its tokens in order; lane kk bumps
+//                    a shared-memory counter of expert idx[t][kk] (a token's experts are
+//                    distinct, so no two lanes touch one counter) and records the rank.
+//   2. k_seg_scan  : per expert an exclusive running sum over chunks; exclusive scan over the
+//                    segment order; builds the work list (segments cut into row_per_item runs).
+//   3. k_permute   : row position = segment offset + chunk prefix + rank; copies the token row.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) k_seg_count(PermuteParams p, int nchunk) {
+  extern __shared__ int cnt_sm[];  // [4][E]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chunk = blockIdx.x * 4 + warp;
+  int *cnt = cnt_sm + (size_t)warp * p.E;
+  for (int e = lane; e < p.E; e += 32) cnt[e] = 0;
+  __syncwarp();
+  if (chunk >= nchunk) return;
+  const int t0 = chunk * 32, t1 = min(p.T, t0 + 32);
+  for (int t = t0; t < t1; ++t) {
+    if (lane < p.k) {
+      const int e = p.topk_idx[(size_t)t * p.k + lane];
+      p.local_rank[(size_t)t * p.k + lane] = cnt[e];
+      cnt[e] += 1;
+    }
+    __syncwarp();
+  }
+  for (int e = lane; e < p.E; e += 32) p.chunk_cnt[(size_t)chunk * p.E + e] = cnt[e];
+}
+
+__global__ void __launch_bounds__(1024) k_seg_scan(PermuteParams p, int nchunk, int max_items) {
+  __shared__ int seg_cnt[1024 + 1];
+  __shared__ int seg_off[1024 + 2];
+  const int E = p.E;
+  const int nseg = E + (p.has_shared ? 1 : 0);
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int c = 0; c < nchunk; ++c) {
+      const int v = p.chunk_cnt[(size_t)c * E + e];
+      p.chunk_cnt[(size_t)c * E + e] = run;
+      run += v;
+    }
+    const int pos = p.expert_slot ? p.expert_slot[e] : e;
+    seg_cnt[pos] = run;
+  }
+  if (threadIdx.x == 0 && p.has_shared) seg_cnt[E] = p.T;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0, items = 0;
+    for (int s = 0; s < nseg; ++s) {
+      seg_off[s] = run;
+      const int n = seg_cnt[s];
+      for (int r = 0; r < n; r += p.rows_per_item) {
+        if (items < max_items) {
+          p.item_seg[items] = s;
+          p.item_row0[items] = run + r;
+          p.item_nrows[items] = min(p.rows_per_item, n - r);
+        }
+        ++items;
+      }
+      run += n;
+    }
+    seg_off[nseg] = run;
+    *p.n_items = min(items, max_items);
+  }
+  __syncthreads();
+  for (int s = threadIdx.x; s <= nseg; s += blockDim.x) p.seg_off[s] = seg_off[s];
+  for (int s = threadIdx.x; s < E; s += blockDim.x) p.seg_count[s] = seg_cnt[s];
+}
+
+__global__ void __launch_bounds__(256) k_permute(PermuteParams p) {
+  // one warp per (t, kk) row; rows T*k .. T*k+T-1 are the shared expert's identity rows
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int nrouted = p.T * p.k;
+  const int total = nrouted + (p.has_shared ? p.T : 0);
+  if (warp >= total) return;
+  int t, pos;
+  if (warp < nrouted) {
+    t = warp / p.k;
+    const int e = p.topk_idx[warp];
+    const int s = p.expert_slot ? p.expert_slot[e] : e;
+    pos = p.seg_off[s] + p.chunk_cnt[(size_t)(t >> 5) * p.E + e] + p.local_rank[warp];
+    if (lane == 0) p.slot[warp] = pos;
+  } else {
+    t = warp - nrouted;
+    pos = p.seg_off[p.E] + t;
+  }
+  if (lane == 0) p.row_token[pos] = t;
+  if (p.xg && warp < nrouted) {
+    const int vec = p.H / 8;
+    const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (size_t)t * p.H);
+    uint4 *dst = reinterpret_cast<uint4 *>(p.xg + (size_t)pos * p.H);
+    for (int c = lane; c < vec; c += 32) dst[c] = src[c];
+  }
+}
+
+int launch_permute(const PermuteParams &p, cudaStream_t st) {
+  if (p.T <= 0) return 1;
+  if (p.E > 1024) {
+    coli_set_error("permute: E=%d exceeds 1024", p.E);
+    return 0;
+  }
+  const int nchunk = (p.T + 31) / 32;
+  const int nseg = p.E + (p.has_shared ? 1 : 0);
+  const int max_items = (p.T * p.k + (p.has_shared ? p.T : 0)) / p.rows_per_item + nseg;
+  k_seg_count<<<(nchunk + 3) / 4, 128, (size_t)4 * p.E * sizeof(int), st>>>(p, nchunk);
+  k_seg_scan<<<1, 1024, 0, st>>>(p, nchunk, max_items);
+  const int total = p.T * p.k + (p.has_shared ? p.T : 0);
+  k_permute<<<(total + 7) / 8, 256, 0, st>>>(p);
+  return coli_cuda_check(cudaGetLastError(), "permute launch") ? 1 : 0;
+}
+
+__global__ void k_items_from_counts(const int32_t *seg_count, int nseg, int rows_per_item, int32_t *seg_off,
+                                    int32_t *item_seg, int32_t *item_row0, int32_t *item_nrows,
+                                    int32_t *n_items) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int run = 0, items = 0;
+  for (int s = 0; s < nseg; ++s) {
+    seg_off[s] = run;
+    const int n = seg_count[s];
+    for (int r = 0; r < n; r += rows_per_item) {
+      item_seg[items] = s;
+      item_row0[items] = run + r;
+      item_nrows[items] = min(rows_per_item, n - r);
+      ++items;
+    }
+    run += n;
+  }
+  seg_off[nseg] = run;
+  *n_items = items;
+}
+
+int launch_items_from_counts(const int32_t *seg_count, int nseg, int rows_per_item, int32_t *seg_off,
+                             int32_t *item_seg, int32_t *item_row0, int32_t *item_nrows, int32_t *n_items,
+                             cudaStream_t st) {
+  k_items_from_counts<<<1, 32, 0, st>>>(seg_count, nseg, rows_per_item, seg_off, item_seg, item_row0,
+                                        item_nrows, n_items);
+  return coli_cuda_check(cudaGetLastError(), "work list launch") ? 1 : 0;
+}
+
+}  // namespace colib
