@@ -152,7 +152,9 @@ size_t coli_b200_moe_workspace_bytes(const ColiMoe *moe);
  * inside).  topk_idx [T,k] int32 and topk_w [T,k] f32 are optional HOST outputs.  All experts
  * must be resident (single GPU). */
 int coli_b200_moe_block(ColiMoe *moe, const void *x, void *out, int T, int32_t *topk_idx, float *topk_w);
-/* Same with DEVICE pointers, asynchronous on `stream` (a cudaStream_t, NULL = the handle's). */
+/* Same with DEVICE pointers, asynchronous on `stream` (a cudaStream_t; NULL is CUDA's default
+ * stream, coli_b200_moe_stream() gives the handle's own).  One handle's workspace serves one
+ * call at a time: calls on different streams must not overlap. */
 int coli_b200_moe_block_dev(ColiMoe *moe, const void *x_dev, void *out_dev, int T, void *stream);
 /* Copy the last call's routing to HOST (after synchronising the stream). */
 int coli_b200_moe_last_routing(ColiMoe *moe, int T, int32_t *topk_idx, float *topk_w);
@@ -175,6 +177,25 @@ int coli_b200_moe_shared_dev(ColiMoe *moe, const void *x_dev, int T, void *y_dev
  * rounded once to bf16 (moe.rs:1549-1553,1875-1885). */
 int coli_b200_moe_combine_dev(ColiMoe *moe, const void *y_rows_dev, const int32_t *slot_dev,
                               const void *shared_y_dev, void *out_dev, int T, void *stream);
+
+/* ---- tracing (the role of the reference's COLI_PROFILE phase counters ROUTER_US, MOE_PREP_US,
+ * GPUFFN_US, SCATTER_US, crates/colibri-engine/src/forward.rs:86-160) ------------------------ */
+#define COLI_PHASE_ROUTER 0  /* router GEMM + score + top-k */
+#define COLI_PHASE_PERMUTE 1 /* segment counts, offsets, row permutation, work list */
+#define COLI_PHASE_GATE_UP 2 /* grouped gate/up GEMM with SiLU*mul */
+#define COLI_PHASE_DOWN 3    /* grouped down GEMM */
+#define COLI_PHASE_COMBINE 4 /* weighted combine + shared add */
+#define COLI_PHASES 5
+/* With profiling on, coli_b200_moe_block_dev brackets each phase with CUDA events on the
+ * launching stream and synchronises at the end of the call to accumulate them (so it is a
+ * measurement mode, not a fast path).  Turning it on clears the accumulators. */
+int coli_b200_moe_profile(ColiMoe *moe, int enable);
+/* Accumulated milliseconds per phase and the number of block calls they cover. */
+int coli_b200_moe_phase_ms(ColiMoe *moe, float *ms /* [COLI_PHASES] */, int *calls);
+/* The handle's own stream (a cudaStream_t), on which the host-pointer block call runs. */
+void *coli_b200_moe_stream(ColiMoe *moe);
+/* Kernels this library has launched in the calling process since it was loaded. */
+uint64_t coli_b200_launch_count(void);
 
 /* FNV-1a fingerprint of an expert->rank map (crates/colibri-cluster/src/sharding.rs:251-265);
  * `owner` NULL = contiguous.  Ranks compare it before the first exchange. */

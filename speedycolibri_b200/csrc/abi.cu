@@ -26,6 +26,11 @@ bool coli_cuda_check(cudaError_t e, const char *what) {
 }
 extern "C" const char *coli_cuda_last_error(void) { return g_err; }
 
+#include <atomic>
+static std::atomic<uint64_t> g_launches{0};
+void coli_count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+extern "C" uint64_t coli_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
 // ---- device contexts (backend_cuda.cu:87-129, 2594-2655) --------------------------------------
 namespace {
 struct DeviceContext {
@@ -349,6 +354,11 @@ struct ColiMoe {
   size_t h_rows_cap;  // rows the h scratch holds
   size_t ws_bytes;
   std::vector<void *> allocs;
+  // tracing
+  bool profiling;
+  cudaEvent_t ev[COLI_PHASES + 1];
+  float phase_ms[COLI_PHASES];
+  int phase_calls;
 };
 
 template <class T>
@@ -367,8 +377,29 @@ extern "C" void coli_b200_moe_destroy(ColiMoe *m) {
     cudaStreamSynchronize(m->ctx->stream);
   }
   for (void *p : m->allocs) cudaFree(p);
+  for (int i = 0; i <= COLI_PHASES; ++i)
+    if (m->ev[i]) cudaEventDestroy(m->ev[i]);
   delete m;
 }
+
+extern "C" int coli_b200_moe_profile(ColiMoe *m, int enable) {
+  if (!m || !select_ctx(m->ctx)) return 0;
+  if (enable) {
+    for (int i = 0; i <= COLI_PHASES; ++i)
+      if (!m->ev[i]) CK(cudaEventCreate(&m->ev[i]), "event creation");
+    for (int i = 0; i < COLI_PHASES; ++i) m->phase_ms[i] = 0.0f;
+    m->phase_calls = 0;
+  }
+  m->profiling = enable != 0;
+  return 1;
+}
+extern "C" int coli_b200_moe_phase_ms(ColiMoe *m, float *ms, int *calls) {
+  if (!m || !ms) return 0;
+  for (int i = 0; i < COLI_PHASES; ++i) ms[i] = m->phase_ms[i];
+  if (calls) *calls = m->phase_calls;
+  return 1;
+}
+extern "C" void *coli_b200_moe_stream(ColiMoe *m) { return m ? (void *)m->ctx->stream : nullptr; }
 
 static int rows_per_item_for(const ColiMoeLayer &L, int rows, int nseg) {
   const int avg = (rows + nseg - 1) / (nseg > 0 ? nseg : 1);
@@ -401,6 +432,10 @@ extern "C" int coli_b200_moe_create(ColiMoe **out, const ColiMoeLayer *L, int ma
   m->ctx = ctx;
   m->max_tokens = max_tokens;
   m->ws_bytes = 0;
+  m->profiling = false;
+  m->phase_calls = 0;
+  for (int i = 0; i <= COLI_PHASES; ++i) m->ev[i] = nullptr;
+  for (int i = 0; i < COLI_PHASES; ++i) m->phase_ms[i] = 0.0f;
   m->has_shared = L->sh_gate && L->sh_up && L->sh_down;
   m->nseg = L->E + (m->has_shared ? 1 : 0);
   const int E = L->E, H = L->H, I = L->I, k = L->k;
@@ -515,7 +550,11 @@ extern "C" int coli_b200_moe_create(ColiMoe **out, const ColiMoeLayer *L, int ma
 
 extern "C" size_t coli_b200_moe_workspace_bytes(const ColiMoe *m) { return m ? m->ws_bytes : 0; }
 
-static cudaStream_t pick_stream(ColiMoe *m, void *stream) { return stream ? (cudaStream_t)stream : m->ctx->stream; }
+// A null stream is CUDA's default stream, as everywhere else in the runtime.
+static cudaStream_t pick_stream(ColiMoe *m, void *stream) {
+  (void)m;
+  return (cudaStream_t)stream;
+}
 
 static bool check_T(ColiMoe *m, int T, const char *who) {
   if (!m) {
@@ -591,8 +630,16 @@ extern "C" int coli_b200_moe_block_dev(ColiMoe *m, const void *x_dev, void *out_
   const int k = m->L.k;
   const int rows = T * k + (m->has_shared ? T : 0);
   const int rpi = rows_per_item_for(m->L, rows, m->nseg);
+  const bool prof = m->profiling;
+#define COLI_MARK(i)                                                         \
+  do {                                                                       \
+    if (prof) CK(cudaEventRecord(m->ev[i], st), "phase event");              \
+  } while (0)
+  COLI_MARK(0);
   if (!colib::launch_router(route_params(m, x_dev, T), st)) return 0;
+  COLI_MARK(1);
   if (!colib::launch_permute(permute_params(m, x_dev, T, m->has_shared, rpi, nullptr, m->seg_count, m->slot), st)) return 0;
+  COLI_MARK(2);
   colib::FfnParams fp;
   fp.fmt = m->L.fmt;
   fp.H = m->L.H;
@@ -612,7 +659,10 @@ extern "C" int coli_b200_moe_block_dev(ColiMoe *m, const void *x_dev, void *out_
   fp.h = m->h;
   fp.y = m->y;
   fp.y32 = nullptr;
-  if (!colib::launch_ffn_small(fp, st)) return 0;
+  if (!colib::launch_gate_up_small(fp, st)) return 0;
+  COLI_MARK(3);
+  if (!colib::launch_down_small(fp, st)) return 0;
+  COLI_MARK(4);
   colib::CombineParams cp;
   cp.T = T;
   cp.H = m->L.H;
@@ -623,7 +673,19 @@ extern "C" int coli_b200_moe_block_dev(ColiMoe *m, const void *x_dev, void *out_
   cp.slot = m->slot;
   cp.topk_w = m->topk_w;
   cp.out = (__nv_bfloat16 *)out_dev;
-  return colib::launch_combine(cp, st);
+  if (!colib::launch_combine(cp, st)) return 0;
+  COLI_MARK(5);
+#undef COLI_MARK
+  if (prof) {
+    CK(cudaEventSynchronize(m->ev[COLI_PHASES]), "phase event sync");
+    for (int i = 0; i < COLI_PHASES; ++i) {
+      float ms = 0.0f;
+      CK(cudaEventElapsedTime(&ms, m->ev[i], m->ev[i + 1]), "phase event read");
+      m->phase_ms[i] += ms;
+    }
+    m->phase_calls++;
+  }
+  return 1;
 }
 
 extern "C" int coli_b200_moe_last_routing(ColiMoe *m, int T, int32_t *topk_idx, float *topk_w) {

@@ -52,6 +52,7 @@ int launch_combine(const CombineParams &p, cudaStream_t st) {
   const __nv_bfloat16 *shared_y = p.has_shared ? p.shared_y : nullptr;
   dim3 grid((p.H / 8 + 255) / 256, p.T);
   k_combine<<<grid, 256, 0, st>>>(p, shared_y);
+  coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "combine launch") ? 1 : 0;
 }
 
@@ -63,6 +64,7 @@ int launch_f32_to_bf16(const float *src, __nv_bfloat16 *dst, size_t n, cudaStrea
   if (n == 0) return 1;
   const size_t blocks = (n + 255) / 256;
   k_f32_to_bf16<<<(unsigned)(blocks > 4736 ? 4736 : blocks), 256, 0, st>>>(src, dst, n);
+  coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "f32->bf16 launch") ? 1 : 0;
 }
 
@@ -79,6 +81,7 @@ int launch_matmul_f32_seq(const float *x, const float *w, float *y, int S, int I
   const size_t n = (size_t)S * O;
   if (n == 0) return 1;
   k_matmul_f32_seq<<<(unsigned)((n + 127) / 128), 128, 0, st>>>(x, w, y, S, I, O);
+  coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "f32 matmul launch") ? 1 : 0;
 }
 

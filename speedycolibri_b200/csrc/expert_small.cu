@@ -302,38 +302,39 @@ __global__ void __launch_bounds__(256) k_ffn_mm(FfnParams p) {
   }
 }
 
+static int pick_w(int KT) { return KT >= 8 ? 8 : KT >= 4 ? 4 : KT >= 2 ? 2 : 1; }
+
 template <int FMT, int NB>
-static int launch_pair(const FfnParams &p, cudaStream_t st) {
-  auto pick_w = [](int KT) { return KT >= 8 ? 8 : KT >= 4 ? 4 : KT >= 2 ? 2 : 1; };
-  {
+static int launch_one(const FfnParams &p, bool gated, cudaStream_t st) {
+  if (gated) {
     const int KT = (p.H + 127) / 128, W = pick_w(KT);
     dim3 grid((p.I + 15) / 16, p.max_items);
     const size_t sm = (size_t)W * 2 * NB * 4 * 32 * sizeof(float);
     k_ffn_mm<FMT, NB, true><<<grid, W * 32, sm, st>>>(p);
-  }
-  {
+  } else {
     const int KT = (p.I + 127) / 128, W = pick_w(KT);
     dim3 grid((p.H + 15) / 16, p.max_items);
     const size_t sm = (size_t)W * 1 * NB * 4 * 32 * sizeof(float);
     k_ffn_mm<FMT, NB, false><<<grid, W * 32, sm, st>>>(p);
   }
+  coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "expert ffn launch") ? 1 : 0;
 }
 
 // rows_per_item the caller cut the work list with selects NB (8 * NB >= rows per item).
-int launch_ffn_small(const FfnParams &p, cudaStream_t st) {
+static int launch_ffn_stage(const FfnParams &p, bool gated, cudaStream_t st) {
   if (p.max_items <= 0) return 1;
   if (p.H % 8 || p.I % 8) {
     coli_set_error("expert ffn: H=%d and I=%d must be multiples of 8", p.H, p.I);
     return 0;
   }
-  const int nb = p.rows_per_item <= 8 ? 1 : p.rows_per_item <= 16 ? 2 : 4;
   if (p.rows_per_item > 32) {
     coli_set_error("expert ffn: rows_per_item=%d exceeds 32", p.rows_per_item);
     return 0;
   }
-#define COLI_DISPATCH(F)                                   \
-  (nb == 1 ? launch_pair<F, 1>(p, st) : nb == 2 ? launch_pair<F, 2>(p, st) : launch_pair<F, 4>(p, st))
+  const int nb = p.rows_per_item <= 8 ? 1 : p.rows_per_item <= 16 ? 2 : 4;
+#define COLI_DISPATCH(F) \
+  (nb == 1 ? launch_one<F, 1>(p, gated, st) : nb == 2 ? launch_one<F, 2>(p, gated, st) : launch_one<F, 4>(p, gated, st))
   switch (p.fmt) {
     case COLI_FMT_NVFP4:
       return COLI_DISPATCH(COLI_FMT_NVFP4);
@@ -346,6 +347,12 @@ int launch_ffn_small(const FfnParams &p, cudaStream_t st) {
       return 0;
   }
 #undef COLI_DISPATCH
+}
+
+int launch_gate_up_small(const FfnParams &p, cudaStream_t st) { return launch_ffn_stage(p, true, st); }
+int launch_down_small(const FfnParams &p, cudaStream_t st) { return launch_ffn_stage(p, false, st); }
+int launch_ffn_small(const FfnParams &p, cudaStream_t st) {
+  return launch_gate_up_small(p, st) && launch_down_small(p, st);
 }
 
 }  // namespace colib

@@ -48,6 +48,9 @@ bool coli_cuda_check(cudaError_t e, const char *what);
     if (!coli_cuda_check((call), (what))) return 0; \
   } while (0)
 
+// every kernel launch of the library bumps this (read through coli_b200_launch_count)
+void coli_count_launch(int n);
+
 // ---- launchers (defined in the kernel translation units) ------------------------------------
 namespace colib {
 
@@ -115,7 +118,9 @@ struct FfnParams {
   __nv_bfloat16 *y;          // [rows, H] out (bf16), or
   float *y32;                // [rows, H] out (f32) when not null
 };
-int launch_ffn_small(const FfnParams &p, cudaStream_t st);
+int launch_gate_up_small(const FfnParams &p, cudaStream_t st);  // h = silu(gate x) * (up x)
+int launch_down_small(const FfnParams &p, cudaStream_t st);     // y = down h
+int launch_ffn_small(const FfnParams &p, cudaStream_t st);      // both
 
 // combine.cu
 struct CombineParams {

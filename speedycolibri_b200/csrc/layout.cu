@@ -96,21 +96,27 @@ static inline unsigned nblk(size_t n, int b) { return (unsigned)((n + b - 1) / b
 
 int pack_nvfp4(const uint8_t *d_nib, const uint8_t *d_bs, int O, int I, ColiCudaTensor *t, cudaStream_t st) {
   k_pack_nvfp4_q<<<nblk((size_t)t->KT * t->Op * 16, 256), 256, 0, st>>>(d_nib, (uint32_t *)t->q, O, I, t->Op, t->KT);
+  coli_count_launch(1);
   k_pack_nvfp4_s<<<nblk((size_t)t->KT * t->Op * 8, 256), 256, 0, st>>>(d_bs, t->s, O, I, t->Op, t->KT);
+  coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "nvfp4 repack") ? 1 : 0;
 }
 int pack_fp8(const uint8_t *d_codes, int O, int I, ColiCudaTensor *t, cudaStream_t st) {
   k_pack_fp8<<<nblk((size_t)t->KT * t->Op * 128, 256), 256, 0, st>>>(d_codes, t->q, O, I, t->Op, t->KT);
+  coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "fp8 repack") ? 1 : 0;
 }
 int unpack_nvfp4(const ColiCudaTensor *t, uint8_t *d_nib, uint8_t *d_bs, cudaStream_t st) {
   const int rb = (t->I + 1) / 2, nb = (t->I + 15) / 16;
   k_unpack_nvfp4_q<<<nblk((size_t)t->O * rb, 256), 256, 0, st>>>((const uint32_t *)t->q, d_nib, t->O, t->I, t->Op);
+  coli_count_launch(1);
   k_unpack_nvfp4_s<<<nblk((size_t)t->O * nb, 256), 256, 0, st>>>(t->s, d_bs, t->O, t->I, t->Op);
+  coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "nvfp4 export") ? 1 : 0;
 }
 int unpack_fp8(const ColiCudaTensor *t, uint8_t *d_codes, cudaStream_t st) {
   k_unpack_fp8<<<nblk((size_t)t->O * t->I, 256), 256, 0, st>>>(t->q, d_codes, t->O, t->I, t->Op);
+  coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "fp8 export") ? 1 : 0;
 }
 
@@ -149,8 +155,10 @@ int quantize_nvfp4(const float *d_w, int O, int I, uint8_t *d_nib, uint8_t *d_bs
   const size_t n = (size_t)O * I;
   k_amax<<<(unsigned)((n + 256 * 8 - 1) / (256 * 8) > 1184 ? 1184 : (n + 256 * 8 - 1) / (256 * 8)), 256, 0, st>>>(
       d_w, n, (unsigned int *)d_amax_scratch);
+  coli_count_launch(1);
   const size_t blocks = (size_t)O * ((I + 15) / 16);
   k_quant_nvfp4<<<nblk(blocks, 128), 128, 0, st>>>(d_w, O, I, d_nib, d_bs, d_amax_scratch);
+  coli_count_launch(1);
   if (!coli_cuda_check(cudaGetLastError(), "nvfp4 quantise")) return 0;
   float amax = 0.0f;
   if (!coli_cuda_check(cudaMemcpyAsync(&amax, d_amax_scratch, sizeof(float), cudaMemcpyDeviceToHost, st), "amax read"))
@@ -189,6 +197,7 @@ __global__ void __launch_bounds__(256) k_quant_fp8_b128(const float *w, int O, i
 int quantize_fp8_b128(const float *d_w, int O, int I, uint8_t *d_codes, float *d_scales, cudaStream_t st) {
   const int nbo = (O + 127) / 128, nbi = (I + 127) / 128;
   k_quant_fp8_b128<<<nbo * nbi, 256, 0, st>>>(d_w, O, I, d_codes, d_scales);
+  coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "fp8 quantise") ? 1 : 0;
 }
 

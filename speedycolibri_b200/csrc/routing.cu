@@ -268,15 +268,19 @@ int launch_router(const RouteParams &p, cudaStream_t st) {
       attr_set = true;
     }
     k_router_decode<<<(p.E + 7) / 8, 64 * ((p.T * 8 + 63) / 64), dec_smem, st>>>(p);
+    coli_count_launch(1);
   } else if ((size_t)p.T * p.E >= 64 * 64 * 64) {
     dim3 grid((p.E + 63) / 64, (p.T + 63) / 64);
     k_router_gemm<4, 4><<<grid, 256, 0, st>>>(p);
+    coli_count_launch(1);
   } else {
     dim3 grid((p.E + 15) / 16, (p.T + 15) / 16);
     k_router_gemm<1, 1><<<grid, 256, 0, st>>>(p);
+    coli_count_launch(1);
   }
   const size_t sm = (size_t)4 * 2 * p.E * sizeof(float);
   k_route_topk<<<(p.T + 3) / 4, 128, sm, st>>>(p);
+  coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "router launch") ? 1 : 0;
 }
 
@@ -386,9 +390,12 @@ int launch_permute(const PermuteParams &p, cudaStream_t st) {
   const int nseg = p.E + (p.has_shared ? 1 : 0);
   const int max_items = (p.T * p.k + (p.has_shared ? p.T : 0)) / p.rows_per_item + nseg;
   k_seg_count<<<(nchunk + 3) / 4, 128, (size_t)4 * p.E * sizeof(int), st>>>(p, nchunk);
+  coli_count_launch(1);
   k_seg_scan<<<1, 1024, 0, st>>>(p, nchunk, max_items);
+  coli_count_launch(1);
   const int total = p.T * p.k + (p.has_shared ? p.T : 0);
   k_permute<<<(total + 7) / 8, 256, 0, st>>>(p);
+  coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "permute launch") ? 1 : 0;
 }
 
@@ -417,6 +424,7 @@ int launch_items_from_counts(const int32_t *seg_count, int nseg, int rows_per_it
                              cudaStream_t st) {
   k_items_from_counts<<<1, 32, 0, st>>>(seg_count, nseg, rows_per_item, seg_off, item_seg, item_row0,
                                         item_nrows, n_items);
+  coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "work list launch") ? 1 : 0;
 }
 

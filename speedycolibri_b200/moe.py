@@ -131,6 +131,27 @@ class MoeBlock:
         _check(_lib_().coli_b200_moe_last_routing(self.handle, T, _np_ptr(idx), _np_ptr(w)), "coli_b200_moe_last_routing")
         return idx, w
 
+    def moe_ptr(self, x_ptr: int, out_ptr: int, T: int) -> None:
+        """coli_b200_moe_block on raw HOST addresses (e.g. pinned buffers): bf16 [T,H] each."""
+        _check(_lib_().coli_b200_moe_block(self.handle, x_ptr, out_ptr, T, None, None), "coli_b200_moe_block")
+
+    def stream(self) -> int:
+        """The cudaStream_t the host-pointer call runs on."""
+        return _lib_().coli_b200_moe_stream(self.handle)
+
+    PHASES = ("router", "permute", "gate_up", "down", "combine")
+
+    def profile(self, enable: bool) -> None:
+        """Per-phase CUDA-event timing inside forward() (synchronises each call while on)."""
+        _check(_lib_().coli_b200_moe_profile(self.handle, int(enable)), "coli_b200_moe_profile")
+
+    def phase_ms(self):
+        """(dict phase -> accumulated ms, number of calls) since profile(True)."""
+        ms = (C.c_float * len(self.PHASES))()
+        n = C.c_int()
+        _check(_lib_().coli_b200_moe_phase_ms(self.handle, ms, C.byref(n)), "coli_b200_moe_phase_ms")
+        return dict(zip(self.PHASES, [float(v) for v in ms])), n.value
+
     def workspace_bytes(self) -> int:
         return _lib_().coli_b200_moe_workspace_bytes(self.handle)
 

@@ -1,0 +1,374 @@
+"""Parity of the CUDA path against the CPU oracle, through the C ABI.  Bars: routing indices and
+weights bit-exact; quantised bytes bit-exact; block output relative L2 <= 1e-2 on bf16 (the
+tolerance the task states), rows compared on the same seeded inputs and quantised weights."""
+import numpy as np
+import pytest
+
+from speedycolibri_b200 import synth
+from speedycolibri_b200.configs import CONFIGS, FMT_E4M3_ROW, FMT_FP8_B128, FMT_NVFP4
+from tests.helpers import host_layer, oracle_layer_from_device, rel_l2, upload_layer
+
+pytestmark = pytest.mark.gpu
+REL_L2_TOL = 1e-2
+
+
+def make_block(shape, layer, max_tokens=None, **kw):
+    from speedycolibri_b200.moe import Config, MoeBlock
+
+    return MoeBlock(Config.from_shape(shape), layer, max_tokens or shape.T, **kw)
+
+
+# ---- byte-exact pieces ------------------------------------------------------------------------------
+@pytest.mark.parametrize("O,I", [(48, 256), (16, 16), (33, 200), (128, 2048), (7, 24)])
+def test_device_quantiser_nvfp4_bit_exact(gpu_backend, orc, O, I):
+    import torch
+
+    rng = np.random.default_rng(O * 1000 + I)
+    w = (rng.standard_normal((O, I)) * 0.02).astype(np.float32)
+    w[0, : min(16, I)] = 0.0                    # an all-zero block (scale code 0)
+    w[-1, -1] = 0.5                             # an outlier that sets the tensor scale
+    nib, bs, g = gpu_backend.quantize_nvfp4_dev(torch.from_numpy(w).cuda())
+    wn, wb, wg = orc.quantize_nvfp4(w)
+    assert g == wg
+    assert np.array_equal(bs.cpu().numpy(), wb)
+    assert np.array_equal(nib.cpu().numpy(), wn)
+
+
+@pytest.mark.parametrize("O,I", [(128, 128), (200, 300), (768, 2048)])
+def test_device_quantiser_fp8_bit_exact(gpu_backend, orc, O, I):
+    import torch
+
+    rng = np.random.default_rng(O + I)
+    w = (rng.standard_normal((O, I)) * 0.02).astype(np.float32)
+    codes, sc = gpu_backend.quantize_fp8_b128_dev(torch.from_numpy(w).cuda())
+    wc, ws = orc.quantize_fp8_b128(w)
+    assert np.array_equal(sc.cpu().numpy(), ws)
+    assert np.array_equal(codes.cpu().numpy(), wc)
+
+
+@pytest.mark.parametrize("O,I", [(32, 128), (40, 200), (768, 2048), (5, 24)])
+def test_upload_export_roundtrip(gpu_backend, orc, O, I):
+    """The HBM repack is a permutation: what went in comes back out, for every format."""
+    rng = np.random.default_rng(5)
+    w = (rng.standard_normal((O, I)) * 0.02).astype(np.float32)
+    nib, bs, g = orc.quantize_nvfp4(w)
+    t = gpu_backend.CudaTensor.wrap_nvfp4(nib, bs, g, I, O)
+    q2, s2, g2 = t.export()
+    assert np.array_equal(q2, nib) and np.array_equal(s2, bs) and g2 == np.float32(g)
+    assert t.nbytes() >= nib.size + bs.size
+    codes, sc = orc.quantize_fp8_b128(w)
+    t8 = gpu_backend.CudaTensor.upload(codes, sc, FMT_FP8_B128, I, O)
+    q3, s3, _ = t8.export()
+    assert np.array_equal(q3, codes) and np.array_equal(s3, sc)
+    n0, _ = gpu_backend.stats(0)
+    t.free(); t8.free()
+    assert gpu_backend.stats(0)[0] == n0 - 2
+
+
+def test_router_matmul_f32_bit_exact(gpu_backend, orc):
+    """coli_cuda_matmul fmt 0 == the reference's sequential matmul_f32 (linear.rs:209-220)."""
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((9, 200)).astype(np.float32)
+    w = rng.standard_normal((33, 200)).astype(np.float32)
+    mm = gpu_backend.F32Matmul(w)
+    y = mm(x)
+    want = orc.matmul_qt(0, w.view(np.uint8), np.zeros(1, np.uint8), 1.0, x, 33)
+    assert np.array_equal(y, want)
+    assert np.array_equal(mm(x[:2]), want[:2])  # cached device copy of W is reused
+    mm.free()
+
+
+# ---- routing ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name,T", [("tiny", 5), ("tiny_sig", 37), ("tiny_zipf", 70), ("tiny_fp8", 19), ("c0", 128),
+                                    ("c1", 1), ("c1", 8), ("c1", 77), ("tiny_sig", 300)])
+def test_routing_bit_exact(gpu_backend, orc, name, T):
+    shape = CONFIGS[name].with_tokens(T)
+    L, packed = host_layer(shape) if shape.E * shape.H * shape.I < 2e7 else (None, None)
+    if L is None:
+        pytest.skip("shape too large for host generation")
+    blk = make_block(shape, upload_layer(shape, packed))
+    x = synth.host_tokens(shape, T)
+    out, idx, w = blk.moe(x, want_routing=True)
+    widx, ww = L.route_tokens(x)
+    assert np.array_equal(idx, widx)
+    assert np.array_equal(w.view(np.uint32), ww.view(np.uint32)), float(np.abs(w - ww).max())
+    blk.close()
+
+
+def test_routing_near_ties_and_extremes(gpu_backend, orc):
+    """Ties (duplicate router rows => equal logits) go to the lowest id; huge logits survive."""
+    shape = CONFIGS["tiny"]
+    L, packed = host_layer(shape)
+    router = packed["router"].copy()
+    router[3] = router[1]
+    router[6] = router[1]                                   # experts 1, 3, 6 always tie
+    packed = dict(packed, router=router)
+    from oracle import oracle
+    Lt = oracle.Layer(shape.H, shape.E, shape.k, shape.I, shape.score, shape.norm_topk, shape.routed_scale, 1, 1,
+                      shape.fmt, router, packed["experts"], packed["shared"], None, None)
+    blk = make_block(shape, upload_layer(shape, packed), max_tokens=64)
+    x = synth.host_tokens(shape, 64)
+    x[0] = synth.f32_to_bf16_bits(synth.bf16_bits_to_f32(x[0]) * 300.0)   # logits in the hundreds
+    _, idx, w = blk.moe(x, want_routing=True)
+    widx, ww = Lt.route_tokens(x)
+    assert np.array_equal(idx, widx) and np.array_equal(w.view(np.uint32), ww.view(np.uint32))
+    for row in idx.tolist():
+        if 3 in row:
+            assert 1 in row and row.index(1) < row.index(3)
+    assert np.isfinite(w).all()
+    blk.close()
+
+
+# ---- whole block ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name,T", [("tiny", 5), ("tiny", 1), ("tiny_sig", 37), ("tiny_fp8", 19), ("tiny_zipf", 70),
+                                    ("tiny_sig", 150)])
+def test_block_small_shapes(gpu_backend, orc, name, T):
+    shape = CONFIGS[name].with_tokens(T)
+    L, packed = host_layer(shape)
+    blk = make_block(shape, upload_layer(shape, packed))
+    x = synth.host_tokens(shape, T)
+    out = blk.moe(x)
+    want = L.moe_block(x)
+    err = rel_l2(out, want["out"])
+    assert err <= REL_L2_TOL, err
+    assert err <= 5e-3, f"small shapes should be well inside the bar, got {err}"
+    blk.close()
+
+
+def test_block_empty_and_bounds(gpu_backend, orc):
+    from speedycolibri_b200.backend import CudaError
+
+    shape = CONFIGS["tiny"]
+    _, packed = host_layer(shape)
+    blk = make_block(shape, upload_layer(shape, packed), max_tokens=4)
+    assert blk.moe(np.zeros((0, shape.H), np.uint16)).shape == (0, shape.H)
+    with pytest.raises(CudaError, match="outside"):
+        blk.moe(synth.host_tokens(shape, 5))
+    assert blk.workspace_bytes() > 0
+    blk.close()
+
+
+def _device_block_vs_oracle(shape, T_check, tokens_for_routing=None):
+    """Full-size run on the GPU with device-generated weights; the oracle recomputes a subset of
+    the tokens (the block is row-independent) from the exported bytes of the same weights."""
+    import torch
+    from speedycolibri_b200.moe import Config, MoeBlock
+
+    layer = synth.device_layer(shape)
+    blk = MoeBlock(Config.from_shape(shape), layer, shape.T)
+    x = synth.device_tokens(shape)
+    out = blk.forward(x)
+    torch.cuda.synchronize()
+    idx, w = blk.last_routing(shape.T)
+    out_h = out.view(torch.int16).cpu().numpy().view(np.uint16)
+    x_h = x.view(torch.int16).cpu().numpy().view(np.uint16)
+    sub = np.linspace(0, shape.T - 1, T_check).astype(int)
+    needed = set(idx[sub].reshape(-1).tolist())
+    L = oracle_layer_from_device(shape, layer, needed)
+    want = L.moe_block(x_h[sub])
+    assert np.array_equal(idx[sub], want["idx"])
+    assert np.array_equal(w[sub].view(np.uint32), want["w"].view(np.uint32))
+    err = rel_l2(out_h[sub], want["out"])
+    # routing of (many) more tokens, cheap on the CPU
+    nr = min(shape.T, tokens_for_routing or shape.T)
+    ridx, rw = L.route_tokens(x_h[:nr])
+    assert np.array_equal(idx[:nr], ridx)
+    assert np.array_equal(w[:nr].view(np.uint32), rw.view(np.uint32))
+    # size-independent properties at full size
+    assert np.isfinite(synth.bf16_bits_to_f32(out_h)).all()
+    assert all(len(set(r)) == shape.k for r in idx[:: max(1, shape.T // 512)].tolist())
+    blk.close()
+    return err, idx
+
+
+def test_block_c0_full(gpu_backend, orc):
+    shape = CONFIGS["c0"]
+    L, packed = host_layer(shape)
+    blk = make_block(shape, upload_layer(shape, packed))
+    x = synth.host_tokens(shape)
+    out, idx, w = blk.moe(x, want_routing=True)
+    want = L.moe_block(x)
+    assert np.array_equal(idx, want["idx"]) and np.array_equal(w.view(np.uint32), want["w"].view(np.uint32))
+    assert rel_l2(out, want["out"]) <= REL_L2_TOL
+    # device-pointer path gives the same bytes as the host-pointer path
+    import torch
+    xd = torch.from_numpy(x.view(np.int16)).cuda().view(torch.bfloat16)
+    od = blk.forward(xd)
+    torch.cuda.synchronize()
+    assert np.array_equal(od.view(torch.int16).cpu().numpy().view(np.uint16), out)
+    blk.close()
+
+
+@pytest.mark.parametrize("T", [1, 4, 8])
+def test_block_c1_decode(gpu_backend, orc, T):
+    err, _ = _device_block_vs_oracle(CONFIGS["c1"].with_tokens(T), T)
+    assert err <= REL_L2_TOL, err
+
+
+def test_block_c2_fp8_prefill(gpu_backend, orc):
+    err, idx = _device_block_vs_oracle(CONFIGS["c2"], 24)
+    assert err <= REL_L2_TOL, err
+    load = np.bincount(idx.reshape(-1), minlength=128)
+    assert load.min() > 0 and load.max() < 4 * load.mean()  # logits ~N(0,1): near-uniform load
+
+
+def test_block_c3_group_limited_full_size(gpu_backend, orc):
+    shape = CONFIGS["c3"]
+    err, idx = _device_block_vs_oracle(shape, 6, tokens_for_routing=512)
+    assert err <= REL_L2_TOL, err
+    groups = idx // (shape.E // shape.n_group)
+    assert all(len(set(g)) <= shape.topk_group for g in groups[::16].tolist())
+
+
+def test_block_c4_zipf_full_size(gpu_backend, orc):
+    shape = CONFIGS["c4"]
+    err, idx = _device_block_vs_oracle(shape, 4, tokens_for_routing=256)
+    assert err <= REL_L2_TOL, err
+    load = np.sort(np.bincount(idx.reshape(-1), minlength=shape.E))[::-1]
+    assert load[0] > 20 * max(1, load[-1])  # Zipf(1.2): heavy skew
+
+
+def test_row_results_do_not_depend_on_batch(gpu_backend, orc):
+    """A token's output must not change with the batch it travels in (the reference's `exact`
+    contract, crates/colibri-engine/src/gpu.rs:122-146)."""
+    shape = CONFIGS["tiny_sig"].with_tokens(96)
+    _, packed = host_layer(shape)
+    blk = make_block(shape, upload_layer(shape, packed))
+    x = synth.host_tokens(shape, 96)
+    full = blk.moe(x)
+    for n in (1, 7, 40):
+        assert np.array_equal(blk.moe(x[:n]), full[:n])
+    blk.close()
+
+
+# ---- the reference's host-pointer expert calls ------------------------------------------------------------
+def test_expert_mlp_and_group_nvfp4(gpu_backend, orc):
+    shape = CONFIGS["tiny_sig"]
+    L, packed = host_layer(shape)
+    layer = upload_layer(shape, packed)
+    rng = np.random.default_rng(11)
+    for S in (1, 4, 16, 32, 33):   # every kernel arm of the reference's own GPU test (gpu.rs:2291-2351)
+        x = synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(rng.standard_normal((S, shape.H)).astype(np.float32)))
+        e = layer.experts[3]
+        y = gpu_backend.expert_mlp_nvfp4(e.gate, e.up, e.down, x)
+        want = L.expert_ffn(3, x)
+        assert np.abs(y - want).max() <= 1e-2 * np.abs(want).max()
+    rows = [3, 1, 9]
+    x = synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(rng.standard_normal((sum(rows), shape.H)).astype(np.float32)))
+    es = [layer.experts[i] for i in (0, 5, 2)]
+    y = gpu_backend.expert_group_nvfp4([e.gate for e in es], [e.up for e in es], [e.down for e in es], rows, x)
+    off = 0
+    for ei, r in zip((0, 5, 2), rows):
+        want = L.expert_ffn(ei, x[off:off + r])
+        assert np.abs(y[off:off + r] - want).max() <= 1e-2 * np.abs(want).max()
+        off += r
+    from speedycolibri_b200.backend import CudaError
+    with pytest.raises(CudaError):  # shape mismatch is refused, as in backend_cuda.cu:3669-3671
+        gpu_backend.expert_mlp_nvfp4(es[0].gate, es[0].down, es[0].down, x)
+
+
+def test_expert_mlp_fp8_row_scaled(gpu_backend, orc):
+    """fmt 4 (per-row scaled e4m3), the reference's resident fp8 expert format (linear.rs:93-109)."""
+    rng = np.random.default_rng(2)
+    H, I, S = 256, 128, 5
+    mats = []
+    for O, K in ((I, H), (I, H), (H, I)):
+        w = (rng.standard_normal((O, K)) * 0.02).astype(np.float32)
+        sc = (np.abs(w).max(axis=1) / 448.0).astype(np.float32)
+        codes = np.array([[orc.lib().orc_f32_to_e4m3(float(v)) for v in row] for row in (w / sc[:, None])], np.uint8)
+        mats.append((codes, sc))
+    ts = [gpu_backend.CudaTensor.upload(c, s, FMT_E4M3_ROW, K, O) for (c, s), (O, K) in zip(mats, ((I, H), (I, H), (H, I)))]
+    x = synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(rng.standard_normal((S, H)).astype(np.float32)))
+    y = gpu_backend.expert_mlp_fp8(ts[0], ts[1], ts[2], x)
+    g = orc.matmul_qt(FMT_E4M3_ROW, mats[0][0], mats[0][1], 1.0, x, I)
+    u = orc.matmul_qt(FMT_E4M3_ROW, mats[1][0], mats[1][1], 1.0, x, I)
+    h = (g / (1 + np.exp(-g)) * u).astype(np.float32)
+    want = orc.matmul_qt(FMT_E4M3_ROW, mats[2][0], mats[2][1], 1.0, h, H)
+    assert np.abs(y - want).max() <= 1e-2 * np.abs(want).max()
+
+
+# ---- stage calls (what expert parallelism is assembled from), emulated on one GPU -------------------------------
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_stage_calls_emulate_expert_parallel(gpu_backend, orc, world):
+    """`world` handles on ONE GPU stand for the ranks (a single process, stages run one after the
+    other, the all-to-all done by slicing) — ranks never wait on one another on the device."""
+    import torch
+    from speedycolibri_b200.cluster import ExpertSharding, exchange_plan
+    from speedycolibri_b200.moe import Config, MoeBlock
+
+    shape = CONFIGS["tiny_sig"].with_tokens(40 * world)
+    L, packed = host_layer(shape)
+    x_all = synth.host_tokens(shape, shape.T)
+    want = L.moe_block(x_all, world=world)
+    sh = ExpertSharding.new(world, shape.E)
+    n_local = [sh.count_for(r) for r in range(world)]
+    bounds = np.concatenate([[0], np.cumsum(n_local)])
+    Tl = shape.T // world
+    blks, st = [], torch.cuda.current_stream().cuda_stream
+    for r in range(world):
+        layer = upload_layer(shape, packed, local=set(sh.local_experts(r)))
+        blks.append(MoeBlock(Config.from_shape(shape), layer, Tl, ep_rank=r, ep_world=world))
+    xs = [torch.from_numpy(x_all[r * Tl:(r + 1) * Tl].view(np.int16)).cuda().view(torch.bfloat16) for r in range(world)]
+    rows, segs, slots = [], [], []
+    for r in range(world):
+        rw = torch.empty((Tl * shape.k, shape.H), dtype=torch.bfloat16, device="cuda")
+        sc = torch.empty(shape.E, dtype=torch.int32, device="cuda")
+        sl = torch.empty(Tl * shape.k, dtype=torch.int32, device="cuda")
+        blks[r].route_dev(xs[r], rw, sc, sl, st)
+        rows.append(rw); segs.append(sc.cpu().numpy()); slots.append(sl)
+    row_off = [np.concatenate([[0], np.cumsum(s)]) for s in segs]
+    y_back = [torch.empty_like(rows[r]) for r in range(world)]
+    for d in range(world):  # destination rank: gather what every source sends it, [src][expert] order
+        recv_counts = np.stack([segs[s][bounds[d]:bounds[d + 1]] for s in range(world)])
+        parts = [rows[s][row_off[s][bounds[d]]:row_off[s][bounds[d + 1]]] for s in range(world)]
+        recv = torch.cat(parts) if parts else rows[0][:0]
+        _, rsplit, perm, per_e = exchange_plan(segs[d], n_local, recv_counts, d)
+        perm_t = torch.from_numpy(perm).cuda()
+        em = recv.index_select(0, perm_t)
+        y_em = torch.empty_like(em)
+        blks[d].experts_dev(em, torch.from_numpy(per_e).cuda(), int(bounds[d]), n_local[d], em.shape[0], y_em, st)
+        y_recv = torch.empty_like(recv)
+        y_recv.index_copy_(0, perm_t, y_em)
+        off = 0
+        for s in range(world):  # the return all-to-all
+            n = rsplit[s]
+            y_back[s][row_off[s][bounds[d]]:row_off[s][bounds[d + 1]]] = y_recv[off:off + n]
+            off += n
+    outs = []
+    for r in range(world):
+        sy = torch.empty((Tl, shape.H), dtype=torch.bfloat16, device="cuda")
+        blks[r].shared_dev(xs[r], sy, st)
+        o = torch.empty((Tl, shape.H), dtype=torch.bfloat16, device="cuda")
+        blks[r].combine_dev(y_back[r], slots[r], sy, o, st)
+        outs.append(o)
+    torch.cuda.synchronize()
+    got = torch.cat(outs).view(torch.int16).cpu().numpy().view(np.uint16)
+    assert rel_l2(got, want["out"]) <= REL_L2_TOL
+    if world == 1:  # identical kernels, identical bytes as the one-call block
+        layer = upload_layer(shape, packed)
+        one = MoeBlock(Config.from_shape(shape), layer, shape.T)
+        assert np.array_equal(one.moe(x_all), got)
+        one.close()
+    for b in blks:
+        b.close()
+
+
+def test_tracing_phases_and_launch_count(gpu_backend):
+    import torch
+    from speedycolibri_b200 import _lib
+
+    shape = CONFIGS["tiny_sig"]
+    _, packed = host_layer(shape)
+    blk = make_block(shape, upload_layer(shape, packed))
+    x = torch.from_numpy(synth.host_tokens(shape).view(np.int16)).cuda().view(torch.bfloat16)
+    n0 = _lib.load().coli_b200_launch_count()
+    blk.forward(x)
+    torch.cuda.synchronize()
+    assert _lib.load().coli_b200_launch_count() - n0 == 8  # router 2, permute 3, gate/up, down, combine
+    blk.profile(True)
+    for _ in range(3):
+        blk.forward(x)
+    ms, calls = blk.phase_ms()
+    blk.profile(False)
+    assert calls == 3 and all(v > 0 for v in ms.values())
+    blk.close()
