@@ -197,6 +197,28 @@ void *coli_b200_moe_stream(ColiMoe *moe);
 /* Kernels this library has launched in the calling process since it was loaded. */
 uint64_t coli_b200_launch_count(void);
 
+/* ---- routing with no allocation (no counterpart in the reference: there the router runs on the
+ * CPU, crates/colibri-engine/src/moe.rs:1047-1132, and allocates freely) ------------------------
+ * For callers that cannot allocate device memory at all — a server whose HBM is fully handed to
+ * its weight and KV pools (cudaMalloc would fail or upset its memory ledger), or a decode loop
+ * that cannot take the device-wide stall of cudaMalloc/cudaFree.  Router GEMM + score + top-k
+ * for x_dev[T,H] (bf16) against router_w_dev[E,H] (bf16); results go to topk_idx_dev [T,k] and
+ * topk_w_dev [T,k], bit-identical to what a ColiMoe handle computes.  Everything is a DEVICE
+ * pointer supplied by the caller; the only scratch, the [T,E] f32 logits, sits in a fixed
+ * 512 KiB device array built into the library (resident on every GPU that loads it, until
+ * exit), so the call makes no cudaMalloc/cudaFree and needs T*E <= COLI_ROUTE_NOALLOC_MAX_LOGITS
+ * (larger batches are refused with an error).
+ * The first call on a device looks up that array's device address (once per device, with the
+ * device current) — make that first call before starting any stream capture.
+ * All calls on one GPU share the one array: it keeps the previous call's logits (harmless, each
+ * call overwrites its own [T,E] before reading) and two calls that overlap on the GPU — on
+ * different streams, or from different threads — race on it; serialise them. */
+#define COLI_ROUTE_NOALLOC_MAX_LOGITS 131072
+int coli_b200_route_noalloc(const void *x_dev, const void *router_w_dev, const float *select_bias_dev,
+                            const float *logit_bias_dev, int T, int H, int E, int k, int score, int norm_topk,
+                            float routed_scale, int n_group, int topk_group, int32_t *topk_idx_dev,
+                            float *topk_w_dev, void *stream);
+
 /* FNV-1a fingerprint of an expert->rank map (crates/colibri-cluster/src/sharding.rs:251-265);
  * `owner` NULL = contiguous.  Ranks compare it before the first exchange. */
 uint64_t coli_b200_sharding_fingerprint(uint32_t num_nodes, uint32_t n_experts, const uint32_t *owner);

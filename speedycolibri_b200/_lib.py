@@ -98,6 +98,7 @@ SIGNATURES = {
     "coli_b200_moe_phase_ms": (_i, [_P, C.POINTER(_f), C.POINTER(_i)]),
     "coli_b200_moe_stream": (_P, [_P]),
     "coli_b200_launch_count": (C.c_uint64, []),
+    "coli_b200_route_noalloc": (_i, [_P, _P, _P, _P, _i, _i, _i, _i, _i, _i, _f, _i, _i, _P, _P, _P]),
     "coli_b200_sharding_fingerprint": (C.c_uint64, [C.c_uint32, C.c_uint32, _P]),
 }
 

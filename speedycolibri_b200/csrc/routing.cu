@@ -429,3 +429,79 @@ int launch_items_from_counts(const int32_t *seg_count, int nseg, int rows_per_it
 }
 
 }  // namespace colib
+
+// ---------------------------------------------------------------------------------------------
+// Routing without any allocation.
+//
+// The router needs a [T,E] f32 logits buffer between its GEMM and its top-k kernel.  Every
+// other entry point takes that buffer from a handle's cudaMalloc'ed workspace.  This one is for
+// callers that must not allocate at all: a serving process that handed every free byte of HBM
+// to its weight and KV pools at start-up (a later cudaMalloc there fails, or trips the host's
+// memory ledger), and decode loops that cannot afford the device-wide synchronisation a
+// cudaMalloc/cudaFree implies.  The logits live in a fixed array that is part of the library
+// image, so each GPU that loads the library carries it (512 KiB) until the process exits.
+//
+// `g_route_scratch` below is a device symbol.  In host code the name is only a stand-in for
+// it, not a device address, so the address handed to the kernels is looked up once per device
+// with cudaGetSymbolAddress while that device is current.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) float g_route_scratch[COLI_ROUTE_NOALLOC_MAX_LOGITS];
+
+static float *g_route_scratch_addr[COLI_CUDA_MAX_DEVICES];  // per device, filled on first use
+static bool g_route_scratch_ready[COLI_CUDA_MAX_DEVICES];
+
+extern "C" int coli_b200_route_noalloc(const void *x_dev, const void *router_w_dev, const float *select_bias_dev,
+                                       const float *logit_bias_dev, int T, int H, int E, int k, int score,
+                                       int norm_topk, float routed_scale, int n_group, int topk_group,
+                                       int32_t *topk_idx_dev, float *topk_w_dev, void *stream) {
+  if (!x_dev || !router_w_dev || !topk_idx_dev || !topk_w_dev || T < 0 || H < 1 || E < 1 || k < 1 || k > E) {
+    coli_set_error("route_noalloc: null pointer or bad shape (T=%d H=%d E=%d k=%d)", T, H, E, k);
+    return 0;
+  }
+  if ((long long)T * E > (long long)COLI_ROUTE_NOALLOC_MAX_LOGITS) {
+    coli_set_error("route_noalloc: T*E = %lld exceeds the built-in scratch of %d logits; use a ColiMoe handle for larger batches",
+                   (long long)T * E, COLI_ROUTE_NOALLOC_MAX_LOGITS);
+    return 0;
+  }
+  if (score != COLI_SCORE_SOFTMAX && score != COLI_SCORE_SIGMOID) {
+    coli_set_error("route_noalloc: unknown score function %d", score);
+    return 0;
+  }
+  int dev = -1;
+  if (!coli_cuda_check(cudaGetDevice(&dev), "route_noalloc: cudaGetDevice")) return 0;
+  if (dev < 0 || dev >= COLI_CUDA_MAX_DEVICES) {
+    coli_set_error("route_noalloc: device ordinal %d out of range", dev);
+    return 0;
+  }
+  if (!g_route_scratch_ready[dev]) {
+    // set-up, once per device, with that device current: resolve the symbol to its device address
+    float *ptr = nullptr;
+    if (!coli_cuda_check(cudaGetSymbolAddress((void **)&ptr, g_route_scratch), "route_noalloc: cudaGetSymbolAddress")) return 0;
+    if (!ptr) {
+      coli_set_error("route_noalloc: scratch symbol resolved to a null address");
+      return 0;
+    }
+    g_route_scratch_addr[dev] = ptr;
+    g_route_scratch_ready[dev] = true;
+  }
+  if (T == 0) return 1;
+  colib::RouteParams p;
+  p.T = T;
+  p.H = H;
+  p.E = E;
+  p.k = k;
+  p.score = score;
+  p.norm_topk = norm_topk;
+  p.routed_scale = routed_scale;
+  p.n_group = n_group < 1 ? 1 : n_group;
+  p.topk_group = topk_group < 1 ? 1 : topk_group;
+  p.x = (const __nv_bfloat16 *)x_dev;
+  p.router_w = (const __nv_bfloat16 *)router_w_dev;
+  p.select_bias = select_bias_dev;
+  p.logit_bias = logit_bias_dev;
+  p.logits = g_route_scratch_addr[dev];  // every logit of [T,E] is written before it is read: nothing to clear
+  p.topk_idx = topk_idx_dev;
+  p.topk_w = topk_w_dev;
+  return colib::launch_router(p, (cudaStream_t)stream);
+}
+
