@@ -156,6 +156,10 @@ int coli_b200_moe_block(ColiMoe *moe, const void *x, void *out, int T, int32_t *
  * stream, coli_b200_moe_stream() gives the handle's own).  One handle's workspace serves one
  * call at a time: calls on different streams must not overlap. */
 int coli_b200_moe_block_dev(ColiMoe *moe, const void *x_dev, void *out_dev, int T, void *stream);
+/* Synchronise the device and return 1 if every kernel launched through this handle since the
+ * last check ran to completion, 0 (with an error text) if one abandoned a bounded device-side
+ * wait.  The host-pointer call above performs this check itself. */
+int coli_b200_moe_check(ColiMoe *moe);
 /* Copy the last call's routing to HOST (after synchronising the stream). */
 int coli_b200_moe_last_routing(ColiMoe *moe, int T, int32_t *topk_idx, float *topk_w);
 

@@ -9,7 +9,7 @@ import threading
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_HERE, "csrc")
 LIB_PATH = os.path.join(_HERE, "libcoli_b200.so")
-SOURCES = ["abi.cu", "routing.cu", "layout.cu", "expert_small.cu", "combine.cu"]
+SOURCES = ["abi.cu", "routing.cu", "layout.cu", "expert_small.cu", "expert_tc.cu", "combine.cu"]
 HEADERS = ["internal.cuh", "coli_math.h", os.path.join("..", "..", "include", "coli_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -89,6 +89,7 @@ SIGNATURES = {
     "coli_b200_moe_workspace_bytes": (_sz, [_P]),
     "coli_b200_moe_block": (_i, [_P, _P, _P, _i, _P, _P]),
     "coli_b200_moe_block_dev": (_i, [_P, _P, _P, _i, _P]),
+    "coli_b200_moe_check": (_i, [_P]),
     "coli_b200_moe_last_routing": (_i, [_P, _i, _P, _P]),
     "coli_b200_moe_route_dev": (_i, [_P, _P, _i, _P, _P, _P, _P]),
     "coli_b200_moe_experts_dev": (_i, [_P, _P, _P, _i, _i, _i, _P, _P]),

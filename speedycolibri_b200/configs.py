@@ -72,5 +72,8 @@ CONFIGS = {
     "tiny_sig": MoeShape("tiny_sig", H=128, E=16, k=4, I=64, T=37, score=SCORE_SIGMOID, norm_topk=True,
                          routed_scale=2.5, n_group=4, topk_group=2, select_bias_std=0.05),
     "tiny_fp8": MoeShape("tiny_fp8", H=256, E=8, k=2, I=128, T=19, fmt=FMT_FP8_B128),
+    # prefill-sized segments (tcgen05 path), small enough for host generation
+    "mid": MoeShape("mid", H=512, E=8, k=2, I=256, T=512, norm_topk=True),
+    "mid_ragged": MoeShape("mid_ragged", H=320, E=6, k=2, I=192, T=333, shared=False),
     "tiny_zipf": MoeShape("tiny_zipf", H=64, E=16, k=4, I=32, T=70, shared=False, zipf_s=1.2),
 }

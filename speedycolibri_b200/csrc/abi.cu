@@ -351,6 +351,9 @@ struct ColiMoe {
   int32_t *item_seg, *item_row0, *item_nrows, *n_items;
   int item_cap;
   __nv_bfloat16 *h, *y, *x_stage, *out_stage;
+  __nv_bfloat16 *xg;  // gathered rows for the tcgen05 path (null when max_tokens never reaches it)
+  int *status;        // device status word of the tcgen05 kernels
+  int sm_count;
   size_t h_rows_cap;  // rows the h scratch holds
   size_t ws_bytes;
   std::vector<void *> allocs;
@@ -400,6 +403,12 @@ extern "C" int coli_b200_moe_phase_ms(ColiMoe *m, float *ms, int *calls) {
   return 1;
 }
 extern "C" void *coli_b200_moe_stream(ColiMoe *m) { return m ? (void *)m->ctx->stream : nullptr; }
+
+// The tcgen05 path takes over when segments are prefill-sized (NVFP4 only); a pure function of
+// (rows, segments, format) so that kernel selection never depends on data or addresses.
+static bool use_tc_path(int fmt, int rows, int nseg) {
+  return fmt == COLI_FMT_NVFP4 && nseg > 0 && rows / nseg >= 48;
+}
 
 static int rows_per_item_for(const ColiMoeLayer &L, int rows, int nseg) {
   const int avg = (rows + nseg - 1) / (nseg > 0 ? nseg : 1);
@@ -517,6 +526,15 @@ extern "C" int coli_b200_moe_create(ColiMoe **out, const ColiMoeLayer *L, int ma
        ws_alloc(m, &m->h, rows * I) && ws_alloc(m, &m->y, rows * H) && ws_alloc(m, &m->x_stage, T * H) &&
        ws_alloc(m, &m->out_stage, T * H);
   m->h_rows_cap = rows;
+  m->xg = nullptr;
+  m->status = nullptr;
+  {
+    cudaDeviceProp prop;
+    ok = ok && coli_cuda_check(cudaGetDeviceProperties(&prop, L->device), "device properties");
+    m->sm_count = ok ? prop.multiProcessorCount : 0;
+  }
+  ok = ok && ws_alloc(m, &m->status, 1) && coli_cuda_check(cudaMemset(m->status, 0, sizeof(int)), "status clear");
+  if (ok && use_tc_path(L->fmt, (int)rows, m->nseg)) ok = ws_alloc(m, &m->xg, rows * H);
   m->select_bias = nullptr;
   m->logit_bias = nullptr;
   if (ok && L->select_bias) ok = ws_alloc(m, &m->select_bias, E);
@@ -612,6 +630,7 @@ static colib::PermuteParams permute_params(ColiMoe *m, const void *x_dev, int T,
   pp.n_items = m->n_items;
   pp.x = (const __nv_bfloat16 *)x_dev;
   pp.xg = (__nv_bfloat16 *)rows_dev;
+  pp.gather_shared = 0;
   return pp;
 }
 
@@ -629,7 +648,9 @@ extern "C" int coli_b200_moe_block_dev(ColiMoe *m, const void *x_dev, void *out_
   cudaStream_t st = pick_stream(m, stream);
   const int k = m->L.k;
   const int rows = T * k + (m->has_shared ? T : 0);
-  const int rpi = rows_per_item_for(m->L, rows, m->nseg);
+  const bool tc = use_tc_path(m->L.fmt, rows, m->nseg) && m->xg != nullptr;
+  const int rpi = tc ? colib::TC_MAX_TOKENS : rows_per_item_for(m->L, rows, m->nseg);
+  const int max_items = rows / rpi + m->nseg;
   const bool prof = m->profiling;
 #define COLI_MARK(i)                                                         \
   do {                                                                       \
@@ -638,30 +659,55 @@ extern "C" int coli_b200_moe_block_dev(ColiMoe *m, const void *x_dev, void *out_
   COLI_MARK(0);
   if (!colib::launch_router(route_params(m, x_dev, T), st)) return 0;
   COLI_MARK(1);
-  if (!colib::launch_permute(permute_params(m, x_dev, T, m->has_shared, rpi, nullptr, m->seg_count, m->slot), st)) return 0;
+  {
+    colib::PermuteParams pp = permute_params(m, x_dev, T, m->has_shared, rpi, tc ? m->xg : nullptr, m->seg_count, m->slot);
+    pp.gather_shared = tc ? 1 : 0;
+    if (!colib::launch_permute(pp, st)) return 0;
+  }
   COLI_MARK(2);
-  colib::FfnParams fp;
-  fp.fmt = m->L.fmt;
-  fp.H = m->L.H;
-  fp.I = m->L.I;
-  fp.gate = m->gate;
-  fp.up = m->up;
-  fp.down = m->down;
-  fp.seg_expert = m->seg_expert;
-  fp.item_seg = m->item_seg;
-  fp.item_row0 = m->item_row0;
-  fp.item_nrows = m->item_nrows;
-  fp.n_items = m->n_items;
-  fp.max_items = rows / rpi + m->nseg;
-  fp.rows_per_item = rpi;
-  fp.x = (const __nv_bfloat16 *)x_dev;
-  fp.row_token = m->row_token;
-  fp.h = m->h;
-  fp.y = m->y;
-  fp.y32 = nullptr;
-  if (!colib::launch_gate_up_small(fp, st)) return 0;
-  COLI_MARK(3);
-  if (!colib::launch_down_small(fp, st)) return 0;
+  if (tc) {
+    colib::TcParams tp;
+    tp.H = m->L.H;
+    tp.I = m->L.I;
+    tp.gate = m->gate;
+    tp.up = m->up;
+    tp.down = m->down;
+    tp.seg_expert = m->seg_expert;
+    tp.item_seg = m->item_seg;
+    tp.item_row0 = m->item_row0;
+    tp.item_nrows = m->item_nrows;
+    tp.n_items = m->n_items;
+    tp.max_items = max_items;
+    tp.h = m->h;
+    tp.y = m->y;
+    tp.status = m->status;
+    if (!colib::launch_gate_up_tc(tp, m->xg, rows, m->sm_count, st)) return 0;
+    COLI_MARK(3);
+    if (!colib::launch_down_tc(tp, rows, m->sm_count, st)) return 0;
+  } else {
+    colib::FfnParams fp;
+    fp.fmt = m->L.fmt;
+    fp.H = m->L.H;
+    fp.I = m->L.I;
+    fp.gate = m->gate;
+    fp.up = m->up;
+    fp.down = m->down;
+    fp.seg_expert = m->seg_expert;
+    fp.item_seg = m->item_seg;
+    fp.item_row0 = m->item_row0;
+    fp.item_nrows = m->item_nrows;
+    fp.n_items = m->n_items;
+    fp.max_items = max_items;
+    fp.rows_per_item = rpi;
+    fp.x = (const __nv_bfloat16 *)x_dev;
+    fp.row_token = m->row_token;
+    fp.h = m->h;
+    fp.y = m->y;
+    fp.y32 = nullptr;
+    if (!colib::launch_gate_up_small(fp, st)) return 0;
+    COLI_MARK(3);
+    if (!colib::launch_down_small(fp, st)) return 0;
+  }
   COLI_MARK(4);
   colib::CombineParams cp;
   cp.T = T;
@@ -684,6 +730,20 @@ extern "C" int coli_b200_moe_block_dev(ColiMoe *m, const void *x_dev, void *out_
       m->phase_ms[i] += ms;
     }
     m->phase_calls++;
+  }
+  return 1;
+}
+
+// Synchronises the device and reports whether any kernel of this handle gave up on a bounded wait.
+extern "C" int coli_b200_moe_check(ColiMoe *m) {
+  if (!m || !select_ctx(m->ctx)) return 0;
+  CK(cudaDeviceSynchronize(), "moe_check sync");
+  int st = 0;
+  CK(cudaMemcpy(&st, m->status, sizeof(int), cudaMemcpyDeviceToHost), "status read");
+  if (st != 0) {
+    coli_set_error("a tcgen05 expert kernel abandoned a bounded wait (code %d: 1 copy, 2 MMA, 3 weight producer, 4 epilogue); results of that call are invalid", st);
+    cudaMemset(m->status, 0, sizeof(int));
+    return 0;
   }
   return 1;
 }
@@ -714,6 +774,13 @@ extern "C" int coli_b200_moe_block(ColiMoe *m, const void *x, void *out, int T, 
   if (topk_idx) CK(cudaMemcpyAsync(topk_idx, m->topk_idx, n * sizeof(int32_t), cudaMemcpyDeviceToHost, st), "routing download");
   if (topk_w) CK(cudaMemcpyAsync(topk_w, m->topk_w, n * sizeof(float), cudaMemcpyDeviceToHost, st), "routing download");
   CK(cudaStreamSynchronize(st), "moe_block sync");
+  int kst = 0;
+  CK(cudaMemcpy(&kst, m->status, sizeof(int), cudaMemcpyDeviceToHost), "status read");
+  if (kst != 0) {
+    coli_set_error("a tcgen05 expert kernel abandoned a bounded wait (code %d); the output is invalid", kst);
+    cudaMemset(m->status, 0, sizeof(int));
+    return 0;
+  }
   return 1;
 }
 
@@ -754,12 +821,31 @@ static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, cons
                         const void *rows_dev, const int32_t *seg_count_dev, int n_seg, int n_rows, void *y_dev,
                         cudaStream_t st) {
   if (n_rows == 0) return 1;
-  const int rpi = rows_per_item_for(m->L, n_rows, n_seg);
+  const bool tc = use_tc_path(m->L.fmt, n_rows, n_seg);
+  const int rpi = tc ? colib::TC_MAX_TOKENS : rows_per_item_for(m->L, n_rows, n_seg);
   const int max_items = n_rows / rpi + n_seg;
   if (!ensure_h(m, (size_t)n_rows) || !ensure_items(m, max_items)) return 0;
   if (!colib::launch_items_from_counts(seg_count_dev, n_seg, rpi, m->seg_off, m->item_seg, m->item_row0, m->item_nrows,
                                        m->n_items, st))
     return 0;
+  if (tc) {
+    colib::TcParams tp;
+    tp.H = m->L.H;
+    tp.I = m->L.I;
+    tp.gate = g;
+    tp.up = u;
+    tp.down = d;
+    tp.seg_expert = seg_expert_dev;
+    tp.item_seg = m->item_seg;
+    tp.item_row0 = m->item_row0;
+    tp.item_nrows = m->item_nrows;
+    tp.n_items = m->n_items;
+    tp.max_items = max_items;
+    tp.h = m->h;
+    tp.y = (__nv_bfloat16 *)y_dev;
+    tp.status = m->status;
+    return colib::launch_gate_up_tc(tp, rows_dev, n_rows, m->sm_count, st) && colib::launch_down_tc(tp, n_rows, m->sm_count, st);
+  }
   colib::FfnParams fp;
   fp.fmt = m->L.fmt;
   fp.H = m->L.H;

@@ -1,0 +1,431 @@
+// Expert FFN for prefill-sized segments on the 5th-generation tensor cores.
+//
+// Formulation (operands swapped so that the ragged token count lands on the MMA's N, which
+// has a granularity of 16, and the always-full feature axis on its M = 128):
+//     D[feature, token] = W[feature, :] . X[token, :]^T          per expert segment
+// * A operand (M side): a 128-feature x 64-k tile of the expert matrix.  The packed NVFP4
+//   bytes are streamed from HBM with 128-bit loads by 8 producer warps, decoded to bf16 in
+//   registers (exact: E2M1 x ue4m3 has <= 6 significant bits) and stored to shared memory in
+//   the K-major 128-byte-swizzled layout the MMA reads.
+// * B operand (N side): up to 256 token rows x 64 k of bf16 activations, copied by TMA
+//   (cp.async.bulk.tensor, 128-byte swizzle, no multicast) straight into the same layout.
+// * tcgen05.mma kind::f16 (bf16 x bf16 -> f32), issued by one thread, accumulates in TMEM; the
+//   gate and the up projection of the same 128 features use two accumulators (columns 0.. and
+//   256..) fed from the same token tile, so SiLU(g)*u is formed in the epilogue registers and
+//   only h is written.
+// * 4 epilogue warps read TMEM with tcgen05.ld (one lane = one feature), apply the per-tensor
+//   scale, the activation, and store bf16.
+// Roles are warp-specialised and synchronise through mbarriers only; the kernel is persistent
+// (one CTA per SM walks the device-built work list).  Every barrier wait is bounded: on a
+// time-out the CTA raises a status word, stops issuing work, waits for its own copies and frees
+// its TMEM before returning, so a logic error can end as an error code but not as a hung GPU.
+//
+// This replaces the reference's dequant-to-half + wmma kernels nvfp4_matmul / nvfp4_gate_up
+// (crates/colibri-backend/cuda/backend_cuda.cu:1355-1430) and its separate silu_mul launch
+// (backend_cuda.cu:3785-3787).
+#include <cuda.h>
+
+#include "internal.cuh"
+
+namespace colib {
+
+constexpr int TC_BM = 128;   // features per tile (UMMA M)
+constexpr int TC_BK = 64;    // k per pipeline stage: one 128-byte swizzle row of bf16
+constexpr int TC_BOXN = 32;  // token rows per TMA box
+constexpr int TC_PROD_WARPS = 8;
+constexpr int TC_EPI_WARPS = 4;
+constexpr int TC_THREADS = 32 * (2 + TC_EPI_WARPS + TC_PROD_WARPS);  // 448
+constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;                        // 16 KiB
+constexpr int TC_B_BYTES = TC_MAX_TOKENS * TC_BK * 2;                // 32 KiB
+constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
+
+enum { TC_OK = 0, TC_ERR_TMA_WAIT = 1, TC_ERR_MMA_WAIT = 2, TC_ERR_PROD_WAIT = 3, TC_ERR_EPI_WAIT = 4 };
+
+// ---- PTX wrappers ----------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when the barrier did not flip in time or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
+  for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 63u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicCAS(status, TC_OK, code);
+  return false;
+}
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr) {
+  uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;          // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;          // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;          // SWIZZLE_128B
+  return d;
+}
+// kind::f16: D = f32, A = B = bf16, both K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t umma_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+}
+
+__device__ __forceinline__ uint32_t tc_hmul2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+// One NVFP4 word (8 consecutive k: even elements in nibble slots 0..3, odd in 4..7) -> 8 bf16
+// (four bf16x2, k ascending), each equal to weight * 2^-16; see expert_small.cu for the bit layout.
+__device__ __forceinline__ uint4 tc_dequant_word(uint32_t w, uint32_t mult) {
+  uint4 o;
+  o.x = tc_hmul2(((w << 6) & 0x01C001C0u) | ((w << 12) & 0x80008000u), mult);
+  o.y = tc_hmul2(((w << 2) & 0x01C001C0u) | ((w << 8) & 0x80008000u), mult);
+  o.z = tc_hmul2(((w >> 2) & 0x01C001C0u) | ((w << 4) & 0x80008000u), mult);
+  o.w = tc_hmul2(((w >> 6) & 0x01C001C0u) | (w & 0x80008000u), mult);
+  return o;
+}
+
+struct TcPacked {
+  uint4 q;      // 32 weights of one row
+  uint32_t sc;  // their two block-scale bytes
+};
+__device__ __forceinline__ TcPacked tc_load_packed(const WeightRef &w, int Op, int row, int kb, int c) {
+  TcPacked r;
+  r.q = make_uint4(0, 0, 0, 0);
+  r.sc = 0;
+  if (row < Op) {
+    const size_t base = (size_t)(kb >> 1) * Op + row;
+    const int half = kb & 1;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.q.x), "=r"(r.q.y), "=r"(r.q.z), "=r"(r.q.w)
+                 : "l"(w.q + base * 64 + half * 32 + c * 16));
+    r.sc = *reinterpret_cast<const uint16_t *>(w.s + base * 8 + half * 4 + c * 2);
+  }
+  return r;
+}
+// Decode 32 weights and store them as chunks 4c..4c+3 of row `row` of a swizzled 128x64 tile.
+__device__ __forceinline__ void tc_store_tile(uint8_t *tile, int row, int c, const TcPacked &pk, const uint32_t *lut) {
+  const uint32_t m0 = lut[pk.sc & 0xffu], m1 = lut[(pk.sc >> 8) & 0xffu];
+  uint8_t *rbase = tile + (row >> 3) * 1024 + (row & 7) * 128;
+  const int sw = row & 7;
+  *reinterpret_cast<uint4 *>(rbase + (((c * 4 + 0) ^ sw) << 4)) = tc_dequant_word(pk.q.x, m0);
+  *reinterpret_cast<uint4 *>(rbase + (((c * 4 + 1) ^ sw) << 4)) = tc_dequant_word(pk.q.y, m0);
+  *reinterpret_cast<uint4 *>(rbase + (((c * 4 + 2) ^ sw) << 4)) = tc_dequant_word(pk.q.z, m1);
+  *reinterpret_cast<uint4 *>(rbase + (((c * 4 + 3) ^ sw) << 4)) = tc_dequant_word(pk.q.w, m1);
+}
+
+template <bool GATED>
+__global__ void __launch_bounds__(TC_THREADS, 1) k_ffn_tc(const __grid_constant__ CUtensorMap tmap, TcParams p) {
+  constexpr int MATS = GATED ? 2 : 1;
+  constexpr int STAGES = GATED ? 3 : 4;
+  constexpr int STAGE_BYTES = MATS * TC_A_BYTES + TC_B_BYTES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
+  const uint32_t full_a = smem_u32(bars), full_b = smem_u32(bars + STAGES), empty = smem_u32(bars + 2 * STAGES);
+  const uint32_t acc_full = smem_u32(bars + 3 * STAGES), acc_empty = smem_u32(bars + 3 * STAGES + 1);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * STAGES + 2);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  uint32_t *lut = tmem_slot + 4;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int K = GATED ? p.H : p.I, Oout = GATED ? p.I : p.H;
+  const int Op = (Oout + 15) & ~15;
+  const int KB = ((K + 127) >> 7) * 2;  // 64-wide k blocks, covering the zero-padded k tiles
+  const int n_ftiles = (Oout + TC_BM - 1) / TC_BM;
+  const int n_work = *p.n_items * n_ftiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_a + 8 * s, TC_PROD_WARPS);
+      mbar_init(full_b + 8 * s, 1);
+      mbar_init(empty + 8 * s, 1);
+    }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, TC_EPI_WARPS);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int b = threadIdx.x; b < 256; b += TC_THREADS) {
+    const float s = coli_e4m3_to_f32((uint8_t)b) * 1.2980742146337069e33f;  // * 2^110
+    const uint32_t h = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(s));
+    lut[b] = h | (h << 16);
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA: token tiles ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool alive = true;
+      for (int w = blockIdx.x; w < n_work && alive; w += gridDim.x) {
+        const int item = w / n_ftiles;
+        const int row0 = p.item_row0[item], nrows = p.item_nrows[item];
+        const int N = (nrows + TC_BOXN - 1) / TC_BOXN * TC_BOXN;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+          if (!mbar_wait(empty + 8 * s, ph ^ 1u, abort_flag, p.status, TC_ERR_TMA_WAIT)) {
+            alive = false;
+            break;
+          }
+          const uint32_t dst = smem_u32(smem + s * STAGE_BYTES + MATS * TC_A_BYTES);
+          mbar_expect_tx(full_b + 8 * s, (uint32_t)N * TC_BK * 2);
+          for (int j = 0; j < N / TC_BOXN; ++j)
+            tma_load_2d(dst + j * (TC_BOXN * TC_BK * 2), &tmap, kb * TC_BK, row0 + j * TC_BOXN, full_b + 8 * s);
+        }
+      }
+      if (!alive) {
+        // copies already issued still land in this CTA's shared memory: give them time before exit
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issue ----------------
+    if (lane == 0) {
+      uint32_t it = 0, tix = 0;
+      bool alive = true;
+      for (int w = blockIdx.x; w < n_work && alive; w += gridDim.x, ++tix) {
+        const int item = w / n_ftiles;
+        const int nrows = p.item_nrows[item];
+        const int N = (nrows + TC_BOXN - 1) / TC_BOXN * TC_BOXN;
+        const uint32_t idesc = umma_idesc(N);
+        if (!mbar_wait(acc_empty, (tix & 1u) ^ 1u, abort_flag, p.status, TC_ERR_MMA_WAIT)) break;
+        tc_fence_after();
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+          if (!mbar_wait(full_a + 8 * s, ph, abort_flag, p.status, TC_ERR_MMA_WAIT) ||
+              !mbar_wait(full_b + 8 * s, ph, abort_flag, p.status, TC_ERR_MMA_WAIT)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a0 = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t b0 = a0 + MATS * TC_A_BYTES;
+#pragma unroll
+          for (int k4 = 0; k4 < TC_BK / 16; ++k4) {
+            const uint64_t bd = umma_smem_desc(b0 + k4 * 32);
+            const uint32_t acc = (kb | k4) ? 1u : 0u;
+            umma_bf16(tmem_base, umma_smem_desc(a0 + k4 * 32), bd, idesc, acc);
+            if (GATED) umma_bf16(tmem_base + TC_MAX_TOKENS, umma_smem_desc(a0 + TC_A_BYTES + k4 * 32), bd, idesc, acc);
+          }
+          umma_commit(empty + 8 * s);  // the stage may be refilled once these MMAs have read it
+        }
+        if (alive) umma_commit(acc_full);
+      }
+    }
+  } else if (warp < 2 + TC_EPI_WARPS) {
+    // ---------------- epilogue: TMEM -> registers -> global ----------------
+    const int lg = warp & 3;  // TMEM lane group this warp may read
+    uint32_t tix = 0;
+    for (int w = blockIdx.x; w < n_work; w += gridDim.x, ++tix) {
+      const int item = w / n_ftiles, ft = w % n_ftiles;
+      const int seg = p.item_seg[item], row0 = p.item_row0[item], nrows = p.item_nrows[item];
+      const int ex = p.seg_expert ? p.seg_expert[seg] : seg;
+      const int N = (nrows + TC_BOXN - 1) / TC_BOXN * TC_BOXN;
+      const float s0 = (GATED ? p.gate[ex].g : p.down[ex].g) * 65536.0f;
+      const float s1 = GATED ? p.up[ex].g * 65536.0f : 0.0f;
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait(acc_full, tix & 1u, abort_flag, p.status, TC_ERR_EPI_WAIT);
+      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+      if (!ok) break;
+      tc_fence_after();
+      const int f = ft * TC_BM + lg * 32 + lane;
+      const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16);
+      __nv_bfloat16 *out = GATED ? p.h : p.y;
+      const int ld = Oout;
+      for (int c0 = 0; c0 < N; c0 += 16) {
+        uint32_t g[16], u[16];
+        tmem_ld16(tbase + c0, g);
+        if (GATED) tmem_ld16(tbase + TC_MAX_TOKENS + c0, u);
+        tmem_ld_wait();
+        if (f < Oout) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int col = c0 + j;
+            if (col < nrows) {
+              float v = __uint_as_float(g[j]) * s0;
+              if (GATED) {
+                const float uv = __uint_as_float(u[j]) * s1;
+                v = v / (1.0f + __expf(-v)) * uv;
+              }
+              out[(size_t)(row0 + col) * ld + f] = __float2bfloat16_rn(v);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty);
+    }
+  } else {
+    // ---------------- weight producers: HBM -> registers -> bf16 -> swizzled shared memory ----------------
+    const int pt = threadIdx.x - 32 * (2 + TC_EPI_WARPS);  // 0..255
+    const int row = pt >> 1, c = pt & 1;
+    uint32_t it = 0;
+    bool alive = true;
+    for (int w = blockIdx.x; w < n_work && alive; w += gridDim.x) {
+      const int item = w / n_ftiles, ft = w % n_ftiles;
+      const int seg = p.item_seg[item];
+      const int ex = p.seg_expert ? p.seg_expert[seg] : seg;
+      const WeightRef w0 = GATED ? p.gate[ex] : p.down[ex];
+      const WeightRef w1 = GATED ? p.up[ex] : w0;
+      const int grow = ft * TC_BM + row;
+      TcPacked cur0 = tc_load_packed(w0, Op, grow, 0, c), cur1, nxt0, nxt1;
+      if (GATED) cur1 = tc_load_packed(w1, Op, grow, 0, c);
+      for (int kb = 0; kb < KB; ++kb, ++it) {
+        if (kb + 1 < KB) {
+          nxt0 = tc_load_packed(w0, Op, grow, kb + 1, c);
+          if (GATED) nxt1 = tc_load_packed(w1, Op, grow, kb + 1, c);
+        }
+        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+        bool ok = true;
+        if (lane == 0) ok = mbar_wait(empty + 8 * s, ph ^ 1u, abort_flag, p.status, TC_ERR_PROD_WAIT);
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        if (!ok) {
+          alive = false;
+          break;
+        }
+        uint8_t *tile = smem + s * STAGE_BYTES;
+        tc_store_tile(tile, row, c, cur0, lut);
+        if (GATED) tc_store_tile(tile + TC_A_BYTES, row, c, cur1, lut);
+        fence_proxy_async_smem();  // make these generic-proxy stores visible to the tensor core
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_a + 8 * s);
+        cur0 = nxt0;
+        if (GATED) cur1 = nxt1;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+// ---- host side ----------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess || !ptr) {
+      coli_set_error("cuTensorMapEncodeTiled is not available from the driver");
+      return nullptr;
+    }
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// bf16 [rows, K] row-major; box = 64 k x 32 rows; 128-byte swizzle; out-of-range reads give zeros
+static bool make_rows_map(CUtensorMap *map, const void *base, int rows, int K) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (K % 8)) {
+    coli_set_error("tensor map: row buffer must be 16-byte aligned with K a multiple of 8 (K=%d)", K);
+    return false;
+  }
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)TC_BOXN};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    coli_set_error("cuTensorMapEncodeTiled failed with code %d (rows=%d K=%d)", (int)r, rows, K);
+    return false;
+  }
+  return true;
+}
+
+template <bool GATED>
+static int launch_tc(const TcParams &p, const void *rows_base, int rows_cap, int sm_count, cudaStream_t st) {
+  constexpr int MATS = GATED ? 2 : 1;
+  constexpr int STAGES = GATED ? 3 : 4;
+  const size_t smem = (size_t)STAGES * (MATS * TC_A_BYTES + TC_B_BYTES) + 1024 /*align*/ + 8 * (3 * STAGES + 2) + 16 + 1024 /*lut*/ + 64;
+  static bool attr_done = false;
+  if (!attr_done) {
+    if (!coli_cuda_check(cudaFuncSetAttribute(k_ffn_tc<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                         "tcgen05 kernel shared-memory attribute"))
+      return 0;
+    attr_done = true;
+  }
+  CUtensorMap map;
+  if (!make_rows_map(&map, rows_base, rows_cap, GATED ? p.H : p.I)) return 0;
+  const int n_ftiles = ((GATED ? p.I : p.H) + TC_BM - 1) / TC_BM;
+  const long max_work = (long)p.max_items * n_ftiles;
+  const int grid = (int)(max_work < sm_count ? max_work : sm_count);
+  if (grid <= 0) return 1;
+  k_ffn_tc<GATED><<<grid, TC_THREADS, smem, st>>>(map, p);
+  coli_count_launch(1);
+  return coli_cuda_check(cudaGetLastError(), "tcgen05 expert ffn launch") ? 1 : 0;
+}
+
+int launch_gate_up_tc(const TcParams &p, const void *x_rows, int rows_cap, int sm_count, cudaStream_t st) {
+  return launch_tc<true>(p, x_rows, rows_cap, sm_count, st);
+}
+int launch_down_tc(const TcParams &p, int rows_cap, int sm_count, cudaStream_t st) {
+  return launch_tc<false>(p, p.h, rows_cap, sm_count, st);
+}
+
+}  // namespace colib

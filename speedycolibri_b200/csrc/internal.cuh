@@ -96,7 +96,8 @@ struct PermuteParams {
   int32_t *item_nrows;         //                rows (<= rows_per_item)
   int32_t *n_items;            // [1]
   const __nv_bfloat16 *x;      // [T,H]  (null = do not materialise rows)
-  __nv_bfloat16 *xg;           // [T*k,H] gathered rows (null = skip)
+  __nv_bfloat16 *xg;           // [T*k (+T),H] gathered rows (null = skip)
+  int gather_shared;           // also copy the shared expert's T identity rows into xg
 };
 int launch_permute(const PermuteParams &p, cudaStream_t st);
 // Work list for rows that are already expert-contiguous (counts on the device).
@@ -121,6 +122,22 @@ struct FfnParams {
 int launch_gate_up_small(const FfnParams &p, cudaStream_t st);  // h = silu(gate x) * (up x)
 int launch_down_small(const FfnParams &p, cudaStream_t st);     // y = down h
 int launch_ffn_small(const FfnParams &p, cudaStream_t st);      // both
+
+// expert_tc.cu — tcgen05 path for prefill-sized segments (NVFP4)
+constexpr int TC_MAX_TOKENS = 256;  // token rows per tile = rows per work item on this path
+struct TcParams {
+  int H, I;
+  const WeightRef *gate, *up, *down;
+  const int32_t *seg_expert;
+  const int32_t *item_seg, *item_row0, *item_nrows, *n_items;
+  int max_items;
+  __nv_bfloat16 *h;  // [rows, I]
+  __nv_bfloat16 *y;  // [rows, H]
+  int *status;       // device word: 0, or the code of the first bounded wait that gave up
+};
+// x_rows: bf16 [rows_cap, H] expert-contiguous rows (row index = position in the work list)
+int launch_gate_up_tc(const TcParams &p, const void *x_rows, int rows_cap, int sm_count, cudaStream_t st);
+int launch_down_tc(const TcParams &p, int rows_cap, int sm_count, cudaStream_t st);
 
 // combine.cu
 struct CombineParams {

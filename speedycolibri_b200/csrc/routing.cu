@@ -372,7 +372,7 @@ __global__ void __launch_bounds__(256) k_permute(PermuteParams p) {
     pos = p.seg_off[p.E] + t;
   }
   if (lane == 0) p.row_token[pos] = t;
-  if (p.xg && warp < nrouted) {
+  if (p.xg && (warp < nrouted || p.gather_shared)) {
     const int vec = p.H / 8;
     const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (size_t)t * p.H);
     uint4 *dst = reinterpret_cast<uint4 *>(p.xg + (size_t)pos * p.H);

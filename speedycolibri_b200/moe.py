@@ -125,6 +125,10 @@ class MoeBlock:
                "coli_b200_moe_block_dev")
         return out
 
+    def check(self) -> None:
+        """Synchronise and raise if a kernel of this handle abandoned a bounded device-side wait."""
+        _check(_lib_().coli_b200_moe_check(self.handle), "coli_b200_moe_check")
+
     def last_routing(self, T: int):
         idx = np.empty((T, self.cfg.topk), np.int32)
         w = np.empty((T, self.cfg.topk), np.float32)

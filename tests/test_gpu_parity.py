@@ -135,6 +135,28 @@ def test_block_small_shapes(gpu_backend, orc, name, T):
     blk.close()
 
 
+@pytest.mark.parametrize("name,T", [("mid", 512), ("mid", 433), ("mid_ragged", 333), ("mid_ragged", 1000)])
+def test_block_prefill_segments_tcgen05(gpu_backend, orc, name, T):
+    """Segments of >= 48 rows take the tcgen05 path (TMA token tiles, TMEM accumulators): ragged
+    segment lengths, K and feature counts that are not multiples of the tile, > 256 rows per expert."""
+    shape = CONFIGS[name].with_tokens(T)
+    L, packed = host_layer(shape)
+    blk = make_block(shape, upload_layer(shape, packed))
+    x = synth.host_tokens(shape, T)
+    out, idx, w = blk.moe(x, want_routing=True)
+    blk.check()
+    want = L.moe_block(x)
+    assert np.array_equal(idx, want["idx"]) and np.array_equal(w.view(np.uint32), want["w"].view(np.uint32))
+    err = rel_l2(out, want["out"])
+    assert err <= 5e-3, err
+    # per-row agreement too: no row may be silently dropped or misplaced
+    a = synth.bf16_bits_to_f32(out).astype(np.float64)
+    b = synth.bf16_bits_to_f32(want["out"]).astype(np.float64)
+    row_err = np.linalg.norm(a - b, axis=1) / np.maximum(np.linalg.norm(b, axis=1), 1e-30)
+    assert row_err.max() <= 2e-2, (int(row_err.argmax()), float(row_err.max()))
+    blk.close()
+
+
 def test_block_empty_and_bounds(gpu_backend, orc):
     from speedycolibri_b200.backend import CudaError
 
