@@ -67,6 +67,11 @@ CONFIGS = {
                    note="large expert-parallel layer, sigmoid group-limited routing, NVFP4"),
     "c4": MoeShape("c4", H=6144, E=384, k=8, I=2048, T=16384, shared=False, zipf_s=1.2,
                    note="skewed load, softmax top-8 + Zipf(1.2) logit bias, NVFP4, no shared expert"),
+    # c3 with 32 experts and 512 tokens: same matrices and rows/expert, 0.8 GB of weights — the
+    # small case that ncu captures are taken on
+    "c3s": MoeShape("c3s", H=7168, E=32, k=8, I=2048, T=512, score=SCORE_SIGMOID, norm_topk=True,
+                    routed_scale=2.5, n_group=8, topk_group=4, select_bias_std=0.01,
+                    note="c3 shapes at 1/8 of the experts and tokens (profiling case)"),
     # small shapes for tests
     "tiny": MoeShape("tiny", H=64, E=8, k=2, I=32, T=5, norm_topk=True),
     "tiny_sig": MoeShape("tiny_sig", H=128, E=16, k=4, I=64, T=37, score=SCORE_SIGMOID, norm_topk=True,

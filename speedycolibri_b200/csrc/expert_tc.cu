@@ -25,6 +25,9 @@
 // (backend_cuda.cu:3785-3787).
 #include <cuda.h>
 
+#include <cstdio>
+#include <cstdlib>
+
 #include "internal.cuh"
 
 namespace colib {
@@ -32,9 +35,14 @@ namespace colib {
 constexpr int TC_BM = 128;   // features per tile (UMMA M)
 constexpr int TC_BK = 64;    // k per pipeline stage: one 128-byte swizzle row of bf16
 constexpr int TC_BOXN = 32;  // token rows per TMA box
-constexpr int TC_PROD_WARPS = 8;
 constexpr int TC_EPI_WARPS = 4;
-constexpr int TC_THREADS = 32 * (2 + TC_EPI_WARPS + TC_PROD_WARPS);  // 448
+// weight-producer warps: every thread decodes one 16-byte chunk (32 weights) of one matrix per
+// stage; 256 threads cover a 128-row tile, so the gated kernel runs 16 producer warps, the down kernel 8
+template <bool GATED>
+struct TcCfg {
+  static constexpr int PROD_WARPS = GATED ? 16 : 8;
+  static constexpr int THREADS = 32 * (2 + TC_EPI_WARPS + PROD_WARPS);
+};
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;                        // 16 KiB
 constexpr int TC_B_BYTES = TC_MAX_TOKENS * TC_BK * 2;                // 32 KiB
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
@@ -61,10 +69,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait.  Returns false when the barrier did not flip in time or another role gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
+// `sleep_ns` > 0 backs off between polls (for waits that normally last a whole main loop), so
+// that a waiting role does not take issue slots from the producer warps.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code,
+                                          uint32_t sleep_ns = 0) {
   for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+    // waits on the critical path of the stage ring poll without suspending; long waits suspend
+    if (sleep_ns ? mbar_try_wait(bar, parity) : mbar_test_wait(bar, parity)) return true;
+    if (sleep_ns && i >= 8) __nanosleep(sleep_ns);
     if ((i & 63u) == 63u && *abort_flag) return false;
   }
   *abort_flag = 1;
@@ -133,18 +155,34 @@ struct TcPacked {
   uint4 q;      // 32 weights of one row
   uint32_t sc;  // their two block-scale bytes
 };
-__device__ __forceinline__ TcPacked tc_load_packed(const WeightRef &w, int Op, int row, int kb, int c) {
-  TcPacked r;
-  r.q = make_uint4(0, 0, 0, 0);
-  r.sc = 0;
+// What one producer thread needs of one k-tile (128 k) of one row: its 16-byte chunk of each
+// 64-k half and the row's eight block-scale bytes.
+struct TcPackedKT {
+  uint4 q0, q1;
+  uint2 sc;
+};
+__device__ __forceinline__ TcPackedKT tc_load_kt(const WeightRef &w, int Op, int row, int kt, int c) {
+  TcPackedKT r;
+  r.q0 = make_uint4(0, 0, 0, 0);
+  r.q1 = make_uint4(0, 0, 0, 0);
+  r.sc = make_uint2(0, 0);
   if (row < Op) {
-    const size_t base = (size_t)(kb >> 1) * Op + row;
-    const int half = kb & 1;
+    const size_t base = (size_t)kt * Op + row;
+    const uint8_t *qp = w.q + base * 64 + c * 16;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r.q.x), "=r"(r.q.y), "=r"(r.q.z), "=r"(r.q.w)
-                 : "l"(w.q + base * 64 + half * 32 + c * 16));
-    r.sc = *reinterpret_cast<const uint16_t *>(w.s + base * 8 + half * 4 + c * 2);
+                 : "=r"(r.q0.x), "=r"(r.q0.y), "=r"(r.q0.z), "=r"(r.q0.w)
+                 : "l"(qp));
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.q1.x), "=r"(r.q1.y), "=r"(r.q1.z), "=r"(r.q1.w)
+                 : "l"(qp + 32));
+    asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(r.sc.x), "=r"(r.sc.y) : "l"(w.s + base * 8));
   }
+  return r;
+}
+__device__ __forceinline__ TcPacked tc_half(const TcPackedKT &t, int half, int c) {
+  TcPacked r;
+  r.q = half ? t.q1 : t.q0;
+  r.sc = ((half ? t.sc.y : t.sc.x) >> (16 * c)) & 0xffffu;
   return r;
 }
 // Decode 32 weights and store them as chunks 4c..4c+3 of row `row` of a swizzled 128x64 tile.
@@ -159,10 +197,12 @@ __device__ __forceinline__ void tc_store_tile(uint8_t *tile, int row, int c, con
 }
 
 template <bool GATED>
-__global__ void __launch_bounds__(TC_THREADS, 1) k_ffn_tc(const __grid_constant__ CUtensorMap tmap, TcParams p) {
+__global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __grid_constant__ CUtensorMap tmap, TcParams p) {
   constexpr int MATS = GATED ? 2 : 1;
   constexpr int STAGES = GATED ? 3 : 4;
   constexpr int STAGE_BYTES = MATS * TC_A_BYTES + TC_B_BYTES;
+  constexpr int TC_PROD_WARPS = TcCfg<GATED>::PROD_WARPS;
+  constexpr int TC_THREADS = TcCfg<GATED>::THREADS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
@@ -170,6 +210,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_ffn_tc(const __grid_constant_
   const uint32_t acc_full = smem_u32(bars + 3 * STAGES), acc_empty = smem_u32(bars + 3 * STAGES + 1);
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * STAGES + 2);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  volatile int *prod_ok = reinterpret_cast<volatile int *>(tmem_slot + 2);
   uint32_t *lut = tmem_slot + 4;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -215,11 +256,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_ffn_tc(const __grid_constant_
         const int N = (nrows + TC_BOXN - 1) / TC_BOXN * TC_BOXN;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-          if (!mbar_wait(empty + 8 * s, ph ^ 1u, abort_flag, p.status, TC_ERR_TMA_WAIT)) {
+          if (!mbar_wait(empty + 8 * s, ph ^ 1u, abort_flag, p.status, TC_ERR_TMA_WAIT, 64)) {
             alive = false;
             break;
           }
           const uint32_t dst = smem_u32(smem + s * STAGE_BYTES + MATS * TC_A_BYTES);
+          if (p.debug_skip & 2) {
+            mbar_arrive(full_b + 8 * s);
+            continue;
+          }
           mbar_expect_tx(full_b + 8 * s, (uint32_t)N * TC_BK * 2);
           for (int j = 0; j < N / TC_BOXN; ++j)
             tma_load_2d(dst + j * (TC_BOXN * TC_BK * 2), &tmap, kb * TC_BK, row0 + j * TC_BOXN, full_b + 8 * s);
@@ -242,26 +287,35 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_ffn_tc(const __grid_constant_
         const uint32_t idesc = umma_idesc(N);
         if (!mbar_wait(acc_empty, (tix & 1u) ^ 1u, abort_flag, p.status, TC_ERR_MMA_WAIT)) break;
         tc_fence_after();
+        if (p.trace && blockIdx.x == 0 && tix < 8) p.trace[960 + tix * 4 + 0] = clock64();
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+          if (p.trace && blockIdx.x == 0 && it < 120) p.trace[it * 8 + 0] = clock64();
           if (!mbar_wait(full_a + 8 * s, ph, abort_flag, p.status, TC_ERR_MMA_WAIT) ||
               !mbar_wait(full_b + 8 * s, ph, abort_flag, p.status, TC_ERR_MMA_WAIT)) {
             alive = false;
             break;
           }
           tc_fence_after();
+          if (p.trace && blockIdx.x == 0 && it < 120) p.trace[it * 8 + 1] = clock64();
           const uint32_t a0 = smem_u32(smem + s * STAGE_BYTES);
           const uint32_t b0 = a0 + MATS * TC_A_BYTES;
 #pragma unroll
           for (int k4 = 0; k4 < TC_BK / 16; ++k4) {
+            if (p.debug_skip & 4) break;
             const uint64_t bd = umma_smem_desc(b0 + k4 * 32);
             const uint32_t acc = (kb | k4) ? 1u : 0u;
             umma_bf16(tmem_base, umma_smem_desc(a0 + k4 * 32), bd, idesc, acc);
             if (GATED) umma_bf16(tmem_base + TC_MAX_TOKENS, umma_smem_desc(a0 + TC_A_BYTES + k4 * 32), bd, idesc, acc);
           }
-          umma_commit(empty + 8 * s);  // the stage may be refilled once these MMAs have read it
+          if (p.debug_skip & 32)
+            mbar_arrive(empty + 8 * s);
+          else
+            umma_commit(empty + 8 * s);  // the stage may be refilled once these MMAs have read it
+          if (p.trace && blockIdx.x == 0 && it < 120) p.trace[it * 8 + 2] = clock64();
         }
         if (alive) umma_commit(acc_full);
+        if (p.trace && blockIdx.x == 0 && tix < 8) p.trace[960 + tix * 4 + 1] = clock64();
       }
     }
   } else if (warp < 2 + TC_EPI_WARPS) {
@@ -276,10 +330,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_ffn_tc(const __grid_constant_
       const float s0 = (GATED ? p.gate[ex].g : p.down[ex].g) * 65536.0f;
       const float s1 = GATED ? p.up[ex].g * 65536.0f : 0.0f;
       bool ok = true;
-      if (lane == 0) ok = mbar_wait(acc_full, tix & 1u, abort_flag, p.status, TC_ERR_EPI_WAIT);
+      if (lane == 0) ok = mbar_wait(acc_full, tix & 1u, abort_flag, p.status, TC_ERR_EPI_WAIT, 256);
       ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
       if (!ok) break;
       tc_fence_after();
+      if (p.trace && blockIdx.x == 0 && tix < 8 && warp == 2 && lane == 0) p.trace[960 + tix * 4 + 2] = clock64();
       const int f = ft * TC_BM + lg * 32 + lane;
       const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16);
       __nv_bfloat16 *out = GATED ? p.h : p.y;
@@ -306,44 +361,66 @@ __global__ void __launch_bounds__(TC_THREADS, 1) k_ffn_tc(const __grid_constant_
       }
       tc_fence_before();
       __syncwarp();
+      if (p.trace && blockIdx.x == 0 && tix < 8 && warp == 2 && lane == 0) p.trace[960 + tix * 4 + 3] = clock64();
       if (lane == 0) mbar_arrive(acc_empty);
     }
   } else {
     // ---------------- weight producers: HBM -> registers -> bf16 -> swizzled shared memory ----------------
-    const int pt = threadIdx.x - 32 * (2 + TC_EPI_WARPS);  // 0..255
-    const int row = pt >> 1, c = pt & 1;
+    // thread -> (matrix, row, 16-byte chunk): 256 threads cover one 128-row tile of one matrix
+    const int pt = threadIdx.x - 32 * (2 + TC_EPI_WARPS);
+    const int mtx = pt >> 8, row = (pt & 255) >> 1, c = pt & 1;
     uint32_t it = 0;
     bool alive = true;
     for (int w = blockIdx.x; w < n_work && alive; w += gridDim.x) {
       const int item = w / n_ftiles, ft = w % n_ftiles;
       const int seg = p.item_seg[item];
       const int ex = p.seg_expert ? p.seg_expert[seg] : seg;
-      const WeightRef w0 = GATED ? p.gate[ex] : p.down[ex];
-      const WeightRef w1 = GATED ? p.up[ex] : w0;
+      const WeightRef wr = GATED ? (mtx ? p.up[ex] : p.gate[ex]) : p.down[ex];
       const int grow = ft * TC_BM + row;
-      TcPacked cur0 = tc_load_packed(w0, Op, grow, 0, c), cur1, nxt0, nxt1;
-      if (GATED) cur1 = tc_load_packed(w1, Op, grow, 0, c);
-      for (int kb = 0; kb < KB; ++kb, ++it) {
-        if (kb + 1 < KB) {
-          nxt0 = tc_load_packed(w0, Op, grow, kb + 1, c);
-          if (GATED) nxt1 = tc_load_packed(w1, Op, grow, kb + 1, c);
+      const int KT = KB >> 1;
+      // Register ring of depth 4: while k-tile kt is decoded, the packed bytes of kt+1..kt+3 are
+      // in flight.  The loop is unrolled by the ring depth so that every slot is a fixed set of
+      // registers; rotating slots with moves would stall on the youngest load at every step.
+      TcPackedKT ring[4];
+#pragma unroll
+      for (int j = 0; j < 3; ++j) {
+        ring[j].q0 = make_uint4(0, 0, 0, 0);
+        ring[j].q1 = ring[j].q0;
+        ring[j].sc = make_uint2(0, 0);
+        if (j < KT && !(p.debug_skip & 8)) ring[j] = tc_load_kt(wr, Op, grow, j, c);
+      }
+      for (int kt0 = 0; kt0 < KT && alive; kt0 += 4) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int kt = kt0 + j;
+          if (kt >= KT || !alive) break;
+          if (kt + 3 < KT && !(p.debug_skip & 8)) ring[(j + 3) & 3] = tc_load_kt(wr, Op, grow, kt + 3, c);
+#pragma unroll
+          for (int half = 0; half < 2; ++half, ++it) {
+            const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+            bool ok = true;
+            if (p.trace && blockIdx.x == 0 && pt == 0 && it < 120) p.trace[it * 8 + 3] = clock64();
+            // One thread polls the mbarrier for all producer warps and releases them through a
+            // hardware named barrier: many warps polling one mbarrier word serialise in the
+            // shared-memory pipe and each poll then costs hundreds of cycles.
+            if (pt == 0) *prod_ok = mbar_wait(empty + 8 * s, ph ^ 1u, abort_flag, p.status, TC_ERR_PROD_WAIT) ? 1 : 0;
+            asm volatile("bar.sync 1, %0;" ::"r"(TC_PROD_WARPS * 32) : "memory");
+            ok = *prod_ok != 0;
+            if (!ok) {
+              alive = false;
+              break;
+            }
+            if (p.trace && blockIdx.x == 0 && pt == 0 && it < 120) p.trace[it * 8 + 4] = clock64();
+            if (!(p.debug_skip & 1))
+              tc_store_tile(smem + s * STAGE_BYTES + mtx * TC_A_BYTES, row, c, tc_half(ring[j], half, c), lut);
+            if (p.trace && blockIdx.x == 0 && pt == 0 && it < 120) p.trace[it * 8 + 5] = clock64();
+            if (!(p.debug_skip & 16)) fence_proxy_async_smem();  // make these generic-proxy stores visible to the tensor core
+            if (p.trace && blockIdx.x == 0 && pt == 0 && it < 120) p.trace[it * 8 + 6] = clock64();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full_a + 8 * s);
+            if (p.trace && blockIdx.x == 0 && pt == 0 && it < 120) p.trace[it * 8 + 7] = clock64();
+          }
         }
-        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-        bool ok = true;
-        if (lane == 0) ok = mbar_wait(empty + 8 * s, ph ^ 1u, abort_flag, p.status, TC_ERR_PROD_WAIT);
-        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-        if (!ok) {
-          alive = false;
-          break;
-        }
-        uint8_t *tile = smem + s * STAGE_BYTES;
-        tc_store_tile(tile, row, c, cur0, lut);
-        if (GATED) tc_store_tile(tile + TC_A_BYTES, row, c, cur1, lut);
-        fence_proxy_async_smem();  // make these generic-proxy stores visible to the tensor core
-        __syncwarp();
-        if (lane == 0) mbar_arrive(full_a + 8 * s);
-        cur0 = nxt0;
-        if (GATED) cur1 = nxt1;
       }
     }
   }
@@ -410,14 +487,46 @@ static int launch_tc(const TcParams &p, const void *rows_base, int rows_cap, int
       return 0;
     attr_done = true;
   }
+  TcParams pp = p;
+  {
+    static int dbg = -1;  // read once; a measurement aid, never set in production
+    if (dbg < 0) {
+      const char *e = getenv("COLI_TC_DEBUG_SKIP");
+      dbg = e ? atoi(e) : 0;
+    }
+    pp.debug_skip = dbg;
+  }
+  static long long *trace_buf = nullptr;
+  static int trace_on = -1;
+  if (trace_on < 0) {
+    trace_on = getenv("COLI_TC_TRACE") ? 1 : 0;
+    if (trace_on) cudaMalloc((void **)&trace_buf, 1024 * sizeof(long long));
+  }
+  pp.trace = trace_on ? trace_buf : nullptr;
+  if (trace_on) cudaMemset(trace_buf, 0, 1024 * sizeof(long long));
   CUtensorMap map;
   if (!make_rows_map(&map, rows_base, rows_cap, GATED ? p.H : p.I)) return 0;
   const int n_ftiles = ((GATED ? p.I : p.H) + TC_BM - 1) / TC_BM;
   const long max_work = (long)p.max_items * n_ftiles;
   const int grid = (int)(max_work < sm_count ? max_work : sm_count);
   if (grid <= 0) return 1;
-  k_ffn_tc<GATED><<<grid, TC_THREADS, smem, st>>>(map, p);
+  k_ffn_tc<GATED><<<grid, TcCfg<GATED>::THREADS, smem, st>>>(map, pp);
   coli_count_launch(1);
+  if (trace_on) {
+    static int dumps = 0;
+    cudaStreamSynchronize(st);
+    if (dumps++ < 2) {
+      long long h[1024];
+      cudaMemcpy(h, trace_buf, sizeof(h), cudaMemcpyDeviceToHost);
+      fprintf(stderr, "[trace gated=%d] it: mma_wait mma_ready mma_commit | p0_wait p0_pass p0_stored p0_fenced p0_arrived\n", (int)GATED);
+      const long long t0 = h[4];
+      for (int i = 0; i < 5; ++i)
+        fprintf(stderr, "  tile %d: mma_start %8lld mma_end %8lld epi_start %8lld epi_end %8lld\n", i, h[960 + i * 4] - t0, h[961 + i * 4] - t0, h[962 + i * 4] - t0, h[963 + i * 4] - t0);
+      for (int i = 0; i < 40; ++i)
+        fprintf(stderr, "  %3d: %7lld %7lld %7lld | %7lld %7lld %7lld | %7lld %7lld\n", i, h[i * 8] - t0, h[i * 8 + 1] - t0, h[i * 8 + 2] - t0,
+                h[i * 8 + 3] - t0, h[i * 8 + 4] - t0, h[i * 8 + 5] - t0, h[i * 8 + 6] - t0, h[i * 8 + 7] - t0);
+    }
+  }
   return coli_cuda_check(cudaGetLastError(), "tcgen05 expert ffn launch") ? 1 : 0;
 }
 

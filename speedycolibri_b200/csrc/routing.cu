@@ -79,6 +79,81 @@ __global__ void __launch_bounds__(256) k_router_gemm(RouteParams p) {
     }
 }
 
+// Router GEMM, prefill shape: 128 tokens x 64 experts per CTA, 8 x 4 outputs per thread, k-chunks
+// of 32 staged with 16-byte loads and stored transposed as f32, so the inner loop is three
+// 128-bit shared loads per 32 FMAs.  Same arithmetic as above: each output is one thread's
+// k-ascending fmaf chain.  Needs H % 8 == 0.
+__global__ void __launch_bounds__(256) k_router_gemm_big(RouteParams p) {
+  constexpr int BM = 128, BN = 64, BK = 32, LDX = BM + 4, LDW = BN + 4;
+  __shared__ __align__(16) float xs[BK][LDX];
+  __shared__ __align__(16) float ws[BK][LDW];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // tx -> 4 experts, ty -> 8 tokens
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+  // staging assignment: x tile = 128 rows x 4 chunks of 8 k (2 per thread), w tile = 64 rows x 4 chunks
+  const int sr = threadIdx.x >> 2, sc = threadIdx.x & 3;
+  for (int k0 = 0; k0 < p.H; k0 += BK) {
+    uint4 xv[2], wv;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int m = m0 + sr + 64 * h, k = k0 + sc * 8;
+      xv[h] = make_uint4(0, 0, 0, 0);
+      if (m < p.T && k < p.H) xv[h] = *reinterpret_cast<const uint4 *>(p.x + (size_t)m * p.H + k);
+    }
+    {
+      const int n = n0 + sr, k = k0 + sc * 8;
+      wv = make_uint4(0, 0, 0, 0);
+      if (n < p.E && k < p.H) wv = *reinterpret_cast<const uint4 *>(p.router_w + (size_t)n * p.H + k);
+    }
+    __syncthreads();  // the previous chunk has been consumed
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t u[4] = {xv[h].x, xv[h].y, xv[h].z, xv[h].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        xs[sc * 8 + 2 * j][sr + 64 * h] = __uint_as_float(u[j] << 16);
+        xs[sc * 8 + 2 * j + 1][sr + 64 * h] = __uint_as_float(u[j] & 0xffff0000u);
+      }
+    }
+    {
+      const uint32_t u[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        ws[sc * 8 + 2 * j][sr] = __uint_as_float(u[j] << 16);
+        ws[sc * 8 + 2 * j + 1][sr] = __uint_as_float(u[j] & 0xffff0000u);
+      }
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int kk = 0; kk < BK; ++kk) {
+      const float4 a0 = *reinterpret_cast<const float4 *>(&xs[kk][ty * 8]);
+      const float4 a1 = *reinterpret_cast<const float4 *>(&xs[kk][ty * 8 + 4]);
+      const float4 b = *reinterpret_cast<const float4 *>(&ws[kk][tx * 4]);
+      const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float bb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = __fmaf_rn(a[i], bb[j], acc[i][j]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int m = m0 + ty * 8 + i, n = n0 + tx * 4 + j;
+      if (m < p.T && n < p.E) {
+        float v = acc[i][j];
+        if (p.logit_bias) v = __fadd_rn(v, p.logit_bias[n]);
+        p.logits[(size_t)m * p.E + n] = v;
+      }
+    }
+}
+
 // Decode shape (T <= 8): one thread per (token, expert) walking its own k chain; the block's 8
 // expert rows and all token rows are staged in shared memory as bf16 with coalesced 16-byte
 // loads first.  The chain of H dependent FMAs is the latency floor of bit-exact routing.
@@ -268,6 +343,10 @@ int launch_router(const RouteParams &p, cudaStream_t st) {
       attr_set = true;
     }
     k_router_decode<<<(p.E + 7) / 8, 64 * ((p.T * 8 + 63) / 64), dec_smem, st>>>(p);
+    coli_count_launch(1);
+  } else if ((size_t)p.T * p.E >= 64 * 64 * 64 && p.H % 8 == 0) {
+    dim3 grid((p.E + 63) / 64, (p.T + 127) / 128);
+    k_router_gemm_big<<<grid, 256, 0, st>>>(p);
     coli_count_launch(1);
   } else if ((size_t)p.T * p.E >= 64 * 64 * 64) {
     dim3 grid((p.E + 63) / 64, (p.T + 63) / 64);
