@@ -25,9 +25,6 @@
 // (backend_cuda.cu:3785-3787).
 #include <cuda.h>
 
-#include <cstdio>
-#include <cstdlib>
-
 #include "internal.cuh"
 
 namespace colib {
@@ -40,7 +37,7 @@ constexpr int TC_EPI_WARPS = 4;
 // stage; 256 threads cover a 128-row tile, so the gated kernel runs 16 producer warps, the down kernel 8
 template <bool GATED>
 struct TcCfg {
-  static constexpr int PROD_WARPS = GATED ? 16 : 8;
+  static constexpr int PROD_WARPS = 16;
   static constexpr int THREADS = 32 * (2 + TC_EPI_WARPS + PROD_WARPS);
 };
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;                        // 16 KiB
@@ -198,8 +195,8 @@ __device__ __forceinline__ void tc_store_tile(uint8_t *tile, int row, int c, con
 
 template <bool GATED>
 __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __grid_constant__ CUtensorMap tmap, TcParams p) {
-  constexpr int MATS = GATED ? 2 : 1;
-  constexpr int STAGES = GATED ? 3 : 4;
+  constexpr int MATS = 2;    // gate + up of the same 128 features, or two adjacent 128-feature tiles of down
+  constexpr int STAGES = 3;
   constexpr int STAGE_BYTES = MATS * TC_A_BYTES + TC_B_BYTES;
   constexpr int TC_PROD_WARPS = TcCfg<GATED>::PROD_WARPS;
   constexpr int TC_THREADS = TcCfg<GATED>::THREADS;
@@ -217,7 +214,8 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
   const int K = GATED ? p.H : p.I, Oout = GATED ? p.I : p.H;
   const int Op = (Oout + 15) & ~15;
   const int KB = ((K + 127) >> 7) * 2;  // 64-wide k blocks, covering the zero-padded k tiles
-  const int n_ftiles = (Oout + TC_BM - 1) / TC_BM;
+  const int FT = GATED ? TC_BM : 2 * TC_BM;  // output features per tile
+  const int n_ftiles = (Oout + FT - 1) / FT;
   const int n_work = *p.n_items * n_ftiles;
 
   if (threadIdx.x == 0) {
@@ -261,10 +259,6 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
             break;
           }
           const uint32_t dst = smem_u32(smem + s * STAGE_BYTES + MATS * TC_A_BYTES);
-          if (p.debug_skip & 2) {
-            mbar_arrive(full_b + 8 * s);
-            continue;
-          }
           mbar_expect_tx(full_b + 8 * s, (uint32_t)N * TC_BK * 2);
           for (int j = 0; j < N / TC_BOXN; ++j)
             tma_load_2d(dst + j * (TC_BOXN * TC_BK * 2), &tmap, kb * TC_BK, row0 + j * TC_BOXN, full_b + 8 * s);
@@ -287,35 +281,26 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
         const uint32_t idesc = umma_idesc(N);
         if (!mbar_wait(acc_empty, (tix & 1u) ^ 1u, abort_flag, p.status, TC_ERR_MMA_WAIT)) break;
         tc_fence_after();
-        if (p.trace && blockIdx.x == 0 && tix < 8) p.trace[960 + tix * 4 + 0] = clock64();
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-          if (p.trace && blockIdx.x == 0 && it < 120) p.trace[it * 8 + 0] = clock64();
           if (!mbar_wait(full_a + 8 * s, ph, abort_flag, p.status, TC_ERR_MMA_WAIT) ||
               !mbar_wait(full_b + 8 * s, ph, abort_flag, p.status, TC_ERR_MMA_WAIT)) {
             alive = false;
             break;
           }
           tc_fence_after();
-          if (p.trace && blockIdx.x == 0 && it < 120) p.trace[it * 8 + 1] = clock64();
           const uint32_t a0 = smem_u32(smem + s * STAGE_BYTES);
           const uint32_t b0 = a0 + MATS * TC_A_BYTES;
 #pragma unroll
           for (int k4 = 0; k4 < TC_BK / 16; ++k4) {
-            if (p.debug_skip & 4) break;
             const uint64_t bd = umma_smem_desc(b0 + k4 * 32);
             const uint32_t acc = (kb | k4) ? 1u : 0u;
             umma_bf16(tmem_base, umma_smem_desc(a0 + k4 * 32), bd, idesc, acc);
-            if (GATED) umma_bf16(tmem_base + TC_MAX_TOKENS, umma_smem_desc(a0 + TC_A_BYTES + k4 * 32), bd, idesc, acc);
+            umma_bf16(tmem_base + TC_MAX_TOKENS, umma_smem_desc(a0 + TC_A_BYTES + k4 * 32), bd, idesc, acc);
           }
-          if (p.debug_skip & 32)
-            mbar_arrive(empty + 8 * s);
-          else
-            umma_commit(empty + 8 * s);  // the stage may be refilled once these MMAs have read it
-          if (p.trace && blockIdx.x == 0 && it < 120) p.trace[it * 8 + 2] = clock64();
+          umma_commit(empty + 8 * s);  // the stage may be refilled once these MMAs have read it
         }
         if (alive) umma_commit(acc_full);
-        if (p.trace && blockIdx.x == 0 && tix < 8) p.trace[960 + tix * 4 + 1] = clock64();
       }
     }
   } else if (warp < 2 + TC_EPI_WARPS) {
@@ -328,40 +313,37 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
       const int ex = p.seg_expert ? p.seg_expert[seg] : seg;
       const int N = (nrows + TC_BOXN - 1) / TC_BOXN * TC_BOXN;
       const float s0 = (GATED ? p.gate[ex].g : p.down[ex].g) * 65536.0f;
-      const float s1 = GATED ? p.up[ex].g * 65536.0f : 0.0f;
+      const float s1 = (GATED ? p.up[ex].g : p.down[ex].g) * 65536.0f;
       bool ok = true;
       if (lane == 0) ok = mbar_wait(acc_full, tix & 1u, abort_flag, p.status, TC_ERR_EPI_WAIT, 256);
       ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
       if (!ok) break;
       tc_fence_after();
-      if (p.trace && blockIdx.x == 0 && tix < 8 && warp == 2 && lane == 0) p.trace[960 + tix * 4 + 2] = clock64();
-      const int f = ft * TC_BM + lg * 32 + lane;
+      const int f = ft * FT + lg * 32 + lane;  // accumulator 0; accumulator 1 is feature f + 128 of down
       const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16);
-      __nv_bfloat16 *out = GATED ? p.h : p.y;
-      const int ld = Oout;
+      __nv_bfloat16 *out = (GATED ? p.h : p.y) + (size_t)row0 * Oout + f;
       for (int c0 = 0; c0 < N; c0 += 16) {
         uint32_t g[16], u[16];
         tmem_ld16(tbase + c0, g);
-        if (GATED) tmem_ld16(tbase + TC_MAX_TOKENS + c0, u);
+        tmem_ld16(tbase + TC_MAX_TOKENS + c0, u);
         tmem_ld_wait();
-        if (f < Oout) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int col = c0 + j;
-            if (col < nrows) {
-              float v = __uint_as_float(g[j]) * s0;
-              if (GATED) {
-                const float uv = __uint_as_float(u[j]) * s1;
-                v = v / (1.0f + __expf(-v)) * uv;
-              }
-              out[(size_t)(row0 + col) * ld + f] = __float2bfloat16_rn(v);
+        for (int j = 0; j < 16; ++j) {
+          const int col = c0 + j;
+          if (col < nrows) {
+            const float v0 = __uint_as_float(g[j]) * s0, v1 = __uint_as_float(u[j]) * s1;
+            __nv_bfloat16 *dst = out + (size_t)col * Oout;
+            if (GATED) {
+              if (f < Oout) *dst = __float2bfloat16_rn(__fdividef(v0, 1.0f + __expf(-v0)) * v1);
+            } else {
+              if (f < Oout) *dst = __float2bfloat16_rn(v0);
+              if (f + TC_BM < Oout) dst[TC_BM] = __float2bfloat16_rn(v1);
             }
           }
         }
       }
       tc_fence_before();
       __syncwarp();
-      if (p.trace && blockIdx.x == 0 && tix < 8 && warp == 2 && lane == 0) p.trace[960 + tix * 4 + 3] = clock64();
       if (lane == 0) mbar_arrive(acc_empty);
     }
   } else {
@@ -376,7 +358,7 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
       const int seg = p.item_seg[item];
       const int ex = p.seg_expert ? p.seg_expert[seg] : seg;
       const WeightRef wr = GATED ? (mtx ? p.up[ex] : p.gate[ex]) : p.down[ex];
-      const int grow = ft * TC_BM + row;
+      const int grow = GATED ? ft * TC_BM + row : ft * FT + mtx * TC_BM + row;
       const int KT = KB >> 1;
       // Register ring of depth 4: while k-tile kt is decoded, the packed bytes of kt+1..kt+3 are
       // in flight.  The loop is unrolled by the ring depth so that every slot is a fixed set of
@@ -387,19 +369,18 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
         ring[j].q0 = make_uint4(0, 0, 0, 0);
         ring[j].q1 = ring[j].q0;
         ring[j].sc = make_uint2(0, 0);
-        if (j < KT && !(p.debug_skip & 8)) ring[j] = tc_load_kt(wr, Op, grow, j, c);
+        if (j < KT) ring[j] = tc_load_kt(wr, Op, grow, j, c);
       }
       for (int kt0 = 0; kt0 < KT && alive; kt0 += 4) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int kt = kt0 + j;
           if (kt >= KT || !alive) break;
-          if (kt + 3 < KT && !(p.debug_skip & 8)) ring[(j + 3) & 3] = tc_load_kt(wr, Op, grow, kt + 3, c);
+          if (kt + 3 < KT) ring[(j + 3) & 3] = tc_load_kt(wr, Op, grow, kt + 3, c);
 #pragma unroll
           for (int half = 0; half < 2; ++half, ++it) {
             const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
             bool ok = true;
-            if (p.trace && blockIdx.x == 0 && pt == 0 && it < 120) p.trace[it * 8 + 3] = clock64();
             // One thread polls the mbarrier for all producer warps and releases them through a
             // hardware named barrier: many warps polling one mbarrier word serialise in the
             // shared-memory pipe and each poll then costs hundreds of cycles.
@@ -410,15 +391,10 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
               alive = false;
               break;
             }
-            if (p.trace && blockIdx.x == 0 && pt == 0 && it < 120) p.trace[it * 8 + 4] = clock64();
-            if (!(p.debug_skip & 1))
-              tc_store_tile(smem + s * STAGE_BYTES + mtx * TC_A_BYTES, row, c, tc_half(ring[j], half, c), lut);
-            if (p.trace && blockIdx.x == 0 && pt == 0 && it < 120) p.trace[it * 8 + 5] = clock64();
-            if (!(p.debug_skip & 16)) fence_proxy_async_smem();  // make these generic-proxy stores visible to the tensor core
-            if (p.trace && blockIdx.x == 0 && pt == 0 && it < 120) p.trace[it * 8 + 6] = clock64();
+            tc_store_tile(smem + s * STAGE_BYTES + mtx * TC_A_BYTES, row, c, tc_half(ring[j], half, c), lut);
+            fence_proxy_async_smem();  // make these generic-proxy stores visible to the tensor core
             __syncwarp();
             if (lane == 0) mbar_arrive(full_a + 8 * s);
-            if (p.trace && blockIdx.x == 0 && pt == 0 && it < 120) p.trace[it * 8 + 7] = clock64();
           }
         }
       }
@@ -477,8 +453,8 @@ static bool make_rows_map(CUtensorMap *map, const void *base, int rows, int K) {
 
 template <bool GATED>
 static int launch_tc(const TcParams &p, const void *rows_base, int rows_cap, int sm_count, cudaStream_t st) {
-  constexpr int MATS = GATED ? 2 : 1;
-  constexpr int STAGES = GATED ? 3 : 4;
+  constexpr int MATS = 2;
+  constexpr int STAGES = 3;
   const size_t smem = (size_t)STAGES * (MATS * TC_A_BYTES + TC_B_BYTES) + 1024 /*align*/ + 8 * (3 * STAGES + 2) + 16 + 1024 /*lut*/ + 64;
   static bool attr_done = false;
   if (!attr_done) {
@@ -487,46 +463,15 @@ static int launch_tc(const TcParams &p, const void *rows_base, int rows_cap, int
       return 0;
     attr_done = true;
   }
-  TcParams pp = p;
-  {
-    static int dbg = -1;  // read once; a measurement aid, never set in production
-    if (dbg < 0) {
-      const char *e = getenv("COLI_TC_DEBUG_SKIP");
-      dbg = e ? atoi(e) : 0;
-    }
-    pp.debug_skip = dbg;
-  }
-  static long long *trace_buf = nullptr;
-  static int trace_on = -1;
-  if (trace_on < 0) {
-    trace_on = getenv("COLI_TC_TRACE") ? 1 : 0;
-    if (trace_on) cudaMalloc((void **)&trace_buf, 1024 * sizeof(long long));
-  }
-  pp.trace = trace_on ? trace_buf : nullptr;
-  if (trace_on) cudaMemset(trace_buf, 0, 1024 * sizeof(long long));
   CUtensorMap map;
   if (!make_rows_map(&map, rows_base, rows_cap, GATED ? p.H : p.I)) return 0;
-  const int n_ftiles = ((GATED ? p.I : p.H) + TC_BM - 1) / TC_BM;
+  const int FT = GATED ? TC_BM : 2 * TC_BM;
+  const int n_ftiles = ((GATED ? p.I : p.H) + FT - 1) / FT;
   const long max_work = (long)p.max_items * n_ftiles;
   const int grid = (int)(max_work < sm_count ? max_work : sm_count);
   if (grid <= 0) return 1;
-  k_ffn_tc<GATED><<<grid, TcCfg<GATED>::THREADS, smem, st>>>(map, pp);
+  k_ffn_tc<GATED><<<grid, TcCfg<GATED>::THREADS, smem, st>>>(map, p);
   coli_count_launch(1);
-  if (trace_on) {
-    static int dumps = 0;
-    cudaStreamSynchronize(st);
-    if (dumps++ < 2) {
-      long long h[1024];
-      cudaMemcpy(h, trace_buf, sizeof(h), cudaMemcpyDeviceToHost);
-      fprintf(stderr, "[trace gated=%d] it: mma_wait mma_ready mma_commit | p0_wait p0_pass p0_stored p0_fenced p0_arrived\n", (int)GATED);
-      const long long t0 = h[4];
-      for (int i = 0; i < 5; ++i)
-        fprintf(stderr, "  tile %d: mma_start %8lld mma_end %8lld epi_start %8lld epi_end %8lld\n", i, h[960 + i * 4] - t0, h[961 + i * 4] - t0, h[962 + i * 4] - t0, h[963 + i * 4] - t0);
-      for (int i = 0; i < 40; ++i)
-        fprintf(stderr, "  %3d: %7lld %7lld %7lld | %7lld %7lld %7lld | %7lld %7lld\n", i, h[i * 8] - t0, h[i * 8 + 1] - t0, h[i * 8 + 2] - t0,
-                h[i * 8 + 3] - t0, h[i * 8 + 4] - t0, h[i * 8 + 5] - t0, h[i * 8 + 6] - t0, h[i * 8 + 7] - t0);
-    }
-  }
   return coli_cuda_check(cudaGetLastError(), "tcgen05 expert ffn launch") ? 1 : 0;
 }
 

@@ -134,8 +134,6 @@ struct TcParams {
   __nv_bfloat16 *h;  // [rows, I]
   __nv_bfloat16 *y;  // [rows, H]
   int *status;       // device word: 0, or the code of the first bounded wait that gave up
-  long long *trace;  // measurement aid (COLI_TC_TRACE): CTA 0 logs clock64 stamps of its first stages
-  int debug_skip;    // measurement aid (COLI_TC_DEBUG_SKIP): 1 no weight decode, 2 no token copies, 4 no MMA; results invalid
 };
 // x_rows: bf16 [rows_cap, H] expert-contiguous rows (row index = position in the work list)
 int launch_gate_up_tc(const TcParams &p, const void *x_rows, int rows_cap, int sm_count, cudaStream_t st);
