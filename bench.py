@@ -4,7 +4,8 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3] [--impl ours|reference]
 
 N = 1 runs the whole block on one B200; N > 1 (launched by torch.distributed.run, one rank per
-GPU) shards the experts across ranks (expert parallelism, NCCL all-to-all) and the tokens with
+GPU) shards the experts across ranks (expert parallelism: NCCL all-gather of tokens, reduce-scatter of
+partial sums) and the tokens with
 them, so the total work is fixed as N grows ("strong" scaling).  Rank 0 prints ONE JSON line.
 
 `--impl reference` times the CPU restatement of the reference's own MoE block (oracle/, the Rust
@@ -229,7 +230,7 @@ def run_ours(args):
         sharding = ExpertSharding.new(world, shape.E)
         verify_peers(sharding)
         layer = synth.device_layer(shape, device=local, local_experts=sharding.local_experts(rank))
-        blk = MoeBlock(cfg, layer, Tl, device=local, ep_rank=rank, ep_world=world)
+        blk = MoeBlock(cfg, layer, shape.T, device=local, ep_rank=rank, ep_world=world)
         step = lambda: moe_sharded(blk, sharding, x)
 
     def barrier():

@@ -163,24 +163,39 @@ int coli_b200_moe_check(ColiMoe *moe);
 /* Copy the last call's routing to HOST (after synchronising the stream). */
 int coli_b200_moe_last_routing(ColiMoe *moe, int T, int32_t *topk_idx, float *topk_w);
 
-/* ---- stages, DEVICE pointers, asynchronous (what the expert-parallel path is built from) --- */
-/* Router GEMM + score + top-k for x_dev[T,H]; then rows are ordered by (owner rank, expert id)
- * and gathered into rows_dev[T*k, H] (bf16).  seg_count_dev[E] receives rows per expert in that
- * order, slot_dev[T*k] the row each (token, kk) pair went to.  Routing stays in the handle for
- * the combine stage. */
-int coli_b200_moe_route_dev(ColiMoe *moe, const void *x_dev, int T, void *rows_dev, int32_t *seg_count_dev,
-                            int32_t *slot_dev, void *stream);
-/* Grouped SwiGLU FFN over expert-contiguous rows: segment j (j < n_seg) holds seg_count_dev[j]
- * rows and uses resident expert first_expert + j in owner order.  rows_dev, y_dev: bf16
- * [n_rows, H].  The device-pointer form of coli_cuda_expert_group_nvfp4. */
-int coli_b200_moe_experts_dev(ColiMoe *moe, const void *rows_dev, const int32_t *seg_count_dev, int first_seg,
-                              int n_seg, int n_rows, void *y_dev, void *stream);
+/* ---- stages, DEVICE pointers, asynchronous (what the expert-parallel path is built from; they
+ * replace crates/colibri-engine/src/moe.rs:1620-1734 `sharded_experts_partial`).  The sequence on
+ * every rank is: topk (own tokens) -> all-gather of tokens and routing -> gather_local -> experts
+ * -> combine_partial -> reduce-scatter of the partials -> finish (+ shared expert of the own
+ * tokens).  All sizes exchanged between ranks follow from (T, H, k) alone, so no host
+ * synchronisation is needed anywhere.  A handle used this way is created with max_tokens = the
+ * token count of ALL ranks. ------------------------------------------------------------------ */
+/* Number of routed experts resident on this rank (= segments of gather_local / experts). */
+int coli_b200_moe_local_experts(const ColiMoe *moe);
+/* Router GEMM + score + top-k for x_dev[T,H] -> topk_idx_dev [T,k] int32, topk_w_dev [T,k] f32. */
+int coli_b200_moe_topk_dev(ColiMoe *moe, const void *x_dev, int T, int32_t *topk_idx_dev, float *topk_w_dev,
+                           void *stream);
+/* For routing topk_idx_dev[T,k] over x_dev[T,H]: copy the rows of the (token, kk) pairs whose
+ * expert is resident here into rows_dev (bf16, capacity T*k rows), expert-contiguous in ascending
+ * expert id, tokens ascending inside an expert (moe.rs:1373-1387).  seg_count_dev[n_local]
+ * receives the rows per resident expert, slot_dev[T*k] the row of each pair or -1. */
+int coli_b200_moe_gather_local_dev(ColiMoe *moe, const void *x_dev, const int32_t *topk_idx_dev, int T, void *rows_dev,
+                                   int32_t *seg_count_dev, int32_t *slot_dev, void *stream);
+/* Grouped SwiGLU FFN of the resident experts over those rows -> y_dev (bf16 [rows, H]); the
+ * device-pointer form of coli_cuda_expert_group_nvfp4.  rows_cap = rows the two buffers hold;
+ * rows_expected (e.g. T*k/world) only selects the kernel family. */
+int coli_b200_moe_experts_dev(ColiMoe *moe, const void *rows_dev, const int32_t *seg_count_dev, int rows_cap,
+                              int rows_expected, void *y_dev, void *stream);
 /* Shared expert over x_dev[T,H] -> y_dev[T,H] (bf16). */
 int coli_b200_moe_shared_dev(ColiMoe *moe, const void *x_dev, int T, void *y_dev, void *stream);
-/* out[t] = sum_kk w[t,kk] * y_rows[slot[t,kk]]  (+ shared_y[t] if not NULL), kk ascending, f32,
- * rounded once to bf16 (moe.rs:1549-1553,1875-1885). */
-int coli_b200_moe_combine_dev(ColiMoe *moe, const void *y_rows_dev, const int32_t *slot_dev,
-                              const void *shared_y_dev, void *out_dev, int T, void *stream);
+/* partial[t] = sum over kk with slot >= 0 of w[t,kk] * y_rows[slot[t,kk]], kk ascending, f32 [T,H]
+ * (moe.rs:1549-1553 restricted to this rank's experts; ranks are summed by the reduce-scatter as
+ * moe.rs:1725-1733 folds peer partials). */
+int coli_b200_moe_combine_partial_dev(ColiMoe *moe, const void *y_rows_dev, const int32_t *slot_dev,
+                                      const float *topk_w_dev, float *partial_dev, int T, void *stream);
+/* out[t] = bf16(partial[t] + shared_y[t]) (shared_y_dev may be NULL) — moe.rs:1875-1885. */
+int coli_b200_moe_finish_dev(ColiMoe *moe, const float *partial_dev, const void *shared_y_dev, void *out_dev, int T,
+                             void *stream);
 
 /* ---- tracing (the role of the reference's COLI_PROFILE phase counters ROUTER_US, MOE_PREP_US,
  * GPUFFN_US, SCATTER_US, crates/colibri-engine/src/forward.rs:86-160) ------------------------ */

@@ -91,10 +91,13 @@ SIGNATURES = {
     "coli_b200_moe_block_dev": (_i, [_P, _P, _P, _i, _P]),
     "coli_b200_moe_check": (_i, [_P]),
     "coli_b200_moe_last_routing": (_i, [_P, _i, _P, _P]),
-    "coli_b200_moe_route_dev": (_i, [_P, _P, _i, _P, _P, _P, _P]),
-    "coli_b200_moe_experts_dev": (_i, [_P, _P, _P, _i, _i, _i, _P, _P]),
+    "coli_b200_moe_local_experts": (_i, [_P]),
+    "coli_b200_moe_topk_dev": (_i, [_P, _P, _i, _P, _P, _P]),
+    "coli_b200_moe_gather_local_dev": (_i, [_P, _P, _P, _i, _P, _P, _P, _P]),
+    "coli_b200_moe_experts_dev": (_i, [_P, _P, _P, _i, _i, _P, _P]),
     "coli_b200_moe_shared_dev": (_i, [_P, _P, _i, _P, _P]),
-    "coli_b200_moe_combine_dev": (_i, [_P, _P, _P, _P, _P, _i, _P]),
+    "coli_b200_moe_combine_partial_dev": (_i, [_P, _P, _P, _P, _P, _i, _P]),
+    "coli_b200_moe_finish_dev": (_i, [_P, _P, _P, _P, _i, _P]),
     "coli_b200_moe_profile": (_i, [_P, _i]),
     "coli_b200_moe_phase_ms": (_i, [_P, C.POINTER(_f), C.POINTER(_i)]),
     "coli_b200_moe_stream": (_P, [_P]),

@@ -6,8 +6,9 @@ What is kept from the reference: the expert -> rank map (contiguous ``e*N/E`` or
 LPT table), the FNV-1a fingerprint every rank compares before exchanging anything, "move
 activations to experts, never weights", and that a peer failure aborts the layer with an
 exception rather than returning zeros.  What changes: tokens are sharded across ranks (each
-rank routes its own T/world tokens) and only the rows a peer's experts need are sent, instead
-of rank 0 broadcasting every activation row to every peer."""
+rank routes its own T/world tokens), activations reach the peers through one NCCL all-gather
+and the partial sums return through one reduce-scatter, instead of rank 0 driving every peer
+with a request/response per layer."""
 from __future__ import annotations
 
 from typing import List, Optional, Sequence
@@ -139,88 +140,89 @@ def verify_peers(sharding: ExpertSharding, group=None) -> None:
             raise RuntimeError(f"sharding fingerprint mismatch: rank {r} disagrees with rank {dist.get_rank(group)} ({fp:#018x})")
 
 
-def exchange_plan(seg_count: np.ndarray, n_local: Sequence[int], recv_counts: np.ndarray, rank: int):
-    """Host-side bookkeeping of the dispatch all-to-all.
+class ShardedMoe:
+    """Expert-parallel block over the ranks of `group` (one process per GPU) — the role of
+    crates/colibri-engine/src/moe.rs:1737 `moe_sharded`.
 
-    seg_count  [E]            rows this rank routes to each expert, in (owner, id) order
-    n_local    [world]        experts owned by each rank
-    recv_counts [world, n_local[rank]]  rows each source rank sends for each of my experts
-    Returns (send_splits, recv_splits, perm, rows_per_local_expert): `perm` reorders the
-    received rows from [source][expert] order into expert-major order (all sources' rows of
-    my first expert, then of my second, ...), sources ascending inside an expert — the order
-    in which the reference folds peer partials (moe.rs:1725-1733)."""
-    world = len(n_local)
-    bounds = np.concatenate([[0], np.cumsum(n_local)])
-    send_splits = [int(seg_count[bounds[r]:bounds[r + 1]].sum()) for r in range(world)]
-    recv_splits = [int(recv_counts[r].sum()) for r in range(world)]
-    nl = int(n_local[rank])
-    c = recv_counts.reshape(world, nl).astype(np.int64)
-    src_off = np.concatenate([[0], np.cumsum(c.reshape(-1))])[:-1].reshape(world, nl)
-    total = int(c.sum())
-    perm = np.empty(total, np.int64)
-    pos = 0
-    for e in range(nl):
-        for s in range(world):
-            n = int(c[s, e])
-            perm[pos:pos + n] = src_off[s, e] + np.arange(n)
-            pos += n
-    return send_splits, recv_splits, perm, c.sum(axis=0).astype(np.int32)
+    Each rank holds T_local tokens and the experts `sharding` gives it.  Per call, on the current
+    stream, with no host synchronisation (every exchanged size follows from T, H, k):
+
+      1. router + top-k of the own tokens                          (block.topk_dev)
+      2. all-gather of tokens, indices, weights                    (NCCL)
+      3. rows of the (token, kk) pairs routed to resident experts  (block.gather_local_dev)
+      4. grouped expert FFN over those rows                        (block.experts_dev)
+      5. f32 partial sum per token over the resident experts       (block.combine_partial_dev)
+      6. reduce-scatter of the partials: every rank receives the sum for its own tokens (NCCL) —
+         the fold of peer partials of moe.rs:1725-1733
+      7. + shared expert of the own tokens, one rounding to bf16   (block.shared_dev, finish_dev)
+
+    Like the reference (moe.rs:1671-1678) every rank sees all activation rows and only weights
+    never move; unlike it, no rank drives the others.  `block` must be created with
+    max_tokens >= world * T_local.  Buffers are allocated once and reused by every call."""
+
+    def __init__(self, block, sharding: ExpertSharding, t_local: int, group=None):
+        import torch
+        import torch.distributed as dist
+
+        self.block, self.sharding, self.group, self.Tl = block, sharding, group, int(t_local)
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        assert self.world == sharding.num_nodes and self.rank == block.ep_rank
+        cfg = block.cfg
+        self.k, self.H = cfg.topk, cfg.hidden
+        T = self.T = self.world * self.Tl
+        assert block.max_tokens >= T, "create the block with max_tokens = tokens of all ranks"
+        assert block.local_experts() == sharding.count_for(self.rank)
+        self.gloo = dist.get_backend(group) == "gloo"
+        dev = "cpu" if self.gloo else torch.device("cuda", block.device)
+        bf, i32, f32 = torch.bfloat16, torch.int32, torch.float32
+        self.x_all = torch.empty((T, self.H), dtype=bf, device=dev)
+        self.idx = torch.empty((self.Tl, self.k), dtype=i32, device=dev)
+        self.w = torch.empty((self.Tl, self.k), dtype=f32, device=dev)
+        self.idx_all = torch.empty((T, self.k), dtype=i32, device=dev)
+        self.w_all = torch.empty((T, self.k), dtype=f32, device=dev)
+        self.rows = torch.empty((T * self.k, self.H), dtype=bf, device=dev)
+        self.y_rows = torch.empty((T * self.k, self.H), dtype=bf, device=dev)
+        self.seg_count = torch.zeros(max(1, block.local_experts()), dtype=i32, device=dev)
+        self.slot = torch.empty(T * self.k, dtype=i32, device=dev)
+        self.partial = torch.empty((T, self.H), dtype=f32, device=dev)
+        self.mine = torch.empty((self.Tl, self.H), dtype=f32, device=dev)
+        self.shared_y = torch.empty((self.Tl, self.H), dtype=bf, device=dev) if block.has_shared else None
+        self.rows_expected = max(1, T * self.k // self.world)
+
+    def _stream(self):
+        import torch
+
+        return 0 if self.gloo else torch.cuda.current_stream().cuda_stream
+
+    def __call__(self, x, out=None):
+        import torch
+        import torch.distributed as dist
+
+        assert x.shape == (self.Tl, self.H)
+        b, st = self.block, self._stream()
+        if out is None:
+            out = torch.empty_like(x)
+        b.topk_dev(x, self.idx, self.w, st)
+        if b.has_shared:  # replicated weights, own tokens; independent of the exchange
+            b.shared_dev(x, self.shared_y, st)
+        dist.all_gather_into_tensor(self.x_all, x, group=self.group)
+        dist.all_gather_into_tensor(self.idx_all, self.idx, group=self.group)
+        dist.all_gather_into_tensor(self.w_all, self.w, group=self.group)
+        b.gather_local_dev(self.x_all, self.idx_all, self.rows, self.seg_count, self.slot, st)
+        b.experts_dev(self.rows, self.seg_count, self.rows_expected, self.y_rows, st)
+        b.combine_partial_dev(self.y_rows, self.slot, self.w_all, self.partial, st)
+        if self.gloo:  # gloo has no reduce-scatter: all-reduce and keep the own slice
+            dist.all_reduce(self.partial, group=self.group)
+            self.mine.copy_(self.partial[self.rank * self.Tl:(self.rank + 1) * self.Tl])
+        else:
+            dist.reduce_scatter_tensor(self.mine, self.partial, group=self.group)
+        b.finish_dev(self.mine, self.shared_y, out, st)
+        return out
 
 
 def moe_sharded(block, sharding: ExpertSharding, x, group=None):
-    """Expert-parallel block over the ranks of `group` (one process per GPU).
-
-    `x` is this rank's token shard, torch bf16 CUDA [T_local, H]; returns this rank's
-    [T_local, H].  Steps: route + permute locally -> counts all-to-all -> rows all-to-all ->
-    local experts (grouped FFN) -> rows all-to-all back -> weighted combine + shared expert
-    at the home rank.  The two row exchanges are ncclSend/ncclRecv groups issued through
-    torch.distributed.all_to_all_single on the current stream."""
-    import torch
-    import torch.distributed as dist
-
-    world, rank = dist.get_world_size(group), dist.get_rank(group)
-    assert world == sharding.num_nodes and rank == block.ep_rank
-    cfg = block.cfg
-    E, k, H = cfg.n_experts, cfg.topk, cfg.hidden
-    T = x.shape[0]
-    dev = x.device
-    st = torch.cuda.current_stream(dev).cuda_stream
-    n_local = [sharding.count_for(r) for r in range(world)]
-    first_seg = sum(n_local[:rank])
-    nl = n_local[rank]
-
-    rows = torch.empty((T * k, H), dtype=torch.bfloat16, device=dev)
-    seg_count = torch.empty(E, dtype=torch.int32, device=dev)
-    slot = torch.empty(max(T * k, 1), dtype=torch.int32, device=dev)
-    block.route_dev(x, rows, seg_count, slot, st)
-
-    shared_y = None
-    if block.has_shared:  # replicated weights, own tokens; independent of the exchange
-        shared_y = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
-        block.shared_dev(x, shared_y, st)
-
-    recv_counts = torch.empty(world * nl, dtype=torch.int32, device=dev)
-    dist.all_to_all_single(recv_counts, seg_count, output_split_sizes=[nl] * world, input_split_sizes=n_local, group=group)
-    seg_h = seg_count.cpu().numpy()
-    rc_h = recv_counts.cpu().numpy().reshape(world, nl)
-    send_splits, recv_splits, perm_h, per_expert = exchange_plan(seg_h, n_local, rc_h, rank)
-    n_recv = int(sum(recv_splits))
-
-    recv = torch.empty((n_recv, H), dtype=torch.bfloat16, device=dev)
-    dist.all_to_all_single(recv, rows, output_split_sizes=recv_splits, input_split_sizes=send_splits, group=group)
-
-    perm = torch.from_numpy(perm_h).to(dev, non_blocking=True)
-    rows_em = recv.index_select(0, perm) if n_recv else recv
-    y_em = torch.empty_like(rows_em)
-    cnt_dev = torch.from_numpy(per_expert).to(dev, non_blocking=True)
-    block.experts_dev(rows_em, cnt_dev, first_seg, nl, n_recv, y_em, st)
-    y_recv = torch.empty_like(recv)
-    if n_recv:
-        y_recv.index_copy_(0, perm, y_em)
-
-    y_rows = torch.empty_like(rows)
-    dist.all_to_all_single(y_rows, y_recv, output_split_sizes=send_splits, input_split_sizes=recv_splits, group=group)
-
-    out = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
-    block.combine_dev(y_rows, slot, shared_y, out, st)
-    return out
+    """One expert-parallel block call; keeps a ShardedMoe (and its buffers) on the block."""
+    sm = getattr(block, "_sharded", None)
+    if sm is None or sm.Tl != x.shape[0] or sm.sharding is not sharding:
+        sm = block._sharded = ShardedMoe(block, sharding, x.shape[0], group)
+    return sm(x)

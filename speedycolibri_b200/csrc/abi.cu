@@ -345,6 +345,7 @@ struct ColiMoe {
   float *select_bias, *logit_bias;
   WeightRef *gate, *up, *down;  // [E+1], entry E = shared expert
   int32_t *expert_slot, *seg_expert;
+  int32_t *local_slot;  // expert -> position among this rank's experts, or -1
   // workspace
   float *logits, *topk_w;
   int32_t *topk_idx, *local_rank, *chunk_cnt, *seg_count, *seg_off, *slot, *row_token;
@@ -517,7 +518,7 @@ extern "C" int coli_b200_moe_create(ColiMoe **out, const ColiMoeLayer *L, int ma
   m->item_cap = (int)(rows / 8 + m->nseg + 1);
   const int nchunk = (max_tokens + 31) / 32;
   ok = ok && ws_alloc(m, &m->router_w, (size_t)E * H) && ws_alloc(m, &m->gate, E + 1) && ws_alloc(m, &m->up, E + 1) &&
-       ws_alloc(m, &m->down, E + 1) && ws_alloc(m, &m->expert_slot, E) && ws_alloc(m, &m->seg_expert, E + 1) &&
+       ws_alloc(m, &m->down, E + 1) && ws_alloc(m, &m->expert_slot, E) && ws_alloc(m, &m->seg_expert, E + 1) && ws_alloc(m, &m->local_slot, E) &&
        ws_alloc(m, &m->logits, T * E) && ws_alloc(m, &m->topk_w, T * k) && ws_alloc(m, &m->topk_idx, T * k) &&
        ws_alloc(m, &m->local_rank, T * k) && ws_alloc(m, &m->chunk_cnt, (size_t)nchunk * E) &&
        ws_alloc(m, &m->seg_count, E + 1) && ws_alloc(m, &m->seg_off, E + 2) && ws_alloc(m, &m->slot, T * k) &&
@@ -546,6 +547,10 @@ extern "C" int coli_b200_moe_create(ColiMoe **out, const ColiMoeLayer *L, int ma
        coli_cuda_check(cudaMemcpyAsync(m->down, td.data(), sizeof(WeightRef) * (E + 1), cudaMemcpyHostToDevice, st), "table upload") &&
        coli_cuda_check(cudaMemcpyAsync(m->expert_slot, m->h_expert_slot.data(), sizeof(int32_t) * E, cudaMemcpyHostToDevice, st), "table upload") &&
        coli_cuda_check(cudaMemcpyAsync(m->seg_expert, m->h_seg_expert.data(), sizeof(int32_t) * (E + 1), cudaMemcpyHostToDevice, st), "table upload");
+  std::vector<int32_t> h_local_slot(E, -1);
+  for (int e = 0; e < E; ++e)
+    if (world == 1 || owner[e] == L->ep_rank) h_local_slot[e] = m->h_expert_slot[e] - m->first_local_seg;
+  ok = ok && coli_cuda_check(cudaMemcpyAsync(m->local_slot, h_local_slot.data(), sizeof(int32_t) * E, cudaMemcpyHostToDevice, st), "table upload");
   if (ok && L->select_bias)
     ok = coli_cuda_check(cudaMemcpyAsync(m->select_bias, L->select_bias, sizeof(float) * E, cudaMemcpyHostToDevice, st), "bias upload");
   if (ok && L->logit_bias)
@@ -614,6 +619,7 @@ static colib::PermuteParams permute_params(ColiMoe *m, const void *x_dev, int T,
   pp.H = m->L.H;
   pp.E = m->L.E;
   pp.k = m->L.k;
+  pp.nseg_routed = m->L.E;
   pp.has_shared = with_shared ? 1 : 0;
   pp.rows_per_item = rpi;
   pp.topk_idx = m->topk_idx;
@@ -719,6 +725,7 @@ extern "C" int coli_b200_moe_block_dev(ColiMoe *m, const void *x_dev, void *out_
   cp.slot = m->slot;
   cp.topk_w = m->topk_w;
   cp.out = (__nv_bfloat16 *)out_dev;
+  cp.out32 = nullptr;
   if (!colib::launch_combine(cp, st)) return 0;
   COLI_MARK(5);
 #undef COLI_MARK
@@ -784,18 +791,41 @@ extern "C" int coli_b200_moe_block(ColiMoe *m, const void *x, void *out, int T, 
   return 1;
 }
 
-// ---- stages ----------------------------------------------------------------------------------------
-extern "C" int coli_b200_moe_route_dev(ColiMoe *m, const void *x_dev, int T, void *rows_dev, int32_t *seg_count_dev,
-                                       int32_t *slot_dev, void *stream) {
-  if (!check_T(m, T, "moe_route_dev")) return 0;
-  if (!x_dev || !rows_dev || !seg_count_dev || !slot_dev) {
-    coli_set_error("moe_route_dev: null pointer");
+// ---- stages (expert parallelism) ---------------------------------------------------------------------
+// The expert-parallel block is assembled from these by the host (speedycolibri_b200/cluster.py):
+//   topk (own tokens) -> all-gather tokens + routing -> gather_local -> experts -> combine_partial
+//   -> reduce-scatter of the f32 partials -> finish (+ shared expert of the own tokens).
+// Every size that crosses ranks is fixed by (T, H, k), so no step needs a host synchronisation.
+extern "C" int coli_b200_moe_local_experts(const ColiMoe *m) { return m ? m->n_local_seg : 0; }
+
+extern "C" int coli_b200_moe_topk_dev(ColiMoe *m, const void *x_dev, int T, int32_t *topk_idx_dev, float *topk_w_dev,
+                                      void *stream) {
+  if (!check_T(m, T, "moe_topk_dev")) return 0;
+  if (T == 0) return 1;
+  if (!x_dev || !topk_idx_dev || !topk_w_dev) {
+    coli_set_error("moe_topk_dev: null pointer");
+    return 0;
+  }
+  colib::RouteParams rp = route_params(m, x_dev, T);
+  rp.topk_idx = topk_idx_dev;
+  rp.topk_w = topk_w_dev;
+  return colib::launch_router(rp, pick_stream(m, stream));
+}
+
+extern "C" int coli_b200_moe_gather_local_dev(ColiMoe *m, const void *x_dev, const int32_t *topk_idx_dev, int T,
+                                              void *rows_dev, int32_t *seg_count_dev, int32_t *slot_dev, void *stream) {
+  if (!check_T(m, T, "moe_gather_local_dev")) return 0;
+  if (!x_dev || !topk_idx_dev || !rows_dev || !seg_count_dev || !slot_dev) {
+    coli_set_error("moe_gather_local_dev: null pointer");
     return 0;
   }
   cudaStream_t st = pick_stream(m, stream);
-  if (T == 0) return coli_cuda_check(cudaMemsetAsync(seg_count_dev, 0, sizeof(int32_t) * m->L.E, st), "count clear") ? 1 : 0;
-  if (!colib::launch_router(route_params(m, x_dev, T), st)) return 0;
-  return colib::launch_permute(permute_params(m, x_dev, T, false, 32, rows_dev, seg_count_dev, slot_dev), st);
+  if (T == 0) return coli_cuda_check(cudaMemsetAsync(seg_count_dev, 0, sizeof(int32_t) * m->n_local_seg, st), "count clear") ? 1 : 0;
+  colib::PermuteParams pp = permute_params(m, x_dev, T, false, colib::TC_MAX_TOKENS, rows_dev, seg_count_dev, slot_dev);
+  pp.topk_idx = topk_idx_dev;
+  pp.expert_slot = m->local_slot;
+  pp.nseg_routed = m->n_local_seg;
+  return colib::launch_permute(pp, st);
 }
 
 // h scratch for the stage calls grows on demand (synchronises the device when it does).
@@ -817,14 +847,16 @@ static bool ensure_items(ColiMoe *m, int need) {
   return ws_alloc(m, &m->item_seg, need) && ws_alloc(m, &m->item_row0, need) && ws_alloc(m, &m->item_nrows, need);
 }
 
+// rows_cap bounds the rows the buffers hold (the work list is sized from it); rows_expected only
+// selects the kernel family, so that the choice is a function of shapes, never of data.
 static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, const WeightRef *d, const int32_t *seg_expert_dev,
-                        const void *rows_dev, const int32_t *seg_count_dev, int n_seg, int n_rows, void *y_dev,
-                        cudaStream_t st) {
-  if (n_rows == 0) return 1;
-  const bool tc = use_tc_path(m->L.fmt, n_rows, n_seg);
-  const int rpi = tc ? colib::TC_MAX_TOKENS : rows_per_item_for(m->L, n_rows, n_seg);
-  const int max_items = n_rows / rpi + n_seg;
-  if (!ensure_h(m, (size_t)n_rows) || !ensure_items(m, max_items)) return 0;
+                        const void *rows_dev, const int32_t *seg_count_dev, int n_seg, int rows_cap, int rows_expected,
+                        void *y_dev, cudaStream_t st) {
+  if (rows_cap == 0 || n_seg == 0) return 1;
+  const bool tc = use_tc_path(m->L.fmt, rows_expected, n_seg);
+  const int rpi = tc ? colib::TC_MAX_TOKENS : rows_per_item_for(m->L, rows_expected, n_seg);
+  const int max_items = rows_cap / rpi + n_seg;
+  if (!ensure_h(m, (size_t)rows_cap) || !ensure_items(m, max_items)) return 0;
   if (!colib::launch_items_from_counts(seg_count_dev, n_seg, rpi, m->seg_off, m->item_seg, m->item_row0, m->item_nrows,
                                        m->n_items, st))
     return 0;
@@ -844,7 +876,7 @@ static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, cons
     tp.h = m->h;
     tp.y = (__nv_bfloat16 *)y_dev;
     tp.status = m->status;
-    return colib::launch_gate_up_tc(tp, rows_dev, n_rows, m->sm_count, st) && colib::launch_down_tc(tp, n_rows, m->sm_count, st);
+    return colib::launch_gate_up_tc(tp, rows_dev, rows_cap, m->sm_count, st) && colib::launch_down_tc(tp, rows_cap, m->sm_count, st);
   }
   colib::FfnParams fp;
   fp.fmt = m->L.fmt;
@@ -868,20 +900,15 @@ static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, cons
   return colib::launch_ffn_small(fp, st);
 }
 
-extern "C" int coli_b200_moe_experts_dev(ColiMoe *m, const void *rows_dev, const int32_t *seg_count_dev, int first_seg,
-                                         int n_seg, int n_rows, void *y_dev, void *stream) {
+extern "C" int coli_b200_moe_experts_dev(ColiMoe *m, const void *rows_dev, const int32_t *seg_count_dev, int rows_cap,
+                                         int rows_expected, void *y_dev, void *stream) {
   if (!m || !select_ctx(m->ctx)) return 0;
-  if (n_seg < 0 || first_seg < 0 || first_seg + n_seg > m->L.E || n_rows < 0 || (n_rows > 0 && (!rows_dev || !y_dev || !seg_count_dev))) {
-    coli_set_error("moe_experts_dev: bad segment range [%d,%d) or null pointer", first_seg, first_seg + n_seg);
+  if (rows_cap < 0 || rows_expected < 0 || (rows_cap > 0 && (!rows_dev || !y_dev || !seg_count_dev))) {
+    coli_set_error("moe_experts_dev: bad row bounds or null pointer");
     return 0;
   }
-  if (first_seg < m->first_local_seg || first_seg + n_seg > m->first_local_seg + m->n_local_seg) {
-    coli_set_error("moe_experts_dev: segments [%d,%d) are not all resident on rank %d (local range [%d,%d))", first_seg,
-                   first_seg + n_seg, m->L.ep_rank, m->first_local_seg, m->first_local_seg + m->n_local_seg);
-    return 0;
-  }
-  return run_segments(m, m->gate, m->up, m->down, m->seg_expert + first_seg, rows_dev, seg_count_dev, n_seg, n_rows, y_dev,
-                      pick_stream(m, stream));
+  return run_segments(m, m->gate, m->up, m->down, m->seg_expert + m->first_local_seg, rows_dev, seg_count_dev, m->n_local_seg,
+                      rows_cap, rows_expected < rows_cap ? rows_expected : rows_cap, y_dev, pick_stream(m, stream));
 }
 
 extern "C" int coli_b200_moe_shared_dev(ColiMoe *m, const void *x_dev, int T, void *y_dev, void *stream) {
@@ -895,28 +922,41 @@ extern "C" int coli_b200_moe_shared_dev(ColiMoe *m, const void *x_dev, int T, vo
   // one segment of T rows; its count lives in seg_count[E]
   if (!coli_cuda_check(cudaMemcpyAsync(m->seg_count + m->L.E, &T, sizeof(int32_t), cudaMemcpyHostToDevice, st), "shared count"))
     return 0;
-  return run_segments(m, m->gate + m->L.E, m->up + m->L.E, m->down + m->L.E, nullptr, x_dev, m->seg_count + m->L.E, 1, T, y_dev, st);
+  return run_segments(m, m->gate + m->L.E, m->up + m->L.E, m->down + m->L.E, nullptr, x_dev, m->seg_count + m->L.E, 1, T, T, y_dev, st);
 }
 
-extern "C" int coli_b200_moe_combine_dev(ColiMoe *m, const void *y_rows_dev, const int32_t *slot_dev,
-                                         const void *shared_y_dev, void *out_dev, int T, void *stream) {
-  if (!check_T(m, T, "moe_combine_dev")) return 0;
+extern "C" int coli_b200_moe_combine_partial_dev(ColiMoe *m, const void *y_rows_dev, const int32_t *slot_dev,
+                                                 const float *topk_w_dev, float *partial_dev, int T, void *stream) {
+  if (!check_T(m, T, "moe_combine_partial_dev")) return 0;
   if (T == 0) return 1;
-  if (!y_rows_dev || !slot_dev || !out_dev) {
-    coli_set_error("moe_combine_dev: null pointer");
+  if (!y_rows_dev || !slot_dev || !topk_w_dev || !partial_dev) {
+    coli_set_error("moe_combine_partial_dev: null pointer");
     return 0;
   }
   colib::CombineParams cp;
   cp.T = T;
   cp.H = m->L.H;
   cp.k = m->L.k;
-  cp.has_shared = shared_y_dev ? 1 : 0;
+  cp.has_shared = 0;
   cp.y = (const __nv_bfloat16 *)y_rows_dev;
-  cp.shared_y = (const __nv_bfloat16 *)shared_y_dev;
+  cp.shared_y = nullptr;
   cp.slot = slot_dev;
-  cp.topk_w = m->topk_w;
-  cp.out = (__nv_bfloat16 *)out_dev;
+  cp.topk_w = topk_w_dev;
+  cp.out = nullptr;
+  cp.out32 = partial_dev;
   return colib::launch_combine(cp, pick_stream(m, stream));
+}
+
+extern "C" int coli_b200_moe_finish_dev(ColiMoe *m, const float *partial_dev, const void *shared_y_dev, void *out_dev, int T,
+                                        void *stream) {
+  if (!check_T(m, T, "moe_finish_dev")) return 0;
+  if (T == 0) return 1;
+  if (!partial_dev || !out_dev) {
+    coli_set_error("moe_finish_dev: null pointer");
+    return 0;
+  }
+  return colib::launch_finish(partial_dev, (const __nv_bfloat16 *)shared_y_dev, (__nv_bfloat16 *)out_dev, T, m->L.H,
+                              pick_stream(m, stream));
 }
 
 // sharding.rs:251-265

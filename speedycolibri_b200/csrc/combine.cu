@@ -16,6 +16,7 @@ __global__ void __launch_bounds__(256) k_combine(CombineParams p, const __nv_bfl
   for (int kk = 0; kk < p.k; ++kk) {
     const float w = p.topk_w[(size_t)t * p.k + kk];
     const int row = p.slot[(size_t)t * p.k + kk];
+    if (row < 0) continue;  // that expert lives on another rank, which adds its own partial
     const uint4 v = *reinterpret_cast<const uint4 *>(p.y + (size_t)row * p.H + c * 8);
     const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -32,6 +33,12 @@ __global__ void __launch_bounds__(256) k_combine(CombineParams p, const __nv_bfl
       acc[2 * i] += __uint_as_float(u[i] << 16);
       acc[2 * i + 1] += __uint_as_float(u[i] & 0xffff0000u);
     }
+  }
+  if (p.out32) {  // f32 partial sum of this rank's experts; summed across ranks before the final rounding
+    float4 *o32 = reinterpret_cast<float4 *>(p.out32 + (size_t)t * p.H + c * 8);
+    o32[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    o32[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    return;
   }
   uint32_t o[4];
 #pragma unroll
@@ -54,6 +61,40 @@ int launch_combine(const CombineParams &p, cudaStream_t st) {
   k_combine<<<grid, 256, 0, st>>>(p, shared_y);
   coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "combine launch") ? 1 : 0;
+}
+
+// out = bf16(partial + shared): the last step of the expert-parallel block
+__global__ void __launch_bounds__(256) k_finish(const float *partial, const __nv_bfloat16 *shared_y, __nv_bfloat16 *out, size_t n8) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  const float4 a = reinterpret_cast<const float4 *>(partial)[2 * i], b = reinterpret_cast<const float4 *>(partial)[2 * i + 1];
+  float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  if (shared_y) {
+    const uint4 sv = reinterpret_cast<const uint4 *>(shared_y)[i];
+    const uint32_t u[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[2 * j] += __uint_as_float(u[j] << 16);
+      v[2 * j + 1] += __uint_as_float(u[j] & 0xffff0000u);
+    }
+  }
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    o[j] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v[2 * j])) |
+           ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v[2 * j + 1])) << 16);
+  reinterpret_cast<uint4 *>(out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+}
+int launch_finish(const float *partial, const __nv_bfloat16 *shared_y, __nv_bfloat16 *out, int T, int H, cudaStream_t st) {
+  if (T <= 0) return 1;
+  if (H % 8) {
+    coli_set_error("finish: H=%d must be a multiple of 8", H);
+    return 0;
+  }
+  const size_t n8 = (size_t)T * H / 8;
+  k_finish<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(partial, shared_y, out, n8);
+  coli_count_launch(1);
+  return coli_cuda_check(cudaGetLastError(), "finish launch") ? 1 : 0;
 }
 
 __global__ void k_f32_to_bf16(const float *src, __nv_bfloat16 *dst, size_t n) {

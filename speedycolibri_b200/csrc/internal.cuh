@@ -81,10 +81,11 @@ int launch_router(const RouteParams &p, cudaStream_t st);
 
 struct PermuteParams {
   int T, H, E, k;
-  int has_shared;              // append T identity rows for the shared expert (segment index E)
+  int nseg_routed;             // routed segments: E, or the number of experts resident on this rank
+  int has_shared;              // append T identity rows for the shared expert (segment index nseg_routed)
   int rows_per_item;           // token rows per work item
   const int32_t *topk_idx;     // [T,k]
-  const int32_t *expert_slot;  // [E] segment position of each expert (null = identity)
+  const int32_t *expert_slot;  // [E] segment position of each expert (null = identity, < 0 = not resident)
   int32_t *local_rank;         // [T*k] scratch
   int32_t *chunk_cnt;          // [nchunk][E] scratch
   int32_t *seg_count;          // [E] out: rows per segment (segment order)
@@ -147,9 +148,11 @@ struct CombineParams {
   const __nv_bfloat16 *shared_y;  // [T,H] shared-expert rows (used when has_shared)
   const int32_t *slot;            // [T*k]
   const float *topk_w;            // [T*k]
-  __nv_bfloat16 *out;             // [T,H]
+  __nv_bfloat16 *out;             // [T,H] bf16 result, or
+  float *out32;                   // [T,H] f32 partial sum (no rounding, no shared add) when not null
 };
 int launch_combine(const CombineParams &p, cudaStream_t st);
+int launch_finish(const float *partial, const __nv_bfloat16 *shared_y, __nv_bfloat16 *out, int T, int H, cudaStream_t st);
 int launch_f32_to_bf16(const float *src, __nv_bfloat16 *dst, size_t n, cudaStream_t st);
 // y[S,O] = x[S,I] @ W[O,I]^T, all f32, one thread per output, multiply then add per k in order
 // (crates/colibri-engine/src/linear.rs:199-220).

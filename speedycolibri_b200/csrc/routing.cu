@@ -344,17 +344,22 @@ int launch_router(const RouteParams &p, cudaStream_t st) {
     }
     k_router_decode<<<(p.E + 7) / 8, 64 * ((p.T * 8 + 63) / 64), dec_smem, st>>>(p);
     coli_count_launch(1);
-  } else if ((size_t)p.T * p.E >= 64 * 64 * 64 && p.H % 8 == 0) {
-    dim3 grid((p.E + 63) / 64, (p.T + 127) / 128);
-    k_router_gemm_big<<<grid, 256, 0, st>>>(p);
-    coli_count_launch(1);
-  } else if ((size_t)p.T * p.E >= 64 * 64 * 64) {
-    dim3 grid((p.E + 63) / 64, (p.T + 63) / 64);
-    k_router_gemm<4, 4><<<grid, 256, 0, st>>>(p);
-    coli_count_launch(1);
   } else {
-    dim3 grid((p.E + 15) / 16, (p.T + 15) / 16);
-    k_router_gemm<1, 1><<<grid, 256, 0, st>>>(p);
+    // the largest tile that still gives ~one CTA per SM; every variant has identical arithmetic
+    auto blocks = [&](int bm, int bn) { return (long)((p.T + bm - 1) / bm) * ((p.E + bn - 1) / bn); };
+    if (p.H % 8 == 0 && blocks(128, 64) >= 96) {
+      dim3 grid((p.E + 63) / 64, (p.T + 127) / 128);
+      k_router_gemm_big<<<grid, 256, 0, st>>>(p);
+    } else if (blocks(64, 64) >= 96) {
+      dim3 grid((p.E + 63) / 64, (p.T + 63) / 64);
+      k_router_gemm<4, 4><<<grid, 256, 0, st>>>(p);
+    } else if (blocks(32, 32) >= 96) {
+      dim3 grid((p.E + 31) / 32, (p.T + 31) / 32);
+      k_router_gemm<2, 2><<<grid, 256, 0, st>>>(p);
+    } else {
+      dim3 grid((p.E + 15) / 16, (p.T + 15) / 16);
+      k_router_gemm<1, 1><<<grid, 256, 0, st>>>(p);
+    }
     coli_count_launch(1);
   }
   const size_t sm = (size_t)4 * 2 * p.E * sizeof(float);
@@ -397,18 +402,26 @@ __global__ void __launch_bounds__(1024) k_seg_scan(PermuteParams p, int nchunk, 
   __shared__ int seg_cnt[1024 + 1];
   __shared__ int seg_off[1024 + 2];
   const int E = p.E;
-  const int nseg = E + (p.has_shared ? 1 : 0);
+  const int nrt = p.nseg_routed;  // routed segments: E, or the experts resident on this rank
+  const int nseg = nrt + (p.has_shared ? 1 : 0);
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    int run = 0;
-    for (int c = 0; c < nchunk; ++c) {
-      const int v = p.chunk_cnt[(size_t)c * E + e];
-      p.chunk_cnt[(size_t)c * E + e] = run;
-      run += v;
-    }
     const int pos = p.expert_slot ? p.expert_slot[e] : e;
+    if (pos < 0) continue;  // expert lives on another rank: its pairs get no row here
+    int run = 0;
+    for (int c0 = 0; c0 < nchunk; c0 += 8) {  // loads of a group are independent of its stores
+      int v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = (c0 + j < nchunk) ? p.chunk_cnt[(size_t)(c0 + j) * E + e] : 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (c0 + j < nchunk) {
+          p.chunk_cnt[(size_t)(c0 + j) * E + e] = run;
+          run += v[j];
+        }
+    }
     seg_cnt[pos] = run;
   }
-  if (threadIdx.x == 0 && p.has_shared) seg_cnt[E] = p.T;
+  if (threadIdx.x == 0 && p.has_shared) seg_cnt[nrt] = p.T;
   __syncthreads();
   if (threadIdx.x == 0) {
     int run = 0, items = 0;
@@ -430,7 +443,7 @@ __global__ void __launch_bounds__(1024) k_seg_scan(PermuteParams p, int nchunk, 
   }
   __syncthreads();
   for (int s = threadIdx.x; s <= nseg; s += blockDim.x) p.seg_off[s] = seg_off[s];
-  for (int s = threadIdx.x; s < E; s += blockDim.x) p.seg_count[s] = seg_cnt[s];
+  for (int s = threadIdx.x; s < nrt; s += blockDim.x) p.seg_count[s] = seg_cnt[s];
 }
 
 __global__ void __launch_bounds__(256) k_permute(PermuteParams p) {
@@ -444,11 +457,15 @@ __global__ void __launch_bounds__(256) k_permute(PermuteParams p) {
     t = warp / p.k;
     const int e = p.topk_idx[warp];
     const int s = p.expert_slot ? p.expert_slot[e] : e;
+    if (s < 0) {  // not resident here: no row, the combine skips negative slots
+      if (lane == 0) p.slot[warp] = -1;
+      return;
+    }
     pos = p.seg_off[s] + p.chunk_cnt[(size_t)(t >> 5) * p.E + e] + p.local_rank[warp];
     if (lane == 0) p.slot[warp] = pos;
   } else {
     t = warp - nrouted;
-    pos = p.seg_off[p.E] + t;
+    pos = p.seg_off[p.nseg_routed] + t;
   }
   if (lane == 0) p.row_token[pos] = t;
   if (p.xg && (warp < nrouted || p.gather_shared)) {
@@ -466,7 +483,7 @@ int launch_permute(const PermuteParams &p, cudaStream_t st) {
     return 0;
   }
   const int nchunk = (p.T + 31) / 32;
-  const int nseg = p.E + (p.has_shared ? 1 : 0);
+  const int nseg = p.nseg_routed + (p.has_shared ? 1 : 0);
   const int max_items = (p.T * p.k + (p.has_shared ? p.T : 0)) / p.rows_per_item + nseg;
   k_seg_count<<<(nchunk + 3) / 4, 128, (size_t)4 * p.E * sizeof(int), st>>>(p, nchunk);
   coli_count_launch(1);

@@ -160,22 +160,32 @@ class MoeBlock:
         return _lib_().coli_b200_moe_workspace_bytes(self.handle)
 
     # -- stages (used by cluster.moe_sharded) ---------------------------------------------------
-    def route_dev(self, x, rows, seg_count, slot, stream):
-        _check(_lib_().coli_b200_moe_route_dev(self.handle, x.data_ptr(), x.shape[0], rows.data_ptr(), seg_count.data_ptr(),
-                                               slot.data_ptr(), stream), "coli_b200_moe_route_dev")
+    def local_experts(self) -> int:
+        return _lib_().coli_b200_moe_local_experts(self.handle)
 
-    def experts_dev(self, rows, seg_count, first_seg, n_seg, n_rows, y, stream):
-        _check(_lib_().coli_b200_moe_experts_dev(self.handle, rows.data_ptr(), seg_count.data_ptr(), first_seg, n_seg, n_rows,
+    def topk_dev(self, x, idx, w, stream):
+        _check(_lib_().coli_b200_moe_topk_dev(self.handle, x.data_ptr(), x.shape[0], idx.data_ptr(), w.data_ptr(), stream),
+               "coli_b200_moe_topk_dev")
+
+    def gather_local_dev(self, x, idx, rows, seg_count, slot, stream):
+        _check(_lib_().coli_b200_moe_gather_local_dev(self.handle, x.data_ptr(), idx.data_ptr(), x.shape[0], rows.data_ptr(),
+                                                      seg_count.data_ptr(), slot.data_ptr(), stream), "coli_b200_moe_gather_local_dev")
+
+    def experts_dev(self, rows, seg_count, rows_expected, y, stream):
+        _check(_lib_().coli_b200_moe_experts_dev(self.handle, rows.data_ptr(), seg_count.data_ptr(), rows.shape[0], rows_expected,
                                                  y.data_ptr(), stream), "coli_b200_moe_experts_dev")
 
     def shared_dev(self, x, y, stream):
         _check(_lib_().coli_b200_moe_shared_dev(self.handle, x.data_ptr(), x.shape[0], y.data_ptr(), stream),
                "coli_b200_moe_shared_dev")
 
-    def combine_dev(self, y_rows, slot, shared_y, out, stream):
-        _check(_lib_().coli_b200_moe_combine_dev(self.handle, y_rows.data_ptr(), slot.data_ptr(),
-                                                 shared_y.data_ptr() if shared_y is not None else None, out.data_ptr(),
-                                                 out.shape[0], stream), "coli_b200_moe_combine_dev")
+    def combine_partial_dev(self, y_rows, slot, w, partial, stream):
+        _check(_lib_().coli_b200_moe_combine_partial_dev(self.handle, y_rows.data_ptr(), slot.data_ptr(), w.data_ptr(),
+                                                         partial.data_ptr(), partial.shape[0], stream), "coli_b200_moe_combine_partial_dev")
+
+    def finish_dev(self, partial, shared_y, out, stream):
+        _check(_lib_().coli_b200_moe_finish_dev(self.handle, partial.data_ptr(), shared_y.data_ptr() if shared_y is not None else None,
+                                                out.data_ptr(), out.shape[0], stream), "coli_b200_moe_finish_dev")
 
     def close(self):
         if self.handle:

@@ -310,67 +310,71 @@ def test_expert_mlp_fp8_row_scaled(gpu_backend, orc):
 
 
 # ---- stage calls (what expert parallelism is assembled from), emulated on one GPU -------------------------------
-@pytest.mark.parametrize("world", [1, 2, 4])
-def test_stage_calls_emulate_expert_parallel(gpu_backend, orc, world):
+@pytest.mark.parametrize("world,name", [(1, "tiny_sig"), (2, "tiny_sig"), (4, "tiny_sig"), (2, "mid")])
+def test_stage_calls_emulate_expert_parallel(gpu_backend, orc, world, name):
     """`world` handles on ONE GPU stand for the ranks (a single process, stages run one after the
-    other, the all-to-all done by slicing) — ranks never wait on one another on the device."""
+    other, the all-gather done by concatenation and the reduce-scatter by a sum in rank order) —
+    ranks never wait on one another on the device."""
     import torch
-    from speedycolibri_b200.cluster import ExpertSharding, exchange_plan
+    from speedycolibri_b200.cluster import ExpertSharding
     from speedycolibri_b200.moe import Config, MoeBlock
 
-    shape = CONFIGS["tiny_sig"].with_tokens(40 * world)
+    shape = CONFIGS[name].with_tokens((40 if name == "tiny_sig" else 160) * world)
     L, packed = host_layer(shape)
-    x_all = synth.host_tokens(shape, shape.T)
-    want = L.moe_block(x_all, world=world)
+    x_all_h = synth.host_tokens(shape, shape.T)
+    want = L.moe_block(x_all_h, world=world)
     sh = ExpertSharding.new(world, shape.E)
-    n_local = [sh.count_for(r) for r in range(world)]
-    bounds = np.concatenate([[0], np.cumsum(n_local)])
-    Tl = shape.T // world
-    blks, st = [], torch.cuda.current_stream().cuda_stream
+    T, Tl, k, H = shape.T, shape.T // world, shape.k, shape.H
+    st = torch.cuda.current_stream().cuda_stream
+    blks = []
     for r in range(world):
         layer = upload_layer(shape, packed, local=set(sh.local_experts(r)))
-        blks.append(MoeBlock(Config.from_shape(shape), layer, Tl, ep_rank=r, ep_world=world))
-    xs = [torch.from_numpy(x_all[r * Tl:(r + 1) * Tl].view(np.int16)).cuda().view(torch.bfloat16) for r in range(world)]
-    rows, segs, slots = [], [], []
+        blks.append(MoeBlock(Config.from_shape(shape), layer, T, ep_rank=r, ep_world=world))
+        assert blks[r].local_experts() == sh.count_for(r)
+    x_all = torch.from_numpy(x_all_h.view(np.int16)).cuda().view(torch.bfloat16)
+    idx_all = torch.empty((T, k), dtype=torch.int32, device="cuda")
+    w_all = torch.empty((T, k), dtype=torch.float32, device="cuda")
+    for r in range(world):  # every rank routes its own tokens; "all-gather" = adjacent slices
+        sl = slice(r * Tl, (r + 1) * Tl)
+        blks[r].topk_dev(x_all[sl], idx_all[sl], w_all[sl], st)
+    torch.cuda.synchronize()
+    assert np.array_equal(idx_all.cpu().numpy(), want["idx"])
+    assert np.array_equal(w_all.cpu().numpy().view(np.uint32), want["w"].view(np.uint32))
+    total = torch.zeros((T, H), dtype=torch.float32, device="cuda")
+    rows_seen = 0
     for r in range(world):
-        rw = torch.empty((Tl * shape.k, shape.H), dtype=torch.bfloat16, device="cuda")
-        sc = torch.empty(shape.E, dtype=torch.int32, device="cuda")
-        sl = torch.empty(Tl * shape.k, dtype=torch.int32, device="cuda")
-        blks[r].route_dev(xs[r], rw, sc, sl, st)
-        rows.append(rw); segs.append(sc.cpu().numpy()); slots.append(sl)
-    row_off = [np.concatenate([[0], np.cumsum(s)]) for s in segs]
-    y_back = [torch.empty_like(rows[r]) for r in range(world)]
-    for d in range(world):  # destination rank: gather what every source sends it, [src][expert] order
-        recv_counts = np.stack([segs[s][bounds[d]:bounds[d + 1]] for s in range(world)])
-        parts = [rows[s][row_off[s][bounds[d]]:row_off[s][bounds[d + 1]]] for s in range(world)]
-        recv = torch.cat(parts) if parts else rows[0][:0]
-        _, rsplit, perm, per_e = exchange_plan(segs[d], n_local, recv_counts, d)
-        perm_t = torch.from_numpy(perm).cuda()
-        em = recv.index_select(0, perm_t)
-        y_em = torch.empty_like(em)
-        blks[d].experts_dev(em, torch.from_numpy(per_e).cuda(), int(bounds[d]), n_local[d], em.shape[0], y_em, st)
-        y_recv = torch.empty_like(recv)
-        y_recv.index_copy_(0, perm_t, y_em)
-        off = 0
-        for s in range(world):  # the return all-to-all
-            n = rsplit[s]
-            y_back[s][row_off[s][bounds[d]]:row_off[s][bounds[d + 1]]] = y_recv[off:off + n]
-            off += n
+        rows = torch.empty((T * k, H), dtype=torch.bfloat16, device="cuda")
+        y = torch.empty_like(rows)
+        seg = torch.zeros(max(1, sh.count_for(r)), dtype=torch.int32, device="cuda")
+        slot = torch.empty(T * k, dtype=torch.int32, device="cuda")
+        part = torch.empty((T, H), dtype=torch.float32, device="cuda")
+        blks[r].gather_local_dev(x_all, idx_all, rows, seg, slot, st)
+        blks[r].experts_dev(rows, seg, T * k // world, y, st)
+        blks[r].combine_partial_dev(y, slot, w_all, part, st)
+        total += part  # ascending rank order, as moe.rs:1725-1733 folds peer partials
+        torch.cuda.synchronize()
+        blks[r].check()
+        # bookkeeping: this rank saw exactly the pairs routed to its experts
+        local = set(sh.local_experts(r))
+        n_local_pairs = int(np.isin(want["idx"], list(local)).sum())
+        assert int(seg.sum()) == n_local_pairs and int((slot >= 0).sum()) == n_local_pairs
+        rows_seen += n_local_pairs
+    assert rows_seen == T * k
     outs = []
     for r in range(world):
-        sy = torch.empty((Tl, shape.H), dtype=torch.bfloat16, device="cuda")
-        blks[r].shared_dev(xs[r], sy, st)
-        o = torch.empty((Tl, shape.H), dtype=torch.bfloat16, device="cuda")
-        blks[r].combine_dev(y_back[r], slots[r], sy, o, st)
+        sl = slice(r * Tl, (r + 1) * Tl)
+        sy = torch.empty((Tl, H), dtype=torch.bfloat16, device="cuda")
+        blks[r].shared_dev(x_all[sl].contiguous(), sy, st)
+        o = torch.empty((Tl, H), dtype=torch.bfloat16, device="cuda")
+        blks[r].finish_dev(total[sl].contiguous(), sy, o, st)
         outs.append(o)
     torch.cuda.synchronize()
     got = torch.cat(outs).view(torch.int16).cpu().numpy().view(np.uint16)
     assert rel_l2(got, want["out"]) <= REL_L2_TOL
-    if world == 1:  # identical kernels, identical bytes as the one-call block
-        layer = upload_layer(shape, packed)
-        one = MoeBlock(Config.from_shape(shape), layer, shape.T)
-        assert np.array_equal(one.moe(x_all), got)
-        one.close()
+    layer = upload_layer(shape, packed)
+    one = MoeBlock(Config.from_shape(shape), layer, T)
+    assert rel_l2(got, one.moe(x_all_h)) <= 2e-3  # same kernels, one extra f32 fold
+    one.close()
     for b in blks:
         b.close()
 
