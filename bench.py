@@ -209,6 +209,8 @@ def run_ours(args):
         import torch.distributed as dist
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "WARN"):
+            os.environ.pop("NCCL_DEBUG")  # its banner goes to stdout, which carries the one JSON line
         dist.init_process_group("nccl", device_id=dev)
     backend.init([local])
     shape = shape_for(args)
