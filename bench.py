@@ -341,6 +341,12 @@ def run_ours(args):
             parity = {"routing_exact": bool(np.array_equal(idx[:n_tok], res["idx"])),
                       "rel_l2": float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30)), "tokens_checked": n_tok}
 
+    if world > 1 and os.environ.get("COLI_EP_PROFILE"):
+        tm = {}
+        for _ in range(args.steps):
+            blk._sharded(x, timing=tm)
+        if rank == 0:
+            print("EP stage ms/step:", {k: round(v / args.steps, 4) for k, v in tm.items()}, file=sys.stderr)
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",

@@ -148,7 +148,7 @@ class ShardedMoe:
     stream, with no host synchronisation (every exchanged size follows from T, H, k):
 
       1. router + top-k of the own tokens                          (block.topk_dev)
-      2. all-gather of tokens, indices, weights                    (NCCL)
+      2. all-gather of tokens (overlapped with 1 and 7a), indices, weights   (NCCL)
       3. rows of the (token, kk) pairs routed to resident experts  (block.gather_local_dev)
       4. grouped expert FFN over those rows                        (block.experts_dev)
       5. f32 partial sum per token over the resident experts       (block.combine_partial_dev)
@@ -194,7 +194,11 @@ class ShardedMoe:
 
         return 0 if self.gloo else torch.cuda.current_stream().cuda_stream
 
-    def __call__(self, x, out=None):
+    STAGES = ("topk", "shared", "all_gather", "gather_local", "experts", "combine_partial", "reduce_scatter", "finish")
+
+    def __call__(self, x, out=None, timing=None):
+        """`timing`: optional dict that receives per-stage milliseconds (CUDA events on the current
+        stream; synchronises at the end, so only for measurement)."""
         import torch
         import torch.distributed as dist
 
@@ -202,21 +206,50 @@ class ShardedMoe:
         b, st = self.block, self._stream()
         if out is None:
             out = torch.empty_like(x)
+        marks = []
+
+        def mark():
+            if timing is not None and not self.gloo:
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                marks.append(e)
+
+        mark()
+        # the token all-gather does not depend on the routing: let it run under the router and the
+        # shared expert (NCCL's own stream), and join before the first kernel that reads x_all
+        gather_x = None
+        if self.gloo:
+            dist.all_gather_into_tensor(self.x_all, x, group=self.group)
+        else:
+            gather_x = dist.all_gather_into_tensor(self.x_all, x, group=self.group, async_op=True)
         b.topk_dev(x, self.idx, self.w, st)
-        if b.has_shared:  # replicated weights, own tokens; independent of the exchange
-            b.shared_dev(x, self.shared_y, st)
-        dist.all_gather_into_tensor(self.x_all, x, group=self.group)
+        mark()
         dist.all_gather_into_tensor(self.idx_all, self.idx, group=self.group)
         dist.all_gather_into_tensor(self.w_all, self.w, group=self.group)
+        if b.has_shared:  # replicated weights, own tokens; independent of the exchange
+            b.shared_dev(x, self.shared_y, st)
+        mark()
+        if gather_x is not None:
+            gather_x.wait()
+        mark()
         b.gather_local_dev(self.x_all, self.idx_all, self.rows, self.seg_count, self.slot, st)
+        mark()
         b.experts_dev(self.rows, self.seg_count, self.rows_expected, self.y_rows, st)
+        mark()
         b.combine_partial_dev(self.y_rows, self.slot, self.w_all, self.partial, st)
+        mark()
         if self.gloo:  # gloo has no reduce-scatter: all-reduce and keep the own slice
             dist.all_reduce(self.partial, group=self.group)
             self.mine.copy_(self.partial[self.rank * self.Tl:(self.rank + 1) * self.Tl])
         else:
             dist.reduce_scatter_tensor(self.mine, self.partial, group=self.group)
+        mark()
         b.finish_dev(self.mine, self.shared_y, out, st)
+        mark()
+        if marks:
+            torch.cuda.synchronize()
+            for name, e0, e1 in zip(self.STAGES, marks[:-1], marks[1:]):
+                timing[name] = timing.get(name, 0.0) + e0.elapsed_time(e1)
         return out
 
 

@@ -83,26 +83,29 @@ __global__ void __launch_bounds__(256) k_router_gemm(RouteParams p) {
 // of 32 staged with 16-byte loads and stored transposed as f32, so the inner loop is three
 // 128-bit shared loads per 32 FMAs.  Same arithmetic as above: each output is one thread's
 // k-ascending fmaf chain.  Needs H % 8 == 0.
+template <int BM>
 __global__ void __launch_bounds__(256) k_router_gemm_big(RouteParams p) {
-  constexpr int BM = 128, BN = 64, BK = 32, LDX = BM + 4, LDW = BN + 4;
+  constexpr int TMR = BM / 16;  // token rows per thread
+  constexpr int BN = 64, BK = 32, LDX = BM + 4, LDW = BN + 4;
   __shared__ __align__(16) float xs[BK][LDX];
   __shared__ __align__(16) float ws[BK][LDW];
-  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // tx -> 4 experts, ty -> 8 tokens
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // tx -> 4 experts, ty -> TMR tokens
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  float acc[8][4];
+  float acc[TMR][4];
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
+  for (int i = 0; i < TMR; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
-  // staging assignment: x tile = 128 rows x 4 chunks of 8 k (2 per thread), w tile = 64 rows x 4 chunks
+  // staging assignment: x tile = BM rows x 4 chunks of 8 k (64 rows per pass), w tile = 64 rows x 4 chunks
+  constexpr int XP = (BM + 63) / 64;
   const int sr = threadIdx.x >> 2, sc = threadIdx.x & 3;
   for (int k0 = 0; k0 < p.H; k0 += BK) {
-    uint4 xv[2], wv;
+    uint4 xv[XP], wv;
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
+    for (int h = 0; h < XP; ++h) {
       const int m = m0 + sr + 64 * h, k = k0 + sc * 8;
       xv[h] = make_uint4(0, 0, 0, 0);
-      if (m < p.T && k < p.H) xv[h] = *reinterpret_cast<const uint4 *>(p.x + (size_t)m * p.H + k);
+      if (sr + 64 * h < BM && m < p.T && k < p.H) xv[h] = *reinterpret_cast<const uint4 *>(p.x + (size_t)m * p.H + k);
     }
     {
       const int n = n0 + sr, k = k0 + sc * 8;
@@ -111,7 +114,8 @@ __global__ void __launch_bounds__(256) k_router_gemm_big(RouteParams p) {
     }
     __syncthreads();  // the previous chunk has been consumed
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
+    for (int h = 0; h < XP; ++h) {
+      if (sr + 64 * h >= BM) break;
       const uint32_t u[4] = {xv[h].x, xv[h].y, xv[h].z, xv[h].w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -130,22 +134,33 @@ __global__ void __launch_bounds__(256) k_router_gemm_big(RouteParams p) {
     __syncthreads();
 #pragma unroll 8
     for (int kk = 0; kk < BK; ++kk) {
-      const float4 a0 = *reinterpret_cast<const float4 *>(&xs[kk][ty * 8]);
-      const float4 a1 = *reinterpret_cast<const float4 *>(&xs[kk][ty * 8 + 4]);
+      float a[TMR];
+      if (TMR >= 4) {
+#pragma unroll
+        for (int q = 0; q < TMR / 4; ++q) {
+          const float4 v = *reinterpret_cast<const float4 *>(&xs[kk][ty * TMR + 4 * q]);
+          a[4 * q] = v.x;
+          a[4 * q + 1] = v.y;
+          a[4 * q + 2] = v.z;
+          a[4 * q + 3] = v.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < TMR; ++i) a[i] = xs[kk][ty * TMR + i];
+      }
       const float4 b = *reinterpret_cast<const float4 *>(&ws[kk][tx * 4]);
-      const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
       const float bb[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
+      for (int i = 0; i < TMR; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = __fmaf_rn(a[i], bb[j], acc[i][j]);
     }
   }
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
+  for (int i = 0; i < TMR; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int m = m0 + ty * 8 + i, n = n0 + tx * 4 + j;
+      const int m = m0 + ty * TMR + i, n = n0 + tx * 4 + j;
       if (m < p.T && n < p.E) {
         float v = acc[i][j];
         if (p.logit_bias) v = __fadd_rn(v, p.logit_bias[n]);
@@ -349,10 +364,13 @@ int launch_router(const RouteParams &p, cudaStream_t st) {
     auto blocks = [&](int bm, int bn) { return (long)((p.T + bm - 1) / bm) * ((p.E + bn - 1) / bn); };
     if (p.H % 8 == 0 && blocks(128, 64) >= 96) {
       dim3 grid((p.E + 63) / 64, (p.T + 127) / 128);
-      k_router_gemm_big<<<grid, 256, 0, st>>>(p);
-    } else if (blocks(64, 64) >= 96) {
+      k_router_gemm_big<128><<<grid, 256, 0, st>>>(p);
+    } else if (p.H % 8 == 0 && p.T >= 64) {  // one wave of 64x64 tiles: 8 x 4 register tiles keep the FMA pipe fed
       dim3 grid((p.E + 63) / 64, (p.T + 63) / 64);
-      k_router_gemm<4, 4><<<grid, 256, 0, st>>>(p);
+      k_router_gemm_big<64><<<grid, 256, 0, st>>>(p);
+    } else if (p.H % 8 == 0 && p.T >= 32) {
+      dim3 grid((p.E + 63) / 64, (p.T + 31) / 32);
+      k_router_gemm_big<32><<<grid, 256, 0, st>>>(p);
     } else if (blocks(32, 32) >= 96) {
       dim3 grid((p.E + 31) / 32, (p.T + 31) / 32);
       k_router_gemm<2, 2><<<grid, 256, 0, st>>>(p);
