@@ -405,10 +405,11 @@ extern "C" int coli_b200_moe_phase_ms(ColiMoe *m, float *ms, int *calls) {
 }
 extern "C" void *coli_b200_moe_stream(ColiMoe *m) { return m ? (void *)m->ctx->stream : nullptr; }
 
-// The tcgen05 path takes over when segments are prefill-sized (NVFP4 only); a pure function of
+// The tcgen05 path takes over from 8 rows per segment on average (NVFP4 only): below that the
+// register-level kernel re-reads so few token rows per weight tile that it wins; a pure function of
 // (rows, segments, format) so that kernel selection never depends on data or addresses.
 static bool use_tc_path(int fmt, int rows, int nseg) {
-  return fmt == COLI_FMT_NVFP4 && nseg > 0 && rows / nseg >= 48;
+  return fmt == COLI_FMT_NVFP4 && nseg > 0 && rows / nseg >= 8;
 }
 
 static int rows_per_item_for(const ColiMoeLayer &L, int rows, int nseg) {

@@ -99,19 +99,20 @@ __global__ void __launch_bounds__(256) k_router_gemm_big(RouteParams p) {
   // staging assignment: x tile = BM rows x 4 chunks of 8 k (64 rows per pass), w tile = 64 rows x 4 chunks
   constexpr int XP = (BM + 63) / 64;
   const int sr = threadIdx.x >> 2, sc = threadIdx.x & 3;
-  for (int k0 = 0; k0 < p.H; k0 += BK) {
-    uint4 xv[XP], wv;
+  uint4 xv[XP], wv;
+  auto fetch = [&](int k0) {  // global -> registers; issued one chunk ahead of its use
 #pragma unroll
     for (int h = 0; h < XP; ++h) {
       const int m = m0 + sr + 64 * h, k = k0 + sc * 8;
       xv[h] = make_uint4(0, 0, 0, 0);
       if (sr + 64 * h < BM && m < p.T && k < p.H) xv[h] = *reinterpret_cast<const uint4 *>(p.x + (size_t)m * p.H + k);
     }
-    {
-      const int n = n0 + sr, k = k0 + sc * 8;
-      wv = make_uint4(0, 0, 0, 0);
-      if (n < p.E && k < p.H) wv = *reinterpret_cast<const uint4 *>(p.router_w + (size_t)n * p.H + k);
-    }
+    const int n = n0 + sr, k = k0 + sc * 8;
+    wv = make_uint4(0, 0, 0, 0);
+    if (n < p.E && k < p.H) wv = *reinterpret_cast<const uint4 *>(p.router_w + (size_t)n * p.H + k);
+  };
+  fetch(0);
+  for (int k0 = 0; k0 < p.H; k0 += BK) {
     __syncthreads();  // the previous chunk has been consumed
 #pragma unroll
     for (int h = 0; h < XP; ++h) {
@@ -132,6 +133,7 @@ __global__ void __launch_bounds__(256) k_router_gemm_big(RouteParams p) {
       }
     }
     __syncthreads();
+    if (k0 + BK < p.H) fetch(k0 + BK);  // in flight while this chunk is multiplied
 #pragma unroll 8
     for (int kk = 0; kk < BK; ++kk) {
       float a[TMR];
