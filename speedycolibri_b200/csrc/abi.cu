@@ -706,6 +706,7 @@ extern "C" int coli_b200_moe_block_dev(ColiMoe *m, const void *x_dev, void *out_
     fp.n_items = m->n_items;
     fp.max_items = max_items;
     fp.rows_per_item = rpi;
+    fp.items_expected = (rows < m->nseg ? rows : m->nseg) + rows / rpi;
     fp.x = (const __nv_bfloat16 *)x_dev;
     fp.row_token = m->row_token;
     fp.h = m->h;
@@ -893,6 +894,7 @@ static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, cons
   fp.n_items = m->n_items;
   fp.max_items = max_items;
   fp.rows_per_item = rpi;
+  fp.items_expected = (rows_expected < n_seg ? rows_expected : n_seg) + rows_expected / rpi;
   fp.x = (const __nv_bfloat16 *)rows_dev;
   fp.row_token = nullptr;
   fp.h = m->h;
@@ -1049,6 +1051,7 @@ static int run_host_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *u
   fp.n_items = d_nit;
   fp.max_items = max_items;
   fp.rows_per_item = rpi;
+  fp.items_expected = max_items;
   fp.x = (const __nv_bfloat16 *)ctx->buf[1];
   fp.row_token = nullptr;
   fp.h = (__nv_bfloat16 *)ctx->buf[2];

@@ -137,7 +137,10 @@ __device__ __forceinline__ void decode_a(const AFrag<FMT> &f, int m, const uint3
 }
 
 // GATED: two matrices (gate, up) -> h = silu(g)*u;  otherwise one matrix (down) -> y.
-template <int FMT, int NB, bool GATED>
+// SPLITK: the W warps of a CTA share one 16-row tile and split the k-tiles (few work items: a
+// single-token decode); otherwise every warp owns its own 16-row tile over all of K and no
+// cross-warp reduction is needed (enough items to fill the machine).
+template <int FMT, int NB, bool GATED, bool SPLITK>
 __global__ void __launch_bounds__(256) k_ffn_mm(FfnParams p) {
   constexpr int MATS = GATED ? 2 : 1;
   extern __shared__ __align__(16) float red[];  // [W][MATS*NB*4][32]
@@ -149,7 +152,7 @@ __global__ void __launch_bounds__(256) k_ffn_mm(FfnParams p) {
   const int K = GATED ? p.H : p.I;     // contraction length
   const int Oout = GATED ? p.I : p.H;  // output features
   const int Kp = (K + 127) & ~127, KT = Kp >> 7, Op = (Oout + 15) & ~15;
-  const int r0 = blockIdx.x * 16;
+  const int r0 = SPLITK ? blockIdx.x * 16 : (blockIdx.x * W + warp) * 16;
   const int seg = p.item_seg[item], row0 = p.item_row0[item], nrows = p.item_nrows[item];
   const int ex = p.seg_expert ? p.seg_expert[seg] : seg;
   const WeightRef w0 = GATED ? p.gate[ex] : p.down[ex];
@@ -187,93 +190,88 @@ __global__ void __launch_bounds__(256) k_ffn_mm(FfnParams p) {
 #pragma unroll
       for (int c = 0; c < 4; ++c) acc[mtx][j][c] = 0.0f;
 
-  AFrag<FMT> cur[MATS], nxt[MATS];
-  int kt = warp;
-  if (kt < KT) {
-    load_a<FMT>(cur[0], w0, Op, r0, kt, lane);
-    if (GATED) load_a<FMT>(cur[MATS - 1], w1, Op, r0, kt, lane);
+  // Register ring of packed weight fragments, D k-tiles deep.  The loop is unrolled by D so that
+  // every ring slot is a fixed set of registers: rotating slots with copies would make each
+  // iteration wait for the youngest load, i.e. expose the full HBM latency per k-tile.
+  constexpr int D = (FMT == COLI_FMT_NVFP4) ? (NB <= 2 ? 4 : 3) : 2;
+  AFrag<FMT> ring[D][MATS];
+  const int kstep = SPLITK ? W : 1;
+  int kt_first = SPLITK ? warp : 0;
+  if (!SPLITK && r0 >= Op) kt_first = KT;  // this warp's tile lies beyond the matrix
+#pragma unroll
+  for (int j = 0; j < D - 1; ++j) {
+    const int ktl = kt_first + j * kstep;
+    if (ktl < KT) {
+      load_a<FMT>(ring[j][0], w0, Op, r0, ktl, lane);
+      if (GATED) load_a<FMT>(ring[j][MATS - 1], w1, Op, r0, ktl, lane);
+    }
   }
-  for (; kt < KT; kt += W) {
-    const int ktn = kt + W;
-    if (ktn < KT) {
-      load_a<FMT>(nxt[0], w0, Op, r0, ktn, lane);
-      if (GATED) load_a<FMT>(nxt[MATS - 1], w1, Op, r0, ktn, lane);
-    }
-    // token fragments of this k-tile: lane (g,t) reads x[token g][kt*128 + 32t .. +31], 16 bytes
-    // (two MMA steps) at a time
-    const int kbase = kt * 128 + t * 32;
-    float part[MATS][NB][4];
-    if (FMT == COLI_FMT_FP8_B128) {
+  for (int kt0 = kt_first; kt0 < KT; kt0 += D * kstep) {
 #pragma unroll
-      for (int mtx = 0; mtx < MATS; ++mtx)
-#pragma unroll
-        for (int j = 0; j < NB; ++j)
-#pragma unroll
-          for (int c = 0; c < 4; ++c) part[mtx][j][c] = 0.0f;
-    }
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint4 xb[NB];
-#pragma unroll
-      for (int j = 0; j < NB; ++j) {
-        xb[j] = make_uint4(0, 0, 0, 0);
-        if (xrow[j] != nullptr && kbase + c * 8 + 8 <= K)
-          xb[j] = *reinterpret_cast<const uint4 *>(xrow[j] + kbase + c * 8);
+    for (int slot = 0; slot < D; ++slot) {
+      const int kt = kt0 + slot * kstep;
+      if (kt >= KT) break;
+      const int ktn = kt + (D - 1) * kstep;
+      if (ktn < KT) {
+        load_a<FMT>(ring[(slot + D - 1) % D][0], w0, Op, r0, ktn, lane);
+        if (GATED) load_a<FMT>(ring[(slot + D - 1) % D][MATS - 1], w1, Op, r0, ktn, lane);
       }
-#pragma unroll
-      for (int mm = 0; mm < 2; ++mm) {
-        const int m = 2 * c + mm;
-#pragma unroll
-        for (int mtx = 0; mtx < MATS; ++mtx) {
-          uint32_t a[4];
-          decode_a<FMT>(cur[mtx], m, lut, a);
-#pragma unroll
-          for (int j = 0; j < NB; ++j) {
-            const uint32_t b0 = mm ? xb[j].z : xb[j].x, b1 = mm ? xb[j].w : xb[j].y;
-            if (FMT == COLI_FMT_FP8_B128)
-              mma_bf16_16816(part[mtx][j], a, b0, b1);
-            else
-              mma_bf16_16816(acc[mtx][j], a, b0, b1);
+      // token fragments of this k-tile: lane (g,t) reads x[token g][kt*128 + 32t .. +31], 16 bytes
+      // (two MMA steps) at a time
+      const int kbase = kt * 128 + t * 32;
+      float part[MATS][NB][4];
+      if (FMT == COLI_FMT_FP8_B128) {
+  #pragma unroll
+        for (int mtx = 0; mtx < MATS; ++mtx)
+  #pragma unroll
+          for (int j = 0; j < NB; ++j)
+  #pragma unroll
+            for (int c = 0; c < 4; ++c) part[mtx][j][c] = 0.0f;
+      }
+  #pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint4 xb[NB];
+  #pragma unroll
+        for (int j = 0; j < NB; ++j) {
+          xb[j] = make_uint4(0, 0, 0, 0);
+          if (xrow[j] != nullptr && kbase + c * 8 + 8 <= K)
+            xb[j] = *reinterpret_cast<const uint4 *>(xrow[j] + kbase + c * 8);
+        }
+  #pragma unroll
+        for (int mm = 0; mm < 2; ++mm) {
+          const int m = 2 * c + mm;
+  #pragma unroll
+          for (int mtx = 0; mtx < MATS; ++mtx) {
+            uint32_t a[4];
+            decode_a<FMT>(ring[slot][mtx], m, lut, a);
+  #pragma unroll
+            for (int j = 0; j < NB; ++j) {
+              const uint32_t b0 = mm ? xb[j].z : xb[j].x, b1 = mm ? xb[j].w : xb[j].y;
+              if (FMT == COLI_FMT_FP8_B128)
+                mma_bf16_16816(part[mtx][j], a, b0, b1);
+              else
+                mma_bf16_16816(acc[mtx][j], a, b0, b1);
+            }
           }
         }
       }
-    }
-    if (FMT == COLI_FMT_FP8_B128) {
-      // one f32 scale per (128-row block, k-tile): convert.rs:731-741
-#pragma unroll
-      for (int mtx = 0; mtx < MATS; ++mtx) {
-        const float *sc = reinterpret_cast<const float *>(mtx == 0 ? w0.s : w1.s);
-        const float s = sc[(size_t)(r0 >> 7) * KT + kt];
-#pragma unroll
-        for (int j = 0; j < NB; ++j)
-#pragma unroll
-          for (int c = 0; c < 4; ++c) acc[mtx][j][c] = fmaf(s, part[mtx][j][c], acc[mtx][j][c]);
+      if (FMT == COLI_FMT_FP8_B128) {
+        // one f32 scale per (128-row block, k-tile): convert.rs:731-741
+  #pragma unroll
+        for (int mtx = 0; mtx < MATS; ++mtx) {
+          const float *sc = reinterpret_cast<const float *>(mtx == 0 ? w0.s : w1.s);
+          const float s = sc[(size_t)(r0 >> 7) * KT + kt];
+  #pragma unroll
+          for (int j = 0; j < NB; ++j)
+  #pragma unroll
+            for (int c = 0; c < 4; ++c) acc[mtx][j][c] = fmaf(s, part[mtx][j][c], acc[mtx][j][c]);
+        }
       }
     }
-#pragma unroll
-    for (int mtx = 0; mtx < MATS; ++mtx) cur[mtx] = nxt[mtx];
   }
 
-  // cross-warp (split-K) reduction
-  constexpr int NV = MATS * NB * 4;
-#pragma unroll
-  for (int mtx = 0; mtx < MATS; ++mtx)
-#pragma unroll
-    for (int j = 0; j < NB; ++j)
-#pragma unroll
-      for (int c = 0; c < 4; ++c) red[((size_t)warp * NV + (mtx * NB + j) * 4 + c) * 32 + lane] = acc[mtx][j][c];
-  __syncthreads();
-
-  for (int j = warp; j < NB; j += W) {
-    float v[MATS][4];
-#pragma unroll
-    for (int mtx = 0; mtx < MATS; ++mtx)
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        float s = 0.0f;
-        for (int w = 0; w < W; ++w) s += red[((size_t)w * NV + (mtx * NB + j) * 4 + c) * 32 + lane];
-        v[mtx][c] = s;
-      }
+  // epilogue of one 8-token block given its reduced accumulators
+  auto emit = [&](int j, const float (&v)[MATS][4]) {
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       const int orow = r0 + g + ((c & 2) ? 8 : 0);  // output feature
@@ -299,23 +297,71 @@ __global__ void __launch_bounds__(256) k_ffn_mm(FfnParams p) {
           p.y[row * p.H + orow] = __float2bfloat16_rn(v[0][c] * s0);
       }
     }
+  };
+
+  if (!SPLITK) {
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+      float v[MATS][4];
+#pragma unroll
+      for (int mtx = 0; mtx < MATS; ++mtx)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) v[mtx][c] = acc[mtx][j][c];
+      emit(j, v);
+    }
+    return;
+  }
+
+  // cross-warp (split-K) reduction
+  constexpr int NV = MATS * NB * 4;
+#pragma unroll
+  for (int mtx = 0; mtx < MATS; ++mtx)
+#pragma unroll
+    for (int j = 0; j < NB; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) red[((size_t)warp * NV + (mtx * NB + j) * 4 + c) * 32 + lane] = acc[mtx][j][c];
+  __syncthreads();
+
+  for (int j = warp; j < NB; j += W) {
+    float v[MATS][4];
+#pragma unroll
+    for (int mtx = 0; mtx < MATS; ++mtx)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float s = 0.0f;
+        for (int w = 0; w < W; ++w) s += red[((size_t)w * NV + (mtx * NB + j) * 4 + c) * 32 + lane];
+        v[mtx][c] = s;
+      }
+    emit(j, v);
   }
 }
 
+
 static int pick_w(int KT) { return KT >= 8 ? 8 : KT >= 4 ? 4 : KT >= 2 ? 2 : 1; }
 
+// Split K across the warps of a CTA only when there are too few (item, row tile) tasks to fill
+// the SMs with one warp each; `p.items_expected` is a host-side estimate from shapes alone.
 template <int FMT, int NB>
 static int launch_one(const FfnParams &p, bool gated, cudaStream_t st) {
-  if (gated) {
-    const int KT = (p.H + 127) / 128, W = pick_w(KT);
-    dim3 grid((p.I + 15) / 16, p.max_items);
-    const size_t sm = (size_t)W * 2 * NB * 4 * 32 * sizeof(float);
-    k_ffn_mm<FMT, NB, true><<<grid, W * 32, sm, st>>>(p);
+  const int K = gated ? p.H : p.I, O = gated ? p.I : p.H;
+  const int KT = (K + 127) / 128, row_tiles = (O + 15) / 16;
+  const long tasks = (long)row_tiles * (p.items_expected > 0 ? p.items_expected : 1);
+  const bool splitk = tasks < 148L * 12;
+  if (splitk) {
+    const int W = pick_w(KT);
+    dim3 grid(row_tiles, p.max_items);
+    const size_t sm = (size_t)W * (gated ? 2 : 1) * NB * 4 * 32 * sizeof(float);
+    if (gated)
+      k_ffn_mm<FMT, NB, true, true><<<grid, W * 32, sm, st>>>(p);
+    else
+      k_ffn_mm<FMT, NB, false, true><<<grid, W * 32, sm, st>>>(p);
   } else {
-    const int KT = (p.I + 127) / 128, W = pick_w(KT);
-    dim3 grid((p.H + 15) / 16, p.max_items);
-    const size_t sm = (size_t)W * 1 * NB * 4 * 32 * sizeof(float);
-    k_ffn_mm<FMT, NB, false><<<grid, W * 32, sm, st>>>(p);
+    const int W = 4;  // four 16-row tiles per CTA
+    dim3 grid((row_tiles + W - 1) / W, p.max_items);
+    if (gated)
+      k_ffn_mm<FMT, NB, true, false><<<grid, W * 32, 0, st>>>(p);
+    else
+      k_ffn_mm<FMT, NB, false, false><<<grid, W * 32, 0, st>>>(p);
   }
   coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "expert ffn launch") ? 1 : 0;

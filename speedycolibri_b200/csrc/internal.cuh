@@ -114,6 +114,7 @@ struct FfnParams {
   const int32_t *item_seg, *item_row0, *item_nrows, *n_items;
   int max_items;
   int rows_per_item;         // rows per work item the list was cut with (<= 32)
+  int items_expected;        // host estimate of the work items (selects split-K vs tile-per-warp)
   const __nv_bfloat16 *x;    // source rows
   const int32_t *row_token;  // row -> source row index (null = identity)
   __nv_bfloat16 *h;          // [rows, I] scratch

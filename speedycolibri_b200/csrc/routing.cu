@@ -359,7 +359,7 @@ int launch_router(const RouteParams &p, cudaStream_t st) {
       cudaFuncSetAttribute(k_router_decode, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
       attr_set = true;
     }
-    k_router_decode<<<(p.E + 7) / 8, 64 * ((p.T * 8 + 63) / 64), dec_smem, st>>>(p);
+    k_router_decode<<<(p.E + 7) / 8, 256, dec_smem, st>>>(p);  // 256 threads stage the rows, T*8 of them walk the chains
     coli_count_launch(1);
   } else {
     // the largest tile that still gives ~one CTA per SM; every variant has identical arithmetic
@@ -496,6 +496,88 @@ __global__ void __launch_bounds__(256) k_permute(PermuteParams p) {
   }
 }
 
+// Decode-sized batches (T*k <= 1024 pairs): count, scan, work list and row positions in ONE
+// single-CTA launch instead of three (each launch costs about as much as the whole decode GEMV).
+// Same stable order as the three-kernel path: positions ascend with the token inside an expert.
+__global__ void __launch_bounds__(1024) k_permute_small(PermuteParams p, int max_items) {
+  __shared__ int cnt[1024 + 1];
+  __shared__ int off[1024 + 2];
+  __shared__ int rank_sm[1024];
+  const int E = p.E, nrt = p.nseg_routed, nseg = nrt + (p.has_shared ? 1 : 0);
+  const int npairs = p.T * p.k;
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  if (threadIdx.x < 32) {  // one warp walks the tokens in order; lane kk owns pair (t, kk)
+    for (int t = 0; t < p.T; ++t) {
+      if ((int)threadIdx.x < p.k) {
+        const int e = p.topk_idx[t * p.k + threadIdx.x];
+        const int s = p.expert_slot ? p.expert_slot[e] : e;
+        if (s >= 0) {
+          rank_sm[t * p.k + threadIdx.x] = cnt[s];
+          cnt[s] += 1;
+        }
+      }
+      __syncwarp();
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (p.has_shared) cnt[nrt] = p.T;
+    int run = 0, items = 0;
+    for (int s = 0; s < nseg; ++s) {
+      off[s] = run;
+      const int n = cnt[s];
+      for (int r = 0; r < n; r += p.rows_per_item) {
+        if (items < max_items) {
+          p.item_seg[items] = s;
+          p.item_row0[items] = run + r;
+          p.item_nrows[items] = min(p.rows_per_item, n - r);
+        }
+        ++items;
+      }
+      run += n;
+    }
+    off[nseg] = run;
+    *p.n_items = min(items, max_items);
+  }
+  __syncthreads();
+  for (int s = threadIdx.x; s <= nseg; s += blockDim.x) p.seg_off[s] = off[s];
+  for (int s = threadIdx.x; s < nrt; s += blockDim.x) p.seg_count[s] = cnt[s];
+  for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
+    const int e = p.topk_idx[i];
+    const int s = p.expert_slot ? p.expert_slot[e] : e;
+    if (s < 0) {
+      p.slot[i] = -1;
+      continue;
+    }
+    const int pos = off[s] + rank_sm[i];
+    p.slot[i] = pos;
+    p.row_token[pos] = i / p.k;
+  }
+  if (p.has_shared)
+    for (int t = threadIdx.x; t < p.T; t += blockDim.x) p.row_token[off[nrt] + t] = t;
+  if (p.xg) {  // gather rows: one warp per row
+    const int total = npairs + ((p.has_shared && p.gather_shared) ? p.T : 0);
+    const int vec = p.H / 8;
+    for (int r = threadIdx.x >> 5; r < total; r += blockDim.x >> 5) {
+      int t, pos;
+      if (r < npairs) {
+        const int e = p.topk_idx[r];
+        const int s = p.expert_slot ? p.expert_slot[e] : e;
+        if (s < 0) continue;
+        t = r / p.k;
+        pos = off[s] + rank_sm[r];
+      } else {
+        t = r - npairs;
+        pos = off[nrt] + t;
+      }
+      const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (size_t)t * p.H);
+      uint4 *dst = reinterpret_cast<uint4 *>(p.xg + (size_t)pos * p.H);
+      for (int c = threadIdx.x & 31; c < vec; c += 32) dst[c] = src[c];
+    }
+  }
+}
+
 int launch_permute(const PermuteParams &p, cudaStream_t st) {
   if (p.T <= 0) return 1;
   if (p.E > 1024) {
@@ -505,6 +587,11 @@ int launch_permute(const PermuteParams &p, cudaStream_t st) {
   const int nchunk = (p.T + 31) / 32;
   const int nseg = p.nseg_routed + (p.has_shared ? 1 : 0);
   const int max_items = (p.T * p.k + (p.has_shared ? p.T : 0)) / p.rows_per_item + nseg;
+  if (p.T * p.k <= 1024 && p.k <= 32) {
+    k_permute_small<<<1, 1024, 0, st>>>(p, max_items);
+    coli_count_launch(1);
+    return coli_cuda_check(cudaGetLastError(), "permute launch") ? 1 : 0;
+  }
   k_seg_count<<<(nchunk + 3) / 4, 128, (size_t)4 * p.E * sizeof(int), st>>>(p, nchunk);
   coli_count_launch(1);
   k_seg_scan<<<1, 1024, 0, st>>>(p, nchunk, max_items);
