@@ -351,8 +351,10 @@ struct ColiMoe {
   int32_t *topk_idx, *local_rank, *chunk_cnt, *seg_count, *seg_off, *slot, *row_token;
   int32_t *item_seg, *item_row0, *item_nrows, *n_items;
   int item_cap;
-  __nv_bfloat16 *h, *y, *x_stage, *out_stage;
-  __nv_bfloat16 *xg;  // gathered rows for the tcgen05 path (null when max_tokens never reaches it)
+  __nv_bfloat16 *y, *x_stage, *out_stage;
+  __half *h;    // intermediate rows of the expert FFN
+  __half *x16;  // token-order f16 copy of the activations (small-batch path, shared expert stage)
+  __half *xg;   // gathered f16 rows for the tcgen05 path (null when max_tokens never reaches it)
   int *status;        // device status word of the tcgen05 kernels
   int sm_count;
   size_t h_rows_cap;  // rows the h scratch holds
@@ -526,7 +528,7 @@ extern "C" int coli_b200_moe_create(ColiMoe **out, const ColiMoeLayer *L, int ma
        ws_alloc(m, &m->row_token, rows) && ws_alloc(m, &m->item_seg, m->item_cap) &&
        ws_alloc(m, &m->item_row0, m->item_cap) && ws_alloc(m, &m->item_nrows, m->item_cap) && ws_alloc(m, &m->n_items, 1) &&
        ws_alloc(m, &m->h, rows * I) && ws_alloc(m, &m->y, rows * H) && ws_alloc(m, &m->x_stage, T * H) &&
-       ws_alloc(m, &m->out_stage, T * H);
+       ws_alloc(m, &m->out_stage, T * H) && ws_alloc(m, &m->x16, T * H);
   m->h_rows_cap = rows;
   m->xg = nullptr;
   m->status = nullptr;
@@ -636,8 +638,9 @@ static colib::PermuteParams permute_params(ColiMoe *m, const void *x_dev, int T,
   pp.item_nrows = m->item_nrows;
   pp.n_items = m->n_items;
   pp.x = (const __nv_bfloat16 *)x_dev;
-  pp.xg = (__nv_bfloat16 *)rows_dev;
+  pp.xg = (__half *)rows_dev;
   pp.gather_shared = 0;
+  pp.x16 = nullptr;
   return pp;
 }
 
@@ -669,6 +672,7 @@ extern "C" int coli_b200_moe_block_dev(ColiMoe *m, const void *x_dev, void *out_
   {
     colib::PermuteParams pp = permute_params(m, x_dev, T, m->has_shared, rpi, tc ? m->xg : nullptr, m->seg_count, m->slot);
     pp.gather_shared = tc ? 1 : 0;
+    pp.x16 = tc ? nullptr : m->x16;
     if (!colib::launch_permute(pp, st)) return 0;
   }
   COLI_MARK(2);
@@ -707,7 +711,7 @@ extern "C" int coli_b200_moe_block_dev(ColiMoe *m, const void *x_dev, void *out_
     fp.max_items = max_items;
     fp.rows_per_item = rpi;
     fp.items_expected = (rows < m->nseg ? rows : m->nseg) + rows / rpi;
-    fp.x = (const __nv_bfloat16 *)x_dev;
+    fp.x = m->x16;
     fp.row_token = m->row_token;
     fp.h = m->h;
     fp.y = m->y;
@@ -834,10 +838,10 @@ extern "C" int coli_b200_moe_gather_local_dev(ColiMoe *m, const void *x_dev, con
 static bool ensure_h(ColiMoe *m, size_t rows) {
   if (rows <= m->h_rows_cap) return true;
   if (!coli_cuda_check(cudaDeviceSynchronize(), "scratch regrow sync")) return false;
-  __nv_bfloat16 *nh = nullptr;
-  if (!coli_cuda_check(cudaMalloc((void **)&nh, rows * m->L.I * sizeof(__nv_bfloat16)), "scratch regrow")) return false;
+  __half *nh = nullptr;
+  if (!coli_cuda_check(cudaMalloc((void **)&nh, rows * m->L.I * sizeof(__half)), "scratch regrow")) return false;
   m->allocs.push_back(nh);  // the old block is released with the handle
-  m->ws_bytes += rows * m->L.I * sizeof(__nv_bfloat16);
+  m->ws_bytes += rows * m->L.I * sizeof(__half);
   m->h = nh;
   m->h_rows_cap = rows;
   return true;
@@ -895,7 +899,7 @@ static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, cons
   fp.max_items = max_items;
   fp.rows_per_item = rpi;
   fp.items_expected = (rows_expected < n_seg ? rows_expected : n_seg) + rows_expected / rpi;
-  fp.x = (const __nv_bfloat16 *)rows_dev;
+  fp.x = (const __half *)rows_dev;
   fp.row_token = nullptr;
   fp.h = m->h;
   fp.y = (__nv_bfloat16 *)y_dev;
@@ -925,7 +929,8 @@ extern "C" int coli_b200_moe_shared_dev(ColiMoe *m, const void *x_dev, int T, vo
   // one segment of T rows; its count lives in seg_count[E]
   if (!coli_cuda_check(cudaMemcpyAsync(m->seg_count + m->L.E, &T, sizeof(int32_t), cudaMemcpyHostToDevice, st), "shared count"))
     return 0;
-  return run_segments(m, m->gate + m->L.E, m->up + m->L.E, m->down + m->L.E, nullptr, x_dev, m->seg_count + m->L.E, 1, T, T, y_dev, st);
+  if (!colib::launch_bf16_to_f16((const __nv_bfloat16 *)x_dev, m->x16, (size_t)T * m->L.H, st)) return 0;
+  return run_segments(m, m->gate + m->L.E, m->up + m->L.E, m->down + m->L.E, nullptr, m->x16, m->seg_count + m->L.E, 1, T, T, y_dev, st);
 }
 
 extern "C" int coli_b200_moe_combine_partial_dev(ColiMoe *m, const void *y_rows_dev, const int32_t *slot_dev,
@@ -980,7 +985,8 @@ extern "C" uint64_t coli_b200_sharding_fingerprint(uint32_t num_nodes, uint32_t 
 // ---- the reference's host-pointer expert calls -------------------------------------------------------
 // Same contract as backend_cuda.cu:3668-3806 / 4410-4792 (host f32 in, host f32 out, synchronous,
 // one mutex per device held across the call).  Activations are rounded to bf16 on the device
-// (the kernels are W4A16 / W8A16 with bf16 activations); outputs are written as f32.
+// (the kernels are W4A16 / W8A16 with bf16 activation values, held in f16 for the MMA); outputs
+// are written as f32.
 static int run_host_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups, ColiCudaTensor *const *downs,
                           const int *rows, int count, float *y, const float *x, int want_fmt_a, int want_fmt_b,
                           const char *who) {
@@ -1013,10 +1019,10 @@ static int run_host_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *u
   const int rpi = avg <= 8 ? 8 : avg <= 16 ? 16 : 32;
   const int max_items = (int)(total / rpi) + count;
   const size_t xb = (size_t)total * D;
-  // slots: 0 x f32 / y f32, 1 x bf16, 2 h bf16, 3 tables + counts + work list
+  // slots: 0 x f32 / y f32, 1 x f16, 2 h f16, 3 tables + counts + work list
   const size_t tbl_bytes = sizeof(WeightRef) * 3 * count + sizeof(int32_t) * (2 * count + 2 + 3 * (size_t)max_items + 1);
-  if (!reserve(ctx, 0, xb * sizeof(float)) || !reserve(ctx, 1, xb * sizeof(__nv_bfloat16)) ||
-      !reserve(ctx, 2, (size_t)total * I * sizeof(__nv_bfloat16)) || !reserve(ctx, 3, tbl_bytes))
+  if (!reserve(ctx, 0, xb * sizeof(float)) || !reserve(ctx, 1, xb * sizeof(__half)) ||
+      !reserve(ctx, 2, (size_t)total * I * sizeof(__half)) || !reserve(ctx, 3, tbl_bytes))
     return 0;
   std::vector<WeightRef> tbl(3 * (size_t)count);
   for (int c = 0; c < count; ++c) {
@@ -1035,7 +1041,7 @@ static int run_host_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *u
   CK(cudaMemcpyAsync(d_tbl, tbl.data(), sizeof(WeightRef) * tbl.size(), cudaMemcpyHostToDevice, st), "expert table upload");
   CK(cudaMemcpyAsync(d_cnt, rows, sizeof(int32_t) * count, cudaMemcpyHostToDevice, st), "row count upload");
   CK(cudaStreamSynchronize(st), "expert upload sync");  // tbl is a local; rows/x belong to the caller
-  if (!colib::launch_f32_to_bf16((const float *)ctx->buf[0], (__nv_bfloat16 *)ctx->buf[1], xb, st)) return 0;
+  if (!colib::launch_f32_to_f16_via_bf16((const float *)ctx->buf[0], (__half *)ctx->buf[1], xb, st)) return 0;
   if (!colib::launch_items_from_counts(d_cnt, count, rpi, d_off, d_iseg, d_irow, d_inr, d_nit, st)) return 0;
   colib::FfnParams fp;
   fp.fmt = fmt;
@@ -1052,9 +1058,9 @@ static int run_host_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *u
   fp.max_items = max_items;
   fp.rows_per_item = rpi;
   fp.items_expected = max_items;
-  fp.x = (const __nv_bfloat16 *)ctx->buf[1];
+  fp.x = (const __half *)ctx->buf[1];
   fp.row_token = nullptr;
-  fp.h = (__nv_bfloat16 *)ctx->buf[2];
+  fp.h = (__half *)ctx->buf[2];
   fp.y = nullptr;
   fp.y32 = (float *)ctx->buf[0];  // x f32 is dead once converted
   if (!colib::launch_ffn_small(fp, st)) return 0;

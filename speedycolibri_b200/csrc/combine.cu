@@ -109,6 +109,35 @@ int launch_f32_to_bf16(const float *src, __nv_bfloat16 *dst, size_t n, cudaStrea
   return coli_cuda_check(cudaGetLastError(), "f32->bf16 launch") ? 1 : 0;
 }
 
+__global__ void k_f32_to_f16_via_bf16(const float *src, __half *dst, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    dst[i] = coli_f32_to_f16_via_bf16(src[i]);
+}
+int launch_f32_to_f16_via_bf16(const float *src, __half *dst, size_t n, cudaStream_t st) {
+  if (n == 0) return 1;
+  const size_t blocks = (n + 255) / 256;
+  k_f32_to_f16_via_bf16<<<(unsigned)(blocks > 4736 ? 4736 : blocks), 256, 0, st>>>(src, dst, n);
+  coli_count_launch(1);
+  return coli_cuda_check(cudaGetLastError(), "f32->f16 launch") ? 1 : 0;
+}
+// n must be a multiple of 8 (rows of H elements, H % 8 == 0)
+__global__ void k_bf16_to_f16(const uint4 *src, uint4 *dst, size_t n8) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x)
+    dst[i] = coli_bf16x8_to_f16x8(src[i]);
+}
+int launch_bf16_to_f16(const __nv_bfloat16 *src, __half *dst, size_t n, cudaStream_t st) {
+  if (n == 0) return 1;
+  if (n % 8) {
+    coli_set_error("bf16->f16: element count %zu is not a multiple of 8", n);
+    return 0;
+  }
+  const size_t n8 = n / 8, blocks = (n8 + 255) / 256;
+  k_bf16_to_f16<<<(unsigned)(blocks > 4736 ? 4736 : blocks), 256, 0, st>>>(reinterpret_cast<const uint4 *>(src),
+                                                                           reinterpret_cast<uint4 *>(dst), n8);
+  coli_count_launch(1);
+  return coli_cuda_check(cudaGetLastError(), "bf16->f16 launch") ? 1 : 0;
+}
+
 __global__ void k_matmul_f32_seq(const float *x, const float *w, float *y, int S, int I, int O) {
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (size_t)S * O) return;

@@ -1,20 +1,22 @@
 // Expert FFN for decode-sized segments: a weight-streaming dequant-GEMV/GEMM in which every
-// weight byte is read from HBM exactly once per work item with 128-bit loads, decoded to
-// bf16 in registers, and contracted against up to 32 token rows with warp-level bf16 MMA
+// weight byte is read from HBM exactly once per work item with 128-bit loads, converted to
+// f16 in registers (one hardware cvt per pair of FP4 or FP8 codes, one half2 multiply by the
+// block scale for NVFP4), and contracted against up to 32 token rows with warp-level f16 MMA
 // (m16n8k16, f32 accumulate).  The path is HBM-bound: the MMA only takes the multiply-adds
-// off the CUDA cores so that the decode arithmetic (about 2.5 integer/half2 operations per
-// FP4 weight) is all the SM has to issue per byte streamed.
+// off the CUDA cores so that the decode arithmetic (about one operation per FP4 weight) is
+// all the SM has to issue per byte streamed.
 //
 // It replaces the reference's per-expert launch trios nvfp4_gemv / nvfp4_wsmm / fp8a16_gemv
 // (crates/colibri-backend/cuda/backend_cuda.cu:707-1110,1436-1510,468-496, dispatched from
 // 4738-4783) with two launches for ALL experts of a layer: gate+up with SiLU*mul fused
 // (the reference runs `silu_mul` as a separate launch, backend_cuda.cu:3785-3787), then down.
 //
-// Numerics (W4A16 as in crates/colibri-engine/src/linear.rs:110-133): activations stay bf16
-// (exact), a decoded weight E2M1*ue4m3 has at most 6 significant bits and is exact in bf16, so
+// Numerics (W4A16 as in crates/colibri-engine/src/linear.rs:110-133): activations are the bf16
+// values held in f16 (exact in [2^-14, 65504]), a decoded weight E2M1*ue4m3 has at most 6
+// significant bits and is exact in f16, so
 // each product is exact and only the f32 summation order differs from the CPU sum.  The
 // per-tensor scale is applied once per output, as the reference does.  The intermediate
-// h = silu(g)*u is rounded to bf16 before the down projection.
+// h = silu(g)*u is rounded to bf16 (then held in f16) before the down projection.
 //
 // Work decomposition: grid = (row tiles of 16 outputs, work items); an item is at most 8*NB
 // consecutive rows of one expert segment.  The W warps of a CTA split the K axis (k-tile kt
@@ -24,15 +26,15 @@
 
 namespace colib {
 
-__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ uint32_t hmul2_bf16(uint32_t a, uint32_t b) {
+__device__ __forceinline__ uint32_t hmul2_f16(uint32_t a, uint32_t b) {
   uint32_t d;
-  asm("mul.rn.bf16x2 %0, %1, %2;\n" : "=r"(d) : "r"(a), "r"(b));
+  asm("mul.rn.f16x2 %0, %1, %2;\n" : "=r"(d) : "r"(a), "r"(b));
   return d;
 }
 __device__ __forceinline__ uint4 ldg_nc_v4(const void *p) {
@@ -43,44 +45,34 @@ __device__ __forceinline__ uint4 ldg_nc_v4(const void *p) {
   return v;
 }
 
-// A NVFP4 word holds 8 consecutive k: even elements in nibble slots 0..3, odd in slots 4..7.
-// Placing the three magnitude bits e,e,m of a nibble at bf16 bits 8..6 yields the E2M1 value
-// times 2^-126 (a bf16 subnormal for 0.5); `mult` = ue4m3 scale * 2^110 in both halves brings
-// the pair to weight * 2^-16 exactly.  Pair p = elements (2p, 2p+1).
-template <int P>
-__device__ __forceinline__ uint32_t fp4_pair(uint32_t w, uint32_t mult) {
-  uint32_t mag, sgn;
-  if (P == 0) {
-    mag = (w << 6) & 0x01C001C0u;
-    sgn = (w << 12) & 0x80008000u;
-  } else if (P == 1) {
-    mag = (w << 2) & 0x01C001C0u;
-    sgn = (w << 8) & 0x80008000u;
-  } else if (P == 2) {
-    mag = (w >> 2) & 0x01C001C0u;
-    sgn = (w << 4) & 0x80008000u;
-  } else {
-    mag = (w >> 6) & 0x01C001C0u;
-    sgn = w & 0x80008000u;
-  }
-  return hmul2_bf16(mag | sgn, mult);
+// Two bytes of a NVFP4 word (each byte = two consecutive k, low nibble first) -> two f16x2.
+// HI selects bytes 2,3 of the word, otherwise bytes 0,1.
+template <bool HI>
+__device__ __forceinline__ void cvt_e2m1x4(uint32_t w, uint32_t &p0, uint32_t &p1) {
+  if (HI)
+    asm("{ .reg .b8 b0, b1, b2, b3;\n"
+        "  mov.b32 {b0, b1, b2, b3}, %2;\n"
+        "  cvt.rn.f16x2.e2m1x2 %0, b2;\n"
+        "  cvt.rn.f16x2.e2m1x2 %1, b3; }\n"
+        : "=r"(p0), "=r"(p1)
+        : "r"(w));
+  else
+    asm("{ .reg .b8 b0, b1, b2, b3;\n"
+        "  mov.b32 {b0, b1, b2, b3}, %2;\n"
+        "  cvt.rn.f16x2.e2m1x2 %0, b0;\n"
+        "  cvt.rn.f16x2.e2m1x2 %1, b1; }\n"
+        : "=r"(p0), "=r"(p1)
+        : "r"(w));
 }
-// An FP8 word holds bytes [k0, k2, k1, k3].  An e4m3 byte s.eeee.mmm placed at bf16 bits
-// 15 | 10..4 is the value times 2^-120; the multiply by 2^120 normalises it exactly.
-template <int P>
-__device__ __forceinline__ uint32_t fp8_pair(uint32_t w) {
-  uint32_t mag, sgn;
-  if (P == 0) {
-    mag = (w << 4) & 0x07F007F0u;
-    sgn = (w << 8) & 0x80008000u;
-  } else {
-    mag = (w >> 4) & 0x07F007F0u;
-    sgn = w & 0x80008000u;
-  }
-  return hmul2_bf16(mag | sgn, 0x7B807B80u);  // bf16 2^120 in both halves
+// One FP8 word (four consecutive k) -> two f16x2; also used for a pair of ue4m3 block scales.
+__device__ __forceinline__ void cvt_e4m3x4(uint32_t w, uint32_t &p0, uint32_t &p1) {
+  asm("{ .reg .b16 h0, h1;\n"
+      "  mov.b32 {h0, h1}, %2;\n"
+      "  cvt.rn.f16x2.e4m3x2 %0, h0;\n"
+      "  cvt.rn.f16x2.e4m3x2 %1, h1; }\n"
+      : "=r"(p0), "=r"(p1)
+      : "r"(w));
 }
-
-constexpr float kFp4AccScale = 65536.0f;  // undoes the 2^-16 carried by decoded NVFP4 weights
 
 template <int FMT>
 struct AFrag {
@@ -109,230 +101,263 @@ __device__ __forceinline__ void load_a(AFrag<FMT> &f, const WeightRef &w, int Op
   }
 }
 
+// Per k-tile: the lane's four block scales (rows g and g+8, two 16-k blocks each) as f16x2
+// with the scale in both halves.
+struct AScale {
+  uint32_t lo[2], hi[2];
+};
+template <int FMT>
+__device__ __forceinline__ AScale decode_scales(const AFrag<FMT> &f) {
+  AScale r;
+  if (FMT == COLI_FMT_NVFP4) {
+    uint32_t sl, sh;
+    cvt_e4m3x4(f.sc, sl, sh);  // (s_blk0, s_blk1) of row g; of row g+8
+    r.lo[0] = __byte_perm(sl, sl, 0x1010);
+    r.lo[1] = __byte_perm(sl, sl, 0x3232);
+    r.hi[0] = __byte_perm(sh, sh, 0x1010);
+    r.hi[1] = __byte_perm(sh, sh, 0x3232);
+  } else {
+    r.lo[0] = r.lo[1] = r.hi[0] = r.hi[1] = 0;
+  }
+  return r;
+}
+
 // Decode the fragment of MMA step m (0..7) of a k-tile: a[0],a[2] = row g pairs, a[1],a[3] = row g+8.
 template <int FMT>
-__device__ __forceinline__ void decode_a(const AFrag<FMT> &f, int m, const uint32_t *lut, uint32_t (&a)[4]) {
+__device__ __forceinline__ void decode_a(const AFrag<FMT> &f, const AScale &sc, int m, uint32_t (&a)[4]) {
   if (FMT == COLI_FMT_NVFP4) {
     const uint32_t wl = (&f.lo[0].x)[m >> 1], wh = (&f.hi[0].x)[m >> 1];
-    const uint32_t ml = lut[(f.sc >> ((m >> 2) * 8)) & 0xffu];
-    const uint32_t mh = lut[(f.sc >> (16 + (m >> 2) * 8)) & 0xffu];
+    uint32_t l0, l1, h0, h1;
     if (m & 1) {
-      a[0] = fp4_pair<2>(wl, ml);
-      a[2] = fp4_pair<3>(wl, ml);
-      a[1] = fp4_pair<2>(wh, mh);
-      a[3] = fp4_pair<3>(wh, mh);
+      cvt_e2m1x4<true>(wl, l0, l1);
+      cvt_e2m1x4<true>(wh, h0, h1);
     } else {
-      a[0] = fp4_pair<0>(wl, ml);
-      a[2] = fp4_pair<1>(wl, ml);
-      a[1] = fp4_pair<0>(wh, mh);
-      a[3] = fp4_pair<1>(wh, mh);
+      cvt_e2m1x4<false>(wl, l0, l1);
+      cvt_e2m1x4<false>(wh, h0, h1);
     }
+    const uint32_t ml = sc.lo[m >> 2], mh = sc.hi[m >> 2];
+    a[0] = hmul2_f16(l0, ml);
+    a[2] = hmul2_f16(l1, ml);
+    a[1] = hmul2_f16(h0, mh);
+    a[3] = hmul2_f16(h1, mh);
   } else {
     const uint32_t wl = (&f.lo[m >> 2].x)[m & 3], wh = (&f.hi[m >> 2].x)[m & 3];
-    a[0] = fp8_pair<0>(wl);
-    a[2] = fp8_pair<1>(wl);
-    a[1] = fp8_pair<0>(wh);
-    a[3] = fp8_pair<1>(wh);
+    cvt_e4m3x4(wl, a[0], a[2]);
+    cvt_e4m3x4(wh, a[1], a[3]);
   }
 }
 
 // GATED: two matrices (gate, up) -> h = silu(g)*u;  otherwise one matrix (down) -> y.
-// SPLITK: the W warps of a CTA share one 16-row tile and split the k-tiles (few work items: a
-// single-token decode); otherwise every warp owns its own 16-row tile over all of K and no
-// cross-warp reduction is needed (enough items to fill the machine).
+// SPLITK: grid = (row tiles, work items); the W warps of a CTA share one 16-row tile and split
+// the k-tiles (few work items: a single-token decode).  Otherwise the grid is one-dimensional
+// and sized to what is resident at once; every warp walks (item, row tile) tasks with a stride,
+// owns its tile over all of K and needs no cross-warp reduction.
 template <int FMT, int NB, bool GATED, bool SPLITK>
-__global__ void __launch_bounds__(256) k_ffn_mm(FfnParams p) {
+__global__ void __launch_bounds__(SPLITK ? 256 : 64, SPLITK                  ? 1
+                                                      : FMT == COLI_FMT_NVFP4 ? (NB == 1 ? 10 : NB == 2 ? 8 : 4)
+                                                                              : (NB == 1 ? 7 : NB == 2 ? 5 : 4))
+    k_ffn_mm(FfnParams p) {
   constexpr int MATS = GATED ? 2 : 1;
+  // weight ring depth (k-tiles) and token-fragment ring depth (quarter k-tiles)
+  constexpr int D = 2;
+  constexpr int R = NB <= 2 ? 4 : 2;
+  constexpr int PF = R - 1;
   extern __shared__ __align__(16) float red[];  // [W][MATS*NB*4][32]
-  __shared__ uint32_t lut[256];
-  const int item = blockIdx.y;
-  if (item >= *p.n_items) return;
+  const int n_items = *p.n_items;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int K = GATED ? p.H : p.I;     // contraction length
   const int Oout = GATED ? p.I : p.H;  // output features
   const int Kp = (K + 127) & ~127, KT = Kp >> 7, Op = (Oout + 15) & ~15;
-  const int r0 = SPLITK ? blockIdx.x * 16 : (blockIdx.x * W + warp) * 16;
-  const int seg = p.item_seg[item], row0 = p.item_row0[item], nrows = p.item_nrows[item];
-  const int ex = p.seg_expert ? p.seg_expert[seg] : seg;
-  const WeightRef w0 = GATED ? p.gate[ex] : p.down[ex];
-  const WeightRef w1 = GATED ? p.up[ex] : w0;
+  const int row_tiles = Op >> 4;
+  const __half *src = GATED ? p.x : p.h;
 
-  if (FMT == COLI_FMT_NVFP4) {
-    for (int b = threadIdx.x; b < 256; b += blockDim.x) {
-      const float s = coli_e4m3_to_f32((uint8_t)b) * 1.2980742146337069e33f;  // * 2^110
-      const uint32_t h = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(s));
-      lut[b] = h | (h << 16);
-    }
-    __syncthreads();
-  }
+  int task = SPLITK ? (int)blockIdx.y * row_tiles + (int)blockIdx.x : (int)blockIdx.x * W + warp;
+  const int task_stride = SPLITK ? 0x40000000 : (int)gridDim.x * W;
+  const int n_tasks = n_items * row_tiles;
+  for (; task < n_tasks; task += task_stride) {
+    const int item = task / row_tiles, r0 = (task - item * row_tiles) * 16;
+    const int seg = p.item_seg[item], row0 = p.item_row0[item], nrows = p.item_nrows[item];
+    const int ex = p.seg_expert ? p.seg_expert[seg] : seg;
+    const WeightRef w0 = GATED ? p.gate[ex] : p.down[ex];
+    const WeightRef w1 = GATED ? p.up[ex] : w0;
 
-  // source row of token column g of each 8-token block (nullptr = column beyond the item)
-  const __nv_bfloat16 *src = GATED ? p.x : p.h;
-  const __nv_bfloat16 *xrow[NB];
+    // source row of token column g of each 8-token block (nullptr = column beyond the item)
+    const __half *xrow[NB];
 #pragma unroll
-  for (int j = 0; j < NB; ++j) {
-    const int r = 8 * j + g;
-    if (r < nrows) {
-      const int row = row0 + r;
-      const size_t sidx = (GATED && p.row_token) ? (size_t)p.row_token[row] : (size_t)row;
-      xrow[j] = src + sidx * K;
-    } else {
-      xrow[j] = nullptr;
-    }
-  }
-
-  float acc[MATS][NB][4];
-#pragma unroll
-  for (int mtx = 0; mtx < MATS; ++mtx)
-#pragma unroll
-    for (int j = 0; j < NB; ++j)
-#pragma unroll
-      for (int c = 0; c < 4; ++c) acc[mtx][j][c] = 0.0f;
-
-  // Register ring of packed weight fragments, D k-tiles deep.  The loop is unrolled by D so that
-  // every ring slot is a fixed set of registers: rotating slots with copies would make each
-  // iteration wait for the youngest load, i.e. expose the full HBM latency per k-tile.
-  constexpr int D = (FMT == COLI_FMT_NVFP4) ? (NB <= 2 ? 4 : 3) : 2;
-  AFrag<FMT> ring[D][MATS];
-  const int kstep = SPLITK ? W : 1;
-  int kt_first = SPLITK ? warp : 0;
-  if (!SPLITK && r0 >= Op) kt_first = KT;  // this warp's tile lies beyond the matrix
-#pragma unroll
-  for (int j = 0; j < D - 1; ++j) {
-    const int ktl = kt_first + j * kstep;
-    if (ktl < KT) {
-      load_a<FMT>(ring[j][0], w0, Op, r0, ktl, lane);
-      if (GATED) load_a<FMT>(ring[j][MATS - 1], w1, Op, r0, ktl, lane);
-    }
-  }
-  for (int kt0 = kt_first; kt0 < KT; kt0 += D * kstep) {
-#pragma unroll
-    for (int slot = 0; slot < D; ++slot) {
-      const int kt = kt0 + slot * kstep;
-      if (kt >= KT) break;
-      const int ktn = kt + (D - 1) * kstep;
-      if (ktn < KT) {
-        load_a<FMT>(ring[(slot + D - 1) % D][0], w0, Op, r0, ktn, lane);
-        if (GATED) load_a<FMT>(ring[(slot + D - 1) % D][MATS - 1], w1, Op, r0, ktn, lane);
+    for (int j = 0; j < NB; ++j) {
+      const int r = 8 * j + g;
+      if (r < nrows) {
+        const int row = row0 + r;
+        const size_t sidx = (GATED && p.row_token) ? (size_t)p.row_token[row] : (size_t)row;
+        xrow[j] = src + sidx * K;
+      } else {
+        xrow[j] = nullptr;
       }
-      // token fragments of this k-tile: lane (g,t) reads x[token g][kt*128 + 32t .. +31], 16 bytes
-      // (two MMA steps) at a time
-      const int kbase = kt * 128 + t * 32;
-      float part[MATS][NB][4];
-      if (FMT == COLI_FMT_FP8_B128) {
-  #pragma unroll
-        for (int mtx = 0; mtx < MATS; ++mtx)
-  #pragma unroll
-          for (int j = 0; j < NB; ++j)
-  #pragma unroll
-            for (int c = 0; c < 4; ++c) part[mtx][j][c] = 0.0f;
+    }
+
+    float acc[MATS][NB][4];
+#pragma unroll
+    for (int mtx = 0; mtx < MATS; ++mtx)
+#pragma unroll
+      for (int j = 0; j < NB; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[mtx][j][c] = 0.0f;
+
+    const int kstep = SPLITK ? W : 1;
+    const int kt_first = SPLITK ? warp : 0;
+
+    // token fragments: lane (g,t) reads x[token g][kt*128 + 32t + 8c .. +7] (16 bytes, two MMA
+    // steps) for quarter c of k-tile kt
+    auto load_x = [&](uint4 (&dst)[NB], int kt, int c) {
+      const int k0 = kt * 128 + t * 32 + c * 8;
+#pragma unroll
+      for (int j = 0; j < NB; ++j) {
+        dst[j] = make_uint4(0, 0, 0, 0);
+        if (xrow[j] != nullptr && kt < KT && k0 + 8 <= K) dst[j] = *reinterpret_cast<const uint4 *>(xrow[j] + k0);
       }
-  #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint4 xb[NB];
-  #pragma unroll
-        for (int j = 0; j < NB; ++j) {
-          xb[j] = make_uint4(0, 0, 0, 0);
-          if (xrow[j] != nullptr && kbase + c * 8 + 8 <= K)
-            xb[j] = *reinterpret_cast<const uint4 *>(xrow[j] + kbase + c * 8);
+    };
+
+    // Register rings, both unrolled so that every slot is a fixed set of registers (rotating
+    // slots with copies would make each iteration wait for the youngest load): packed weight
+    // fragments D k-tiles deep, token fragments R quarter-k-tiles deep.
+    AFrag<FMT> ring[D][MATS];
+    uint4 xq[R][NB];
+#pragma unroll
+    for (int j = 0; j < D - 1; ++j) {
+      const int ktl = kt_first + j * kstep;
+      if (ktl < KT) {
+        load_a<FMT>(ring[j][0], w0, Op, r0, ktl, lane);
+        if (GATED) load_a<FMT>(ring[j][MATS - 1], w1, Op, r0, ktl, lane);
+      }
+    }
+#pragma unroll
+    for (int f = 0; f < PF; ++f) load_x(xq[f % R], kt_first + (f / 4) * kstep, f % 4);
+
+    for (int kt0 = kt_first; kt0 < KT; kt0 += D * kstep) {
+#pragma unroll
+      for (int slot = 0; slot < D; ++slot) {
+        const int kt = kt0 + slot * kstep;
+        if (kt >= KT) break;
+        const int ktn = kt + (D - 1) * kstep;
+        if (ktn < KT) {
+          load_a<FMT>(ring[(slot + D - 1) % D][0], w0, Op, r0, ktn, lane);
+          if (GATED) load_a<FMT>(ring[(slot + D - 1) % D][MATS - 1], w1, Op, r0, ktn, lane);
         }
-  #pragma unroll
-        for (int mm = 0; mm < 2; ++mm) {
-          const int m = 2 * c + mm;
-  #pragma unroll
-          for (int mtx = 0; mtx < MATS; ++mtx) {
-            uint32_t a[4];
-            decode_a<FMT>(ring[slot][mtx], m, lut, a);
-  #pragma unroll
-            for (int j = 0; j < NB; ++j) {
-              const uint32_t b0 = mm ? xb[j].z : xb[j].x, b1 = mm ? xb[j].w : xb[j].y;
-              if (FMT == COLI_FMT_FP8_B128)
-                mma_bf16_16816(part[mtx][j], a, b0, b1);
-              else
-                mma_bf16_16816(acc[mtx][j], a, b0, b1);
+        AScale asc[MATS];
+#pragma unroll
+        for (int mtx = 0; mtx < MATS; ++mtx) asc[mtx] = decode_scales<FMT>(ring[slot][mtx]);
+        float part[MATS][NB][4];
+        if (FMT == COLI_FMT_FP8_B128) {
+#pragma unroll
+          for (int mtx = 0; mtx < MATS; ++mtx)
+#pragma unroll
+            for (int j = 0; j < NB; ++j)
+#pragma unroll
+              for (int c = 0; c < 4; ++c) part[mtx][j][c] = 0.0f;
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int f = slot * 4 + c;  // position in the unrolled body; 4*D is a multiple of R
+          load_x(xq[(f + PF) % R], kt + ((c + PF) / 4) * kstep, (c + PF) % 4);
+          const uint4(&xb)[NB] = xq[f % R];
+#pragma unroll
+          for (int mm = 0; mm < 2; ++mm) {
+            const int m = 2 * c + mm;
+#pragma unroll
+            for (int mtx = 0; mtx < MATS; ++mtx) {
+              uint32_t a[4];
+              decode_a<FMT>(ring[slot][mtx], asc[mtx], m, a);
+#pragma unroll
+              for (int j = 0; j < NB; ++j) {
+                const uint32_t b0 = mm ? xb[j].z : xb[j].x, b1 = mm ? xb[j].w : xb[j].y;
+                if (FMT == COLI_FMT_FP8_B128)
+                  mma_f16_16816(part[mtx][j], a, b0, b1);
+                else
+                  mma_f16_16816(acc[mtx][j], a, b0, b1);
+              }
             }
           }
         }
-      }
-      if (FMT == COLI_FMT_FP8_B128) {
-        // one f32 scale per (128-row block, k-tile): convert.rs:731-741
-  #pragma unroll
-        for (int mtx = 0; mtx < MATS; ++mtx) {
-          const float *sc = reinterpret_cast<const float *>(mtx == 0 ? w0.s : w1.s);
-          const float s = sc[(size_t)(r0 >> 7) * KT + kt];
-  #pragma unroll
-          for (int j = 0; j < NB; ++j)
-  #pragma unroll
-            for (int c = 0; c < 4; ++c) acc[mtx][j][c] = fmaf(s, part[mtx][j][c], acc[mtx][j][c]);
+        if (FMT == COLI_FMT_FP8_B128) {
+          // one f32 scale per (128-row block, k-tile): convert.rs:731-741
+#pragma unroll
+          for (int mtx = 0; mtx < MATS; ++mtx) {
+            const float *sc = reinterpret_cast<const float *>(mtx == 0 ? w0.s : w1.s);
+            const float s = sc[(size_t)(r0 >> 7) * KT + kt];
+#pragma unroll
+            for (int j = 0; j < NB; ++j)
+#pragma unroll
+              for (int c = 0; c < 4; ++c) acc[mtx][j][c] = fmaf(s, part[mtx][j][c], acc[mtx][j][c]);
+          }
         }
       }
     }
-  }
 
-  // epilogue of one 8-token block given its reduced accumulators
-  auto emit = [&](int j, const float (&v)[MATS][4]) {
+    // epilogue of one 8-token block given its reduced accumulators
+    auto emit = [&](int j, const float(&v)[MATS][4]) {
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const int orow = r0 + g + ((c & 2) ? 8 : 0);  // output feature
-      const int col = 8 * j + 2 * t + (c & 1);      // token within the item
-      if (orow >= Oout || col >= nrows) continue;
-      float s0 = 1.0f, s1 = 1.0f;
-      if (FMT == COLI_FMT_NVFP4) {
-        s0 = w0.g * kFp4AccScale;
-        s1 = w1.g * kFp4AccScale;
-      } else if (FMT == COLI_FMT_E4M3_ROW) {
-        s0 = reinterpret_cast<const float *>(w0.s)[orow];
-        s1 = reinterpret_cast<const float *>(w1.s)[orow];
+      for (int c = 0; c < 4; ++c) {
+        const int orow = r0 + g + ((c & 2) ? 8 : 0);  // output feature
+        const int col = 8 * j + 2 * t + (c & 1);      // token within the item
+        if (orow >= Oout || col >= nrows) continue;
+        float s0 = 1.0f, s1 = 1.0f;
+        if (FMT == COLI_FMT_NVFP4) {
+          s0 = w0.g;
+          s1 = w1.g;
+        } else if (FMT == COLI_FMT_E4M3_ROW) {
+          s0 = reinterpret_cast<const float *>(w0.s)[orow];
+          s1 = reinterpret_cast<const float *>(w1.s)[orow];
+        }
+        const size_t row = (size_t)(row0 + col);
+        if (GATED) {
+          const float gv = v[0][c] * s0, uv = v[MATS - 1][c] * s1;
+          const float hv = gv / (1.0f + __expf(-gv)) * uv;
+          p.h[row * p.I + orow] = coli_f32_to_f16_via_bf16(hv);
+        } else {
+          if (p.y32)
+            p.y32[row * p.H + orow] = v[0][c] * s0;
+          else
+            p.y[row * p.H + orow] = __float2bfloat16_rn(v[0][c] * s0);
+        }
       }
-      const size_t row = (size_t)(row0 + col);
-      if (GATED) {
-        const float gv = v[0][c] * s0, uv = v[MATS - 1][c] * s1;
-        const float hv = gv / (1.0f + __expf(-gv)) * uv;
-        p.h[row * p.I + orow] = __float2bfloat16_rn(hv);
-      } else {
-        if (p.y32)
-          p.y32[row * p.H + orow] = v[0][c] * s0;
-        else
-          p.y[row * p.H + orow] = __float2bfloat16_rn(v[0][c] * s0);
+    };
+
+    if (!SPLITK) {
+#pragma unroll
+      for (int j = 0; j < NB; ++j) {
+        float v[MATS][4];
+#pragma unroll
+        for (int mtx = 0; mtx < MATS; ++mtx)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) v[mtx][c] = acc[mtx][j][c];
+        emit(j, v);
       }
+      continue;
     }
-  };
 
-  if (!SPLITK) {
+    // cross-warp (split-K) reduction; every warp of the CTA is on the same task
+    constexpr int NV = MATS * NB * 4;
 #pragma unroll
-    for (int j = 0; j < NB; ++j) {
+    for (int mtx = 0; mtx < MATS; ++mtx)
+#pragma unroll
+      for (int j = 0; j < NB; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) red[((size_t)warp * NV + (mtx * NB + j) * 4 + c) * 32 + lane] = acc[mtx][j][c];
+    __syncthreads();
+
+    for (int j = warp; j < NB; j += W) {
       float v[MATS][4];
 #pragma unroll
       for (int mtx = 0; mtx < MATS; ++mtx)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) v[mtx][c] = acc[mtx][j][c];
+        for (int c = 0; c < 4; ++c) {
+          float s = 0.0f;
+          for (int w = 0; w < W; ++w) s += red[((size_t)w * NV + (mtx * NB + j) * 4 + c) * 32 + lane];
+          v[mtx][c] = s;
+        }
       emit(j, v);
     }
-    return;
-  }
-
-  // cross-warp (split-K) reduction
-  constexpr int NV = MATS * NB * 4;
-#pragma unroll
-  for (int mtx = 0; mtx < MATS; ++mtx)
-#pragma unroll
-    for (int j = 0; j < NB; ++j)
-#pragma unroll
-      for (int c = 0; c < 4; ++c) red[((size_t)warp * NV + (mtx * NB + j) * 4 + c) * 32 + lane] = acc[mtx][j][c];
-  __syncthreads();
-
-  for (int j = warp; j < NB; j += W) {
-    float v[MATS][4];
-#pragma unroll
-    for (int mtx = 0; mtx < MATS; ++mtx)
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        float s = 0.0f;
-        for (int w = 0; w < W; ++w) s += red[((size_t)w * NV + (mtx * NB + j) * 4 + c) * 32 + lane];
-        v[mtx][c] = s;
-      }
-    emit(j, v);
   }
 }
 
@@ -356,8 +381,21 @@ static int launch_one(const FfnParams &p, bool gated, cudaStream_t st) {
     else
       k_ffn_mm<FMT, NB, false, true><<<grid, W * 32, sm, st>>>(p);
   } else {
-    const int W = 4;  // four 16-row tiles per CTA
-    dim3 grid((row_tiles + W - 1) / W, p.max_items);
+    // two warps per CTA keep the per-SM share of tasks even; the grid covers what fits at once
+    constexpr int W = 2;
+    static int resident[2] = {0, 0};  // CTAs per device, per kernel variant
+    if (resident[gated ? 1 : 0] == 0) {
+      int dev = 0, sms = 0, per_sm = 0;
+      if (!coli_cuda_check(cudaGetDevice(&dev), "device query") ||
+          !coli_cuda_check(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "device query"))
+        return 0;
+      const cudaError_t e = gated ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_ffn_mm<FMT, NB, true, false>, W * 32, 0)
+                                  : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_ffn_mm<FMT, NB, false, false>, W * 32, 0);
+      if (!coli_cuda_check(e, "occupancy query")) return 0;
+      resident[gated ? 1 : 0] = sms * (per_sm > 0 ? per_sm : 1);
+    }
+    const long max_ctas = ((long)row_tiles * p.max_items + W - 1) / W;
+    const int grid = (int)(max_ctas < resident[gated ? 1 : 0] ? max_ctas : resident[gated ? 1 : 0]);
     if (gated)
       k_ffn_mm<FMT, NB, true, false><<<grid, W * 32, 0, st>>>(p);
     else

@@ -4,17 +4,18 @@
 // has a granularity of 16, and the always-full feature axis on its M = 128):
 //     D[feature, token] = W[feature, :] . X[token, :]^T          per expert segment
 // * A operand (M side): a 128-feature x 64-k tile of the expert matrix.  The packed NVFP4
-//   bytes are streamed from HBM with 128-bit loads by 8 producer warps, decoded to bf16 in
-//   registers (exact: E2M1 x ue4m3 has <= 6 significant bits) and stored to shared memory in
-//   the K-major 128-byte-swizzled layout the MMA reads.
-// * B operand (N side): up to 256 token rows x 64 k of bf16 activations, copied by TMA
+//   bytes are streamed from HBM with 128-bit loads by the producer warps, converted to f16 in
+//   registers (cvt.rn.f16x2.e2m1x2 per byte, one half2 multiply by the block scale; exact:
+//   E2M1 x ue4m3 has <= 6 significant bits) and stored to shared memory in the K-major
+//   128-byte-swizzled layout the MMA reads.
+// * B operand (N side): up to 256 token rows x 64 k of f16 activations, copied by TMA
 //   (cp.async.bulk.tensor, 128-byte swizzle, no multicast) straight into the same layout.
-// * tcgen05.mma kind::f16 (bf16 x bf16 -> f32), issued by one thread, accumulates in TMEM; the
+// * tcgen05.mma kind::f16 (f16 x f16 -> f32), issued by one thread, accumulates in TMEM; the
 //   gate and the up projection of the same 128 features use two accumulators (columns 0.. and
 //   256..) fed from the same token tile, so SiLU(g)*u is formed in the epilogue registers and
 //   only h is written.
 // * 4 epilogue warps read TMEM with tcgen05.ld (one lane = one feature), apply the per-tensor
-//   scale, the activation, and store bf16.
+//   scale, the activation, and store h (f16 holding the bf16-rounded value) or y (bf16).
 // Roles are warp-specialised and synchronise through mbarriers only; the kernel is persistent
 // (one CTA per SM walks the device-built work list).  Every barrier wait is bounded: on a
 // time-out the CTA raises a status word, stops issuing work, waits for its own copies and frees
@@ -30,7 +31,7 @@
 namespace colib {
 
 constexpr int TC_BM = 128;   // features per tile (UMMA M)
-constexpr int TC_BK = 64;    // k per pipeline stage: one 128-byte swizzle row of bf16
+constexpr int TC_BK = 64;    // k per pipeline stage: one 128-byte swizzle row of f16
 constexpr int TC_BOXN = 32;  // token rows per TMA box
 constexpr int TC_EPI_WARPS = 4;
 // weight-producer warps: every thread decodes one 16-byte chunk (32 weights) of one matrix per
@@ -99,7 +100,7 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
       ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
@@ -127,25 +128,44 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr) {
   d |= (uint64_t)2 << 61;          // SWIZZLE_128B
   return d;
 }
-// kind::f16: D = f32, A = B = bf16, both K-major, M = 128, N = n.
+// kind::f16: D = f32, A = B = f16 (format code 0), both K-major, M = 128, N = n.
 __device__ __forceinline__ uint32_t umma_idesc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
 }
 
 __device__ __forceinline__ uint32_t tc_hmul2(uint32_t a, uint32_t b) {
   uint32_t d;
-  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
   return d;
 }
-// One NVFP4 word (8 consecutive k: even elements in nibble slots 0..3, odd in 4..7) -> 8 bf16
-// (four bf16x2, k ascending), each equal to weight * 2^-16; see expert_small.cu for the bit layout.
+// One NVFP4 word (8 consecutive k, two per byte, low nibble first) -> 8 f16 (four f16x2, k
+// ascending) times the block scale held in both halves of `mult`.
 __device__ __forceinline__ uint4 tc_dequant_word(uint32_t w, uint32_t mult) {
   uint4 o;
-  o.x = tc_hmul2(((w << 6) & 0x01C001C0u) | ((w << 12) & 0x80008000u), mult);
-  o.y = tc_hmul2(((w << 2) & 0x01C001C0u) | ((w << 8) & 0x80008000u), mult);
-  o.z = tc_hmul2(((w >> 2) & 0x01C001C0u) | ((w << 4) & 0x80008000u), mult);
-  o.w = tc_hmul2(((w >> 6) & 0x01C001C0u) | (w & 0x80008000u), mult);
+  asm("{ .reg .b8 b0, b1, b2, b3;\n"
+      "  mov.b32 {b0, b1, b2, b3}, %4;\n"
+      "  cvt.rn.f16x2.e2m1x2 %0, b0;\n"
+      "  cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+      "  cvt.rn.f16x2.e2m1x2 %2, b2;\n"
+      "  cvt.rn.f16x2.e2m1x2 %3, b3; }\n"
+      : "=r"(o.x), "=r"(o.y), "=r"(o.z), "=r"(o.w)
+      : "r"(w));
+  o.x = tc_hmul2(o.x, mult);
+  o.y = tc_hmul2(o.y, mult);
+  o.z = tc_hmul2(o.z, mult);
+  o.w = tc_hmul2(o.w, mult);
   return o;
+}
+// two ue4m3 block scales (low 16 bits of sc) -> each as f16 in both halves of a word
+__device__ __forceinline__ void tc_scales(uint32_t sc, uint32_t &m0, uint32_t &m1) {
+  uint32_t v;
+  asm("{ .reg .b16 h0, h1;\n"
+      "  mov.b32 {h0, h1}, %1;\n"
+      "  cvt.rn.f16x2.e4m3x2 %0, h0; }\n"
+      : "=r"(v)
+      : "r"(sc));
+  m0 = __byte_perm(v, v, 0x1010);
+  m1 = __byte_perm(v, v, 0x3232);
 }
 
 struct TcPacked {
@@ -183,8 +203,9 @@ __device__ __forceinline__ TcPacked tc_half(const TcPackedKT &t, int half, int c
   return r;
 }
 // Decode 32 weights and store them as chunks 4c..4c+3 of row `row` of a swizzled 128x64 tile.
-__device__ __forceinline__ void tc_store_tile(uint8_t *tile, int row, int c, const TcPacked &pk, const uint32_t *lut) {
-  const uint32_t m0 = lut[pk.sc & 0xffu], m1 = lut[(pk.sc >> 8) & 0xffu];
+__device__ __forceinline__ void tc_store_tile(uint8_t *tile, int row, int c, const TcPacked &pk) {
+  uint32_t m0, m1;
+  tc_scales(pk.sc, m0, m1);
   uint8_t *rbase = tile + (row >> 3) * 1024 + (row & 7) * 128;
   const int sw = row & 7;
   *reinterpret_cast<uint4 *>(rbase + (((c * 4 + 0) ^ sw) << 4)) = tc_dequant_word(pk.q.x, m0);
@@ -199,7 +220,6 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
   constexpr int STAGES = 3;
   constexpr int STAGE_BYTES = MATS * TC_A_BYTES + TC_B_BYTES;
   constexpr int TC_PROD_WARPS = TcCfg<GATED>::PROD_WARPS;
-  constexpr int TC_THREADS = TcCfg<GATED>::THREADS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
@@ -208,7 +228,6 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * STAGES + 2);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   volatile int *prod_ok = reinterpret_cast<volatile int *>(tmem_slot + 2);
-  uint32_t *lut = tmem_slot + 4;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int K = GATED ? p.H : p.I, Oout = GATED ? p.I : p.H;
@@ -228,11 +247,6 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
     mbar_init(acc_empty, TC_EPI_WARPS);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  for (int b = threadIdx.x; b < 256; b += TC_THREADS) {
-    const float s = coli_e4m3_to_f32((uint8_t)b) * 1.2980742146337069e33f;  // * 2^110
-    const uint32_t h = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(s));
-    lut[b] = h | (h << 16);
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
@@ -295,8 +309,8 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
           for (int k4 = 0; k4 < TC_BK / 16; ++k4) {
             const uint64_t bd = umma_smem_desc(b0 + k4 * 32);
             const uint32_t acc = (kb | k4) ? 1u : 0u;
-            umma_bf16(tmem_base, umma_smem_desc(a0 + k4 * 32), bd, idesc, acc);
-            umma_bf16(tmem_base + TC_MAX_TOKENS, umma_smem_desc(a0 + TC_A_BYTES + k4 * 32), bd, idesc, acc);
+            umma_f16(tmem_base, umma_smem_desc(a0 + k4 * 32), bd, idesc, acc);
+            umma_f16(tmem_base + TC_MAX_TOKENS, umma_smem_desc(a0 + TC_A_BYTES + k4 * 32), bd, idesc, acc);
           }
           umma_commit(empty + 8 * s);  // the stage may be refilled once these MMAs have read it
         }
@@ -312,8 +326,8 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
       const int seg = p.item_seg[item], row0 = p.item_row0[item], nrows = p.item_nrows[item];
       const int ex = p.seg_expert ? p.seg_expert[seg] : seg;
       const int N = (nrows + TC_BOXN - 1) / TC_BOXN * TC_BOXN;
-      const float s0 = (GATED ? p.gate[ex].g : p.down[ex].g) * 65536.0f;
-      const float s1 = (GATED ? p.up[ex].g : p.down[ex].g) * 65536.0f;
+      const float s0 = GATED ? p.gate[ex].g : p.down[ex].g;
+      const float s1 = GATED ? p.up[ex].g : p.down[ex].g;
       bool ok = true;
       if (lane == 0) ok = mbar_wait(acc_full, tix & 1u, abort_flag, p.status, TC_ERR_EPI_WAIT, 256);
       ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
@@ -321,7 +335,8 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
       tc_fence_after();
       const int f = ft * FT + lg * 32 + lane;  // accumulator 0; accumulator 1 is feature f + 128 of down
       const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16);
-      __nv_bfloat16 *out = (GATED ? p.h : p.y) + (size_t)row0 * Oout + f;
+      __half *out_h = p.h + (size_t)row0 * Oout + f;
+      __nv_bfloat16 *out_y = p.y + (size_t)row0 * Oout + f;
       for (int c0 = 0; c0 < N; c0 += 16) {
         uint32_t g[16], u[16];
         tmem_ld16(tbase + c0, g);
@@ -332,10 +347,10 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
           const int col = c0 + j;
           if (col < nrows) {
             const float v0 = __uint_as_float(g[j]) * s0, v1 = __uint_as_float(u[j]) * s1;
-            __nv_bfloat16 *dst = out + (size_t)col * Oout;
             if (GATED) {
-              if (f < Oout) *dst = __float2bfloat16_rn(__fdividef(v0, 1.0f + __expf(-v0)) * v1);
+              if (f < Oout) out_h[(size_t)col * Oout] = coli_f32_to_f16_via_bf16(__fdividef(v0, 1.0f + __expf(-v0)) * v1);
             } else {
+              __nv_bfloat16 *dst = out_y + (size_t)col * Oout;
               if (f < Oout) *dst = __float2bfloat16_rn(v0);
               if (f + TC_BM < Oout) dst[TC_BM] = __float2bfloat16_rn(v1);
             }
@@ -347,7 +362,7 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
       if (lane == 0) mbar_arrive(acc_empty);
     }
   } else {
-    // ---------------- weight producers: HBM -> registers -> bf16 -> swizzled shared memory ----------------
+    // ---------------- weight producers: HBM -> registers -> f16 -> swizzled shared memory ----------------
     // thread -> (matrix, row, 16-byte chunk): 256 threads cover one 128-row tile of one matrix
     const int pt = threadIdx.x - 32 * (2 + TC_EPI_WARPS);
     const int mtx = pt >> 8, row = (pt & 255) >> 1, c = pt & 1;
@@ -391,7 +406,7 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
               alive = false;
               break;
             }
-            tc_store_tile(smem + s * STAGE_BYTES + mtx * TC_A_BYTES, row, c, tc_half(ring[j], half, c), lut);
+            tc_store_tile(smem + s * STAGE_BYTES + mtx * TC_A_BYTES, row, c, tc_half(ring[j], half, c));
             fence_proxy_async_smem();  // make these generic-proxy stores visible to the tensor core
             __syncwarp();
             if (lane == 0) mbar_arrive(full_a + 8 * s);
@@ -429,7 +444,7 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// bf16 [rows, K] row-major; box = 64 k x 32 rows; 128-byte swizzle; out-of-range reads give zeros
+// f16 [rows, K] row-major; box = 64 k x 32 rows; 128-byte swizzle; out-of-range reads give zeros
 static bool make_rows_map(CUtensorMap *map, const void *base, int rows, int K) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
@@ -441,7 +456,7 @@ static bool make_rows_map(CUtensorMap *map, const void *base, int rows, int K) {
   const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
   const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)TC_BOXN};
   const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -455,7 +470,7 @@ template <bool GATED>
 static int launch_tc(const TcParams &p, const void *rows_base, int rows_cap, int sm_count, cudaStream_t st) {
   constexpr int MATS = 2;
   constexpr int STAGES = 3;
-  const size_t smem = (size_t)STAGES * (MATS * TC_A_BYTES + TC_B_BYTES) + 1024 /*align*/ + 8 * (3 * STAGES + 2) + 16 + 1024 /*lut*/ + 64;
+  const size_t smem = (size_t)STAGES * (MATS * TC_A_BYTES + TC_B_BYTES) + 1024 /*align*/ + 8 * (3 * STAGES + 2) + 16 + 64;
   static bool attr_done = false;
   if (!attr_done) {
     if (!coli_cuda_check(cudaFuncSetAttribute(k_ffn_tc<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),

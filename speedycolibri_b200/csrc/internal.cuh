@@ -2,6 +2,7 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <stdint.h>
 #include <stddef.h>
 
@@ -12,15 +13,20 @@
 // HBM layout ("k-tile major"): the K (input) axis is cut into tiles of 128; for each k-tile
 // all O rows are stored back to back, so the slab a CTA streams for (rows r0..r0+n, k-tile kt)
 // is one contiguous run of bytes.
-//   NVFP4     q: [KT][Op][64 B]   16 B chunk c of a row covers k = kt*128 + 32c .. +31; each
-//                                 32-bit word covers 8 consecutive k, even elements in nibble
-//                                 slots 0..3 and odd elements in slots 4..7 (so one shift+mask
-//                                 yields a (k, k+1) pair aligned to the halves of a bf16x2).
+//   NVFP4     q: [KT][Op][64 B]   16 B chunk c of a row covers k = kt*128 + 32c .. +31; every
+//                                 byte holds two consecutive k, low nibble first (the operand
+//                                 form of cvt.rn.f16x2.e2m1x2).
 //             s: [KT][Op][8 B]    the ue4m3 code of each 16-wide block, k ascending
 //   FP8_B128  q: [KT][Op][128 B]  e4m3 codes, k ascending
 //             s: f32 [ceil(O/128)][KT]   (the reference's own grid, convert.rs:731-741)
 //   E4M3_ROW  q as FP8_B128; s: f32 [O] row scales (linear.rs:93-109)
 // Op = O rounded up to 16, Kp = I rounded up to 128; padding bytes are zero (decode to 0.0).
+//
+// Arithmetic type of the expert GEMMs: f16 x f16 -> f32.  FP4/FP8 codes convert to f16 with one
+// hardware cvt per pair, a decoded weight (code x block scale, at most 6 significant bits, between
+// 2^-10 and 2688) is exact in f16, and a bf16 activation is exact in f16 whenever its magnitude
+// lies in [2^-14, 65504]; smaller ones lose at most 2^-25 absolute, larger ones saturate.  The
+// intermediate h keeps the value rounded to bf16 (what the reference stores) held in f16.
 struct ColiCudaTensor {
   int fmt, I, O, device;
   int Kp, Op, KT;
@@ -97,8 +103,9 @@ struct PermuteParams {
   int32_t *item_nrows;         //                rows (<= rows_per_item)
   int32_t *n_items;            // [1]
   const __nv_bfloat16 *x;      // [T,H]  (null = do not materialise rows)
-  __nv_bfloat16 *xg;           // [T*k (+T),H] gathered rows (null = skip)
+  __half *xg;                  // [T*k (+T),H] gathered rows as f16 (null = skip)
   int gather_shared;           // also copy the shared expert's T identity rows into xg
+  __half *x16;                 // [T,H] f16 copy of x in token order (null = skip)
 };
 int launch_permute(const PermuteParams &p, cudaStream_t st);
 // Work list for rows that are already expert-contiguous (counts on the device).
@@ -115,9 +122,9 @@ struct FfnParams {
   int max_items;
   int rows_per_item;         // rows per work item the list was cut with (<= 32)
   int items_expected;        // host estimate of the work items (selects split-K vs tile-per-warp)
-  const __nv_bfloat16 *x;    // source rows
+  const __half *x;           // source rows (f16)
   const int32_t *row_token;  // row -> source row index (null = identity)
-  __nv_bfloat16 *h;          // [rows, I] scratch
+  __half *h;                 // [rows, I] scratch
   __nv_bfloat16 *y;          // [rows, H] out (bf16), or
   float *y32;                // [rows, H] out (f32) when not null
 };
@@ -133,11 +140,11 @@ struct TcParams {
   const int32_t *seg_expert;
   const int32_t *item_seg, *item_row0, *item_nrows, *n_items;
   int max_items;
-  __nv_bfloat16 *h;  // [rows, I]
+  __half *h;         // [rows, I]
   __nv_bfloat16 *y;  // [rows, H]
   int *status;       // device word: 0, or the code of the first bounded wait that gave up
 };
-// x_rows: bf16 [rows_cap, H] expert-contiguous rows (row index = position in the work list)
+// x_rows: f16 [rows_cap, H] expert-contiguous rows (row index = position in the work list)
 int launch_gate_up_tc(const TcParams &p, const void *x_rows, int rows_cap, int sm_count, cudaStream_t st);
 int launch_down_tc(const TcParams &p, int rows_cap, int sm_count, cudaStream_t st);
 
@@ -155,8 +162,28 @@ struct CombineParams {
 int launch_combine(const CombineParams &p, cudaStream_t st);
 int launch_finish(const float *partial, const __nv_bfloat16 *shared_y, __nv_bfloat16 *out, int T, int H, cudaStream_t st);
 int launch_f32_to_bf16(const float *src, __nv_bfloat16 *dst, size_t n, cudaStream_t st);
+// activations for the expert GEMMs: the bf16 value (rounding f32 to bf16 first), held in f16
+int launch_bf16_to_f16(const __nv_bfloat16 *src, __half *dst, size_t n, cudaStream_t st);
+int launch_f32_to_f16_via_bf16(const float *src, __half *dst, size_t n, cudaStream_t st);
 // y[S,O] = x[S,I] @ W[O,I]^T, all f32, one thread per output, multiply then add per k in order
 // (crates/colibri-engine/src/linear.rs:199-220).
 int launch_matmul_f32_seq(const float *x, const float *w, float *y, int S, int I, int O, cudaStream_t st);
+
+// bf16 pair (one 32-bit word) -> f16 pair, saturating at the largest finite f16
+__device__ __forceinline__ uint32_t coli_bf16x2_to_f16x2(uint32_t w) {
+  const float lo = fminf(fmaxf(__uint_as_float(w << 16), -65504.0f), 65504.0f);
+  const float hi = fminf(fmaxf(__uint_as_float(w & 0xffff0000u), -65504.0f), 65504.0f);
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+__device__ __forceinline__ uint4 coli_bf16x8_to_f16x8(uint4 v) {
+  return make_uint4(coli_bf16x2_to_f16x2(v.x), coli_bf16x2_to_f16x2(v.y), coli_bf16x2_to_f16x2(v.z),
+                    coli_bf16x2_to_f16x2(v.w));
+}
+// f32 -> (rounded to bf16) -> f16 bits, saturating
+__device__ __forceinline__ __half coli_f32_to_f16_via_bf16(float v) {
+  const float r = __bfloat162float(__float2bfloat16_rn(v));
+  return __float2half_rn(fminf(fmaxf(r, -65504.0f), 65504.0f));
+}
 
 }  // namespace colib

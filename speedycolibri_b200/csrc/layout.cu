@@ -13,8 +13,9 @@ __device__ __forceinline__ uint32_t nib_at(const uint8_t *nib, int rb, int row, 
   return (k & 1) ? (uint32_t)(b >> 4) : (uint32_t)(b & 0x0f);
 }
 
-// one thread per 32-bit word of the packed array: (kt, row, word j) covers k = kt*128 + 8j .. +7;
-// even elements go to nibble slots 0..3, odd elements to slots 4..7
+// one thread per 32-bit word of the packed array: (kt, row, word j) covers k = kt*128 + 8j .. +7,
+// k ascending from the least significant nibble (the container's own order: byte = two
+// consecutive k, low nibble first, which is what cvt.rn.f16x2.e2m1x2 consumes)
 __global__ void k_pack_nvfp4_q(const uint8_t *nib, uint32_t *q, int O, int I, int Op, int KT) {
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t total = (size_t)KT * Op * 16;
@@ -26,10 +27,7 @@ __global__ void k_pack_nvfp4_q(const uint8_t *nib, uint32_t *q, int O, int I, in
   const int k0 = kt * 128 + j * 8;
   uint32_t w = 0;
 #pragma unroll
-  for (int pp = 0; pp < 4; ++pp) {
-    w |= nib_at(nib, rb, row, k0 + 2 * pp, O, I) << (4 * pp);
-    w |= nib_at(nib, rb, row, k0 + 2 * pp + 1, O, I) << (4 * pp + 16);
-  }
+  for (int el = 0; el < 8; ++el) w |= nib_at(nib, rb, row, k0 + el, O, I) << (4 * el);
   q[idx] = w;
 }
 __global__ void k_pack_nvfp4_s(const uint8_t *bs, uint8_t *s, int O, int I, int Op, int KT) {
@@ -54,8 +52,7 @@ __global__ void k_unpack_nvfp4_q(const uint32_t *q, uint8_t *nib, int O, int I, 
     if (k >= I) break;
     const int kt = k >> 7, j = (k & 127) >> 3, el = k & 7;
     const uint32_t w = q[((size_t)kt * Op + row) * 16 + j];
-    const int slot = (el >> 1) + ((el & 1) ? 4 : 0);
-    out |= ((w >> (4 * slot)) & 0xfu) << (4 * h);
+    out |= ((w >> (4 * el)) & 0xfu) << (4 * h);
   }
   nib[idx] = (uint8_t)out;
 }
@@ -68,11 +65,7 @@ __global__ void k_unpack_nvfp4_s(const uint8_t *s, uint8_t *bs, int O, int I, in
 }
 
 // ---- FP8 ---------------------------------------------------------------------------------------
-// byte order inside every 4-byte word is [k0, k2, k1, k3], so that (w & 0x00ff00ff) is the
-// (k0,k1) pair and ((w >> 8) & 0x00ff00ff) the (k2,k3) pair, each aligned to bf16x2 halves
-__device__ __forceinline__ int fp8_pos(int el) {  // position of element el (0..3) in its word
-  return el == 0 ? 0 : el == 1 ? 2 : el == 2 ? 1 : 3;
-}
+// bytes stay in k order: a 16-bit half word is one (k, k+1) pair for cvt.rn.f16x2.e4m3x2
 __global__ void k_pack_fp8(const uint8_t *codes, uint8_t *q, int O, int I, int Op, int KT) {
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t total = (size_t)KT * Op * 128;
@@ -82,14 +75,14 @@ __global__ void k_pack_fp8(const uint8_t *codes, uint8_t *q, int O, int I, int O
   const int kt = (int)(idx / 128 / Op);
   const int k = kt * 128 + j;
   const uint8_t v = (row < O && k < I) ? codes[(size_t)row * I + k] : (uint8_t)0;
-  q[idx - j + (j & ~3) + fp8_pos(j & 3)] = v;
+  q[idx] = v;
 }
 __global__ void k_unpack_fp8(const uint8_t *q, uint8_t *codes, int O, int I, int Op) {
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (size_t)O * I) return;
   const int row = (int)(idx / I), k = (int)(idx % I);
   const int kt = k >> 7, j = k & 127;
-  codes[idx] = q[((size_t)kt * Op + row) * 128 + (j & ~3) + fp8_pos(j & 3)];
+  codes[idx] = q[((size_t)kt * Op + row) * 128 + j];
 }
 
 static inline unsigned nblk(size_t n, int b) { return (unsigned)((n + b - 1) / b); }

@@ -467,11 +467,21 @@ __global__ void __launch_bounds__(1024) k_seg_scan(PermuteParams p, int nchunk, 
 }
 
 __global__ void __launch_bounds__(256) k_permute(PermuteParams p) {
-  // one warp per (t, kk) row; rows T*k .. T*k+T-1 are the shared expert's identity rows
+  // one warp per (t, kk) row; rows T*k .. T*k+T-1 are the shared expert's identity rows; when a
+  // token-order f16 copy of x is wanted, T more warps write it
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int nrouted = p.T * p.k;
   const int total = nrouted + (p.has_shared ? p.T : 0);
-  if (warp >= total) return;
+  if (warp >= total) {
+    const int t = warp - total;
+    if (p.x16 && t < p.T) {
+      const int vec = p.H / 8;
+      const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (size_t)t * p.H);
+      uint4 *dst = reinterpret_cast<uint4 *>(p.x16 + (size_t)t * p.H);
+      for (int c = lane; c < vec; c += 32) dst[c] = coli_bf16x8_to_f16x8(src[c]);
+    }
+    return;
+  }
   int t, pos;
   if (warp < nrouted) {
     t = warp / p.k;
@@ -492,7 +502,7 @@ __global__ void __launch_bounds__(256) k_permute(PermuteParams p) {
     const int vec = p.H / 8;
     const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (size_t)t * p.H);
     uint4 *dst = reinterpret_cast<uint4 *>(p.xg + (size_t)pos * p.H);
-    for (int c = lane; c < vec; c += 32) dst[c] = src[c];
+    for (int c = lane; c < vec; c += 32) dst[c] = coli_bf16x8_to_f16x8(src[c]);
   }
 }
 
@@ -503,6 +513,14 @@ __global__ void __launch_bounds__(1024) k_permute_small(PermuteParams p, int max
   __shared__ int cnt[1024 + 1];
   __shared__ int off[1024 + 2];
   __shared__ int rank_sm[1024];
+  if (blockIdx.x > 0) {  // the extra CTAs only write the token-order f16 copy of x
+    const size_t n = (size_t)p.T * p.H / 8;
+    const uint4 *src = reinterpret_cast<const uint4 *>(p.x);
+    uint4 *dst = reinterpret_cast<uint4 *>(p.x16);
+    for (size_t i = (size_t)(blockIdx.x - 1) * blockDim.x + threadIdx.x; i < n; i += (size_t)(gridDim.x - 1) * blockDim.x)
+      dst[i] = coli_bf16x8_to_f16x8(src[i]);
+    return;
+  }
   const int E = p.E, nrt = p.nseg_routed, nseg = nrt + (p.has_shared ? 1 : 0);
   const int npairs = p.T * p.k;
   for (int e = threadIdx.x; e <= E; e += blockDim.x) cnt[e] = 0;
@@ -573,7 +591,7 @@ __global__ void __launch_bounds__(1024) k_permute_small(PermuteParams p, int max
       }
       const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (size_t)t * p.H);
       uint4 *dst = reinterpret_cast<uint4 *>(p.xg + (size_t)pos * p.H);
-      for (int c = threadIdx.x & 31; c < vec; c += 32) dst[c] = src[c];
+      for (int c = threadIdx.x & 31; c < vec; c += 32) dst[c] = coli_bf16x8_to_f16x8(src[c]);
     }
   }
 }
@@ -588,7 +606,13 @@ int launch_permute(const PermuteParams &p, cudaStream_t st) {
   const int nseg = p.nseg_routed + (p.has_shared ? 1 : 0);
   const int max_items = (p.T * p.k + (p.has_shared ? p.T : 0)) / p.rows_per_item + nseg;
   if (p.T * p.k <= 1024 && p.k <= 32) {
-    k_permute_small<<<1, 1024, 0, st>>>(p, max_items);
+    int conv = 0;
+    if (p.x16) {
+      const size_t n = (size_t)p.T * p.H / 8;
+      conv = (int)((n + 1023) / 1024);
+      if (conv > 64) conv = 64;
+    }
+    k_permute_small<<<1 + conv, 1024, 0, st>>>(p, max_items);
     coli_count_launch(1);
     return coli_cuda_check(cudaGetLastError(), "permute launch") ? 1 : 0;
   }
@@ -596,7 +620,7 @@ int launch_permute(const PermuteParams &p, cudaStream_t st) {
   coli_count_launch(1);
   k_seg_scan<<<1, 1024, 0, st>>>(p, nchunk, max_items);
   coli_count_launch(1);
-  const int total = p.T * p.k + (p.has_shared ? p.T : 0);
+  const int total = p.T * p.k + (p.has_shared ? p.T : 0) + (p.x16 ? p.T : 0);
   k_permute<<<(total + 7) / 8, 256, 0, st>>>(p);
   coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "permute launch") ? 1 : 0;
