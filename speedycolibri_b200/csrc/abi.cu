@@ -356,6 +356,7 @@ struct ColiMoe {
   __half *x16;  // token-order f16 copy of the activations (small-batch path, shared expert stage)
   __half *xg;   // gathered f16 rows for the tcgen05 path (null when max_tokens never reaches it)
   int *status;        // device status word of the tcgen05 kernels
+  unsigned int *ticket;  // device word of the fused decode front end (zero between launches)
   int sm_count;
   size_t h_rows_cap;  // rows the h scratch holds
   size_t ws_bytes;
@@ -538,6 +539,8 @@ extern "C" int coli_b200_moe_create(ColiMoe **out, const ColiMoeLayer *L, int ma
     m->sm_count = ok ? prop.multiProcessorCount : 0;
   }
   ok = ok && ws_alloc(m, &m->status, 1) && coli_cuda_check(cudaMemset(m->status, 0, sizeof(int)), "status clear");
+  m->ticket = nullptr;
+  ok = ok && ws_alloc(m, &m->ticket, 1) && coli_cuda_check(cudaMemset(m->ticket, 0, sizeof(unsigned int)), "ticket clear");
   if (ok && use_tc_path(L->fmt, (int)rows, m->nseg)) ok = ws_alloc(m, &m->xg, rows * H);
   m->select_bias = nullptr;
   m->logit_bias = nullptr;
@@ -667,13 +670,17 @@ extern "C" int coli_b200_moe_block_dev(ColiMoe *m, const void *x_dev, void *out_
     if (prof) CK(cudaEventRecord(m->ev[i], st), "phase event");              \
   } while (0)
   COLI_MARK(0);
-  if (!colib::launch_router(route_params(m, x_dev, T), st)) return 0;
-  COLI_MARK(1);
   {
     colib::PermuteParams pp = permute_params(m, x_dev, T, m->has_shared, rpi, tc ? m->xg : nullptr, m->seg_count, m->slot);
     pp.gather_shared = tc ? 1 : 0;
     pp.x16 = tc ? nullptr : m->x16;
-    if (!colib::launch_permute(pp, st)) return 0;
+    // decode-sized batches: one launch for router, top-k and permutation (its time is booked
+    // under the router phase)
+    const int fused = T <= 8 ? colib::launch_decode_front(route_params(m, x_dev, T), pp, m->ticket, st) : -1;
+    if (fused == 0) return 0;
+    if (fused < 0 && !colib::launch_router(route_params(m, x_dev, T), st)) return 0;
+    COLI_MARK(1);
+    if (fused < 0 && !colib::launch_permute(pp, st)) return 0;
   }
   COLI_MARK(2);
   if (tc) {

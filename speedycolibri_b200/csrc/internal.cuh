@@ -108,6 +108,10 @@ struct PermuteParams {
   __half *x16;                 // [T,H] f16 copy of x in token order (null = skip)
 };
 int launch_permute(const PermuteParams &p, cudaStream_t st);
+// Router + top-k + permutation of a decode-sized batch (T <= 8) in one launch.  Returns 1 on
+// success, 0 on error, -1 when the shapes do not qualify (run launch_router + launch_permute).
+// `ticket` is a device word that is zero between launches.
+int launch_decode_front(const RouteParams &rp, const PermuteParams &pp, unsigned int *ticket, cudaStream_t st);
 // Work list for rows that are already expert-contiguous (counts on the device).
 int launch_items_from_counts(const int32_t *seg_count, int nseg, int rows_per_item, int32_t *seg_off,
                              int32_t *item_seg, int32_t *item_row0, int32_t *item_nrows, int32_t *n_items,

@@ -174,26 +174,43 @@ __global__ void __launch_bounds__(256) k_router_gemm_big(RouteParams p) {
 // Decode shape (T <= 8): one thread per (token, expert) walking its own k chain; the block's 8
 // expert rows and all token rows are staged in shared memory as bf16 with coalesced 16-byte
 // loads first.  The chain of H dependent FMAs is the latency floor of bit-exact routing.
-__global__ void __launch_bounds__(256) k_router_decode(RouteParams p) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16 *xs = reinterpret_cast<__nv_bfloat16 *>(smem_raw);  // [T][H]
-  __nv_bfloat16 *ws = xs + (size_t)p.T * p.H;                       // [8][H]
+__device__ __forceinline__ void router_decode_block(const RouteParams &p, unsigned char *smem_raw) {
+  // rows of H bf16 plus 16 bytes of padding: the chain threads of a warp read 4 token rows and 8
+  // expert rows at the same column, and unpadded rows (a multiple of 128 bytes apart) would all
+  // start in the same shared-memory bank
+  uint4 *xs = reinterpret_cast<uint4 *>(smem_raw);  // [T][vec + 1]
   const int e0 = blockIdx.x * 8;
   const int H = p.H;
   const int vec = H / 8;  // H % 8 == 0 checked by the launcher
-  for (int idx = threadIdx.x; idx < p.T * vec; idx += blockDim.x)
-    reinterpret_cast<uint4 *>(xs)[idx] = reinterpret_cast<const uint4 *>(p.x)[idx];
-  for (int idx = threadIdx.x; idx < 8 * vec; idx += blockDim.x) {
-    const int r = idx / vec, c = idx % vec;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (e0 + r < p.E) v = reinterpret_cast<const uint4 *>(p.router_w + (size_t)(e0 + r) * H)[c];
-    reinterpret_cast<uint4 *>(ws)[idx] = v;
+  const int rs = vec + 1; // row stride in 16-byte units
+  uint4 *ws = xs + (size_t)p.T * rs;                // [8][vec + 1]
+  // staging in batches of 8 independent 16-byte loads per thread: a load-store loop would pay one
+  // memory round trip per iteration
+  const int nx = p.T * vec, nw = 8 * vec;
+  for (int base = 0; base < nx + nw; base += 8 * (int)blockDim.x) {
+    uint4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int idx = base + u * (int)blockDim.x + (int)threadIdx.x;
+      v[u] = make_uint4(0, 0, 0, 0);
+      if (idx < nx) {
+        v[u] = reinterpret_cast<const uint4 *>(p.x)[idx];
+      } else if (idx < nx + nw) {
+        const int r = (idx - nx) / vec, c = (idx - nx) % vec;
+        if (e0 + r < p.E) v[u] = reinterpret_cast<const uint4 *>(p.router_w + (size_t)(e0 + r) * H)[c];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int idx = base + u * (int)blockDim.x + (int)threadIdx.x;
+      if (idx < nx + nw) xs[(idx / vec) * rs + idx % vec] = v[u];  // ws follows xs directly
+    }
   }
   __syncthreads();
   const int t = threadIdx.x >> 3, el = threadIdx.x & 7;
   if (t >= p.T || e0 + el >= p.E) return;
-  const uint4 *xr = reinterpret_cast<const uint4 *>(xs + (size_t)t * H);
-  const uint4 *wr = reinterpret_cast<const uint4 *>(ws + (size_t)el * H);
+  const uint4 *xr = xs + (size_t)t * rs;
+  const uint4 *wr = ws + (size_t)el * rs;
   float acc = 0.0f;
 #pragma unroll 4
   for (int c = 0; c < vec; ++c) {
@@ -207,6 +224,10 @@ __global__ void __launch_bounds__(256) k_router_decode(RouteParams p) {
   }
   if (p.logit_bias) acc = __fadd_rn(acc, p.logit_bias[e0 + el]);
   p.logits[(size_t)t * p.E + e0 + el] = acc;
+}
+__global__ void __launch_bounds__(256) k_router_decode(RouteParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  router_decode_block(p, smem_raw);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -230,23 +251,19 @@ __device__ __forceinline__ void warp_argmax(float &v, int &i, bool &has) {
   }
 }
 
-__global__ void __launch_bounds__(128) k_route_topk(RouteParams p) {
-  extern __shared__ float sm[];  // per warp: score[E] then choice[E]
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 4 + warp;
-  if (t >= p.T) return;
+// One warp scores token t and selects its experts; score/choice are E floats of shared memory
+// each, private to the warp.
+__device__ __forceinline__ void route_topk_token(const RouteParams &p, int t, float *score, float *choice, int lane) {
   const int E = p.E, k = min(p.k, p.E);
-  float *score = sm + (size_t)warp * 2 * E;
-  float *choice = score + E;
   const float *z = p.logits + (size_t)t * E;
   const float NEG_INF = __uint_as_float(0xff800000u);
 
   if (p.score == COLI_SCORE_SOFTMAX) {
     float mx = NEG_INF;
-    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);  // max is order-independent
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, __ldcg(z + e));  // max is order-independent
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-    for (int e = lane; e < E; e += 32) score[e] = coli_expf(__fsub_rn(z[e], mx));
+    for (int e = lane; e < E; e += 32) score[e] = coli_expf(__fsub_rn(__ldcg(z + e), mx));
     __syncwarp();
     float tot = 0.0f;  // sequential over e, every lane redundantly (moe.rs:1068)
     for (int e = 0; e < E; ++e) tot = __fadd_rn(tot, score[e]);
@@ -259,7 +276,7 @@ __global__ void __launch_bounds__(128) k_route_topk(RouteParams p) {
     }
   } else {
     for (int e = lane; e < E; e += 32) {
-      const float s = coli_sigmoidf(z[e]);
+      const float s = coli_sigmoidf(__ldcg(z + e));
       score[e] = s;
       choice[e] = __fadd_rn(s, p.select_bias ? p.select_bias[e] : 0.0f);
     }
@@ -300,30 +317,43 @@ __global__ void __launch_bounds__(128) k_route_topk(RouteParams p) {
     }
   }
 
-  // k rounds of arg-max over the allowed, not yet chosen experts
-  uint32_t chosen = 0;  // bit s = slot s of this lane already chosen
-  int my_idx = 0;       // lane kk keeps idx[kk]
-  float my_w = 0.0f;
-  for (int kk = 0; kk < k; ++kk) {
-    float bv = NEG_INF;
-    int bi = 0;
-    bool has = false;
-#pragma unroll 4
+  // k rounds of arg-max over the allowed, not yet chosen experts.  Every lane keeps the best of
+  // its own remaining experts as an order-preserving integer key (0 = none left; a candidate
+  // must be above -inf, as in the reference's scan from -inf with a strict compare); a round is
+  // two warp reductions -- the largest key, then the lowest expert id among its holders -- and
+  // only the winning lane rescans its experts.
+  const bool grouped = p.n_group > 1;
+  auto lane_best = [&](uint32_t chosen_mask, uint32_t &key, uint32_t &idx) {
+    key = 0u;
+    idx = 0xffffffffu;
     for (int s = 0; s < kMaxSlots; ++s) {
       const int e = lane + 32 * s;
       if (e >= E) break;
-      if ((chosen >> s) & 1u) continue;
-      if (!((gmask >> (e / gs)) & 1u)) continue;
+      if ((chosen_mask >> s) & 1u) continue;
+      if (grouped && !((gmask >> (e / gs)) & 1u)) continue;
       const float c = choice[e];
-      if (c > bv) {  // ascending e within the lane: strict > keeps the lowest index
-        bv = c;
-        bi = e;
-        has = true;
+      if (!(c > NEG_INF)) continue;
+      const uint32_t bits = __float_as_uint(__fadd_rn(c, 0.0f));  // -0 and +0 tie like the float compare
+      const uint32_t kk = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+      if (kk > key) {  // ascending e within the lane: strict > keeps the lowest index
+        key = kk;
+        idx = (uint32_t)e;
       }
     }
-    warp_argmax(bv, bi, has);
-    const int best = has ? bi : 0;
-    if ((best & 31) == lane) chosen |= 1u << (best >> 5);
+  };
+  uint32_t chosen = 0;  // bit s = slot s of this lane already chosen
+  int my_idx = 0;       // lane kk keeps idx[kk]
+  float my_w = 0.0f;
+  uint32_t bkey, bidx;
+  lane_best(chosen, bkey, bidx);
+  for (int kk = 0; kk < k; ++kk) {
+    const uint32_t top = __reduce_max_sync(0xffffffffu, bkey);
+    const uint32_t win = __reduce_min_sync(0xffffffffu, (top != 0u && bkey == top) ? bidx : 0xffffffffu);
+    const int best = top != 0u ? (int)win : 0;
+    if (top != 0u && (best & 31) == lane) {
+      chosen |= 1u << (best >> 5);
+      lane_best(chosen, bkey, bidx);
+    }
     if (lane == kk) {
       my_idx = best;
       my_w = score[best];
@@ -342,6 +372,14 @@ __global__ void __launch_bounds__(128) k_route_topk(RouteParams p) {
   }
 }
 
+__global__ void __launch_bounds__(128) k_route_topk(RouteParams p) {
+  extern __shared__ float sm[];  // per warp: score[E] then choice[E]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= p.T) return;
+  route_topk_token(p, t, sm + (size_t)warp * 2 * p.E, sm + (size_t)warp * 2 * p.E + p.E, lane);
+}
+
 int launch_router(const RouteParams &p, cudaStream_t st) {
   if (p.T <= 0) return 1;
   if (p.E > 32 * kMaxSlots) {
@@ -352,7 +390,7 @@ int launch_router(const RouteParams &p, cudaStream_t st) {
     coli_set_error("router: unsupported k=%d / n_group=%d for E=%d", p.k, p.n_group, p.E);
     return 0;
   }
-  const size_t dec_smem = (size_t)(p.T + 8) * p.H * sizeof(__nv_bfloat16);
+  const size_t dec_smem = (size_t)(p.T + 8) * (p.H + 8) * sizeof(__nv_bfloat16);
   if (p.T <= 8 && p.H % 8 == 0 && dec_smem <= 200 * 1024) {
     static bool attr_set = false;
     if (!attr_set) {
@@ -418,9 +456,62 @@ __global__ void __launch_bounds__(128) k_seg_count(PermuteParams p, int nchunk) 
   for (int e = lane; e < p.E; e += 32) p.chunk_cnt[(size_t)chunk * p.E + e] = cnt[e];
 }
 
+// Segment offsets and the work list from per-segment row counts in shared memory, by the whole
+// CTA: warp 0 runs a chunked shuffle scan over the counts (row offsets and item bases at once),
+// then one thread per segment writes that segment's items.  off and ibase hold nseg + 1 entries.
+// A serial walk by one thread costs ~60 ns per segment, more than the decode GEMV of a layer
+// with a few hundred experts.
+__device__ __forceinline__ void build_work_list(const PermuteParams &p, const int *cnt, int nseg, int max_items, int *off,
+                                                int *ibase) {
+  const int rpi = p.rows_per_item;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int run = 0, items = 0;
+    for (int base = 0; base < nseg; base += 32) {
+      const int s = base + lane;
+      const int n = s < nseg ? cnt[s] : 0;
+      const int ni = (n + rpi - 1) / rpi;
+      int a = n, b = ni;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int ua = __shfl_up_sync(0xffffffffu, a, o), ub = __shfl_up_sync(0xffffffffu, b, o);
+        if (lane >= o) {
+          a += ua;
+          b += ub;
+        }
+      }
+      if (s < nseg) {
+        off[s] = run + a - n;
+        ibase[s] = items + b - ni;
+      }
+      run += __shfl_sync(0xffffffffu, a, 31);
+      items += __shfl_sync(0xffffffffu, b, 31);
+    }
+    if (lane == 0) {
+      off[nseg] = run;
+      ibase[nseg] = items;
+      *p.n_items = min(items, max_items);
+    }
+  }
+  __syncthreads();
+  for (int s = threadIdx.x; s < nseg; s += blockDim.x) {
+    const int n = cnt[s], r0 = off[s];
+    int it = ibase[s];
+    for (int r = 0; r < n; r += rpi, ++it) {
+      if (it < max_items) {
+        p.item_seg[it] = s;
+        p.item_row0[it] = r0 + r;
+        p.item_nrows[it] = min(rpi, n - r);
+      }
+    }
+  }
+  __syncthreads();
+}
+
 __global__ void __launch_bounds__(1024) k_seg_scan(PermuteParams p, int nchunk, int max_items) {
   __shared__ int seg_cnt[1024 + 1];
   __shared__ int seg_off[1024 + 2];
+  __shared__ int seg_ibase[1024 + 2];
   const int E = p.E;
   const int nrt = p.nseg_routed;  // routed segments: E, or the experts resident on this rank
   const int nseg = nrt + (p.has_shared ? 1 : 0);
@@ -443,25 +534,7 @@ __global__ void __launch_bounds__(1024) k_seg_scan(PermuteParams p, int nchunk, 
   }
   if (threadIdx.x == 0 && p.has_shared) seg_cnt[nrt] = p.T;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int run = 0, items = 0;
-    for (int s = 0; s < nseg; ++s) {
-      seg_off[s] = run;
-      const int n = seg_cnt[s];
-      for (int r = 0; r < n; r += p.rows_per_item) {
-        if (items < max_items) {
-          p.item_seg[items] = s;
-          p.item_row0[items] = run + r;
-          p.item_nrows[items] = min(p.rows_per_item, n - r);
-        }
-        ++items;
-      }
-      run += n;
-    }
-    seg_off[nseg] = run;
-    *p.n_items = min(items, max_items);
-  }
-  __syncthreads();
+  build_work_list(p, seg_cnt, nseg, max_items, seg_off, seg_ibase);
   for (int s = threadIdx.x; s <= nseg; s += blockDim.x) p.seg_off[s] = seg_off[s];
   for (int s = threadIdx.x; s < nrt; s += blockDim.x) p.seg_count[s] = seg_cnt[s];
 }
@@ -506,30 +579,31 @@ __global__ void __launch_bounds__(256) k_permute(PermuteParams p) {
   }
 }
 
-// Decode-sized batches (T*k <= 1024 pairs): count, scan, work list and row positions in ONE
-// single-CTA launch instead of three (each launch costs about as much as the whole decode GEMV).
+// Decode-sized batches (T*k <= 1024 pairs): count, scan, work list and row positions by ONE CTA
+// instead of three launches (each launch costs about as much as the whole decode GEMV).
 // Same stable order as the three-kernel path: positions ascend with the token inside an expert.
-__global__ void __launch_bounds__(1024) k_permute_small(PermuteParams p, int max_items) {
-  __shared__ int cnt[1024 + 1];
-  __shared__ int off[1024 + 2];
-  __shared__ int rank_sm[1024];
-  if (blockIdx.x > 0) {  // the extra CTAs only write the token-order f16 copy of x
-    const size_t n = (size_t)p.T * p.H / 8;
-    const uint4 *src = reinterpret_cast<const uint4 *>(p.x);
-    uint4 *dst = reinterpret_cast<uint4 *>(p.x16);
-    for (size_t i = (size_t)(blockIdx.x - 1) * blockDim.x + threadIdx.x; i < n; i += (size_t)(gridDim.x - 1) * blockDim.x)
-      dst[i] = coli_bf16x8_to_f16x8(src[i]);
-    return;
-  }
+struct PermuteSmallSmem {
+  int cnt[1024 + 1];
+  int off[1024 + 2];
+  int rank[1024];
+  int idx[1024];
+  int ibase[1024 + 2];
+};
+__device__ __forceinline__ void permute_small_body(const PermuteParams &p, int max_items, PermuteSmallSmem &sm) {
+  int *cnt = sm.cnt, *off = sm.off, *rank_sm = sm.rank, *idx_sm = sm.idx;
   const int E = p.E, nrt = p.nseg_routed, nseg = nrt + (p.has_shared ? 1 : 0);
   const int npairs = p.T * p.k;
   for (int e = threadIdx.x; e <= E; e += blockDim.x) cnt[e] = 0;
+  // segment of every pair, fetched with independent loads before the ordered walk below
+  for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
+    const int e = p.topk_idx[i];
+    idx_sm[i] = p.expert_slot ? p.expert_slot[e] : e;
+  }
   __syncthreads();
   if (threadIdx.x < 32) {  // one warp walks the tokens in order; lane kk owns pair (t, kk)
     for (int t = 0; t < p.T; ++t) {
       if ((int)threadIdx.x < p.k) {
-        const int e = p.topk_idx[t * p.k + threadIdx.x];
-        const int s = p.expert_slot ? p.expert_slot[e] : e;
+        const int s = idx_sm[t * p.k + threadIdx.x];
         if (s >= 0) {
           rank_sm[t * p.k + threadIdx.x] = cnt[s];
           cnt[s] += 1;
@@ -537,33 +611,14 @@ __global__ void __launch_bounds__(1024) k_permute_small(PermuteParams p, int max
       }
       __syncwarp();
     }
+    if (threadIdx.x == 0 && p.has_shared) cnt[nrt] = p.T;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    if (p.has_shared) cnt[nrt] = p.T;
-    int run = 0, items = 0;
-    for (int s = 0; s < nseg; ++s) {
-      off[s] = run;
-      const int n = cnt[s];
-      for (int r = 0; r < n; r += p.rows_per_item) {
-        if (items < max_items) {
-          p.item_seg[items] = s;
-          p.item_row0[items] = run + r;
-          p.item_nrows[items] = min(p.rows_per_item, n - r);
-        }
-        ++items;
-      }
-      run += n;
-    }
-    off[nseg] = run;
-    *p.n_items = min(items, max_items);
-  }
-  __syncthreads();
+  build_work_list(p, cnt, nseg, max_items, off, sm.ibase);
   for (int s = threadIdx.x; s <= nseg; s += blockDim.x) p.seg_off[s] = off[s];
   for (int s = threadIdx.x; s < nrt; s += blockDim.x) p.seg_count[s] = cnt[s];
   for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
-    const int e = p.topk_idx[i];
-    const int s = p.expert_slot ? p.expert_slot[e] : e;
+    const int s = idx_sm[i];
     if (s < 0) {
       p.slot[i] = -1;
       continue;
@@ -580,8 +635,7 @@ __global__ void __launch_bounds__(1024) k_permute_small(PermuteParams p, int max
     for (int r = threadIdx.x >> 5; r < total; r += blockDim.x >> 5) {
       int t, pos;
       if (r < npairs) {
-        const int e = p.topk_idx[r];
-        const int s = p.expert_slot ? p.expert_slot[e] : e;
+        const int s = idx_sm[r];
         if (s < 0) continue;
         t = r / p.k;
         pos = off[s] + rank_sm[r];
@@ -596,6 +650,78 @@ __global__ void __launch_bounds__(1024) k_permute_small(PermuteParams p, int max
   }
 }
 
+__global__ void __launch_bounds__(1024) k_permute_small(PermuteParams p, int max_items) {
+  __shared__ PermuteSmallSmem sm;
+  if (blockIdx.x > 0) {  // the extra CTAs only write the token-order f16 copy of x
+    const size_t n = (size_t)p.T * p.H / 8;
+    const uint4 *src = reinterpret_cast<const uint4 *>(p.x);
+    uint4 *dst = reinterpret_cast<uint4 *>(p.x16);
+    for (size_t i = (size_t)(blockIdx.x - 1) * blockDim.x + threadIdx.x; i < n; i += (size_t)(gridDim.x - 1) * blockDim.x)
+      dst[i] = coli_bf16x8_to_f16x8(src[i]);
+    return;
+  }
+  permute_small_body(p, max_items, sm);
+}
+
+// Decode front end (T <= 8): router logits, top-k and the permutation in ONE launch.  Every CTA
+// computes the logits of 8 experts (and converts its slice of the staged tokens to f16); the CTA
+// that finishes last -- found with an atomic ticket, nobody waits for anybody -- scores the
+// tokens and builds the segments.  `ticket` must be zero at launch and is left zero.
+__global__ void __launch_bounds__(256) k_decode_front(RouteParams rp, PermuteParams pp, int max_items, unsigned int *ticket) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ PermuteSmallSmem psm;
+  __shared__ int is_last;
+  router_decode_block(rp, smem_raw);
+  if (pp.x16) {
+    const int n = rp.T * (rp.H / 8);
+    const int per = (n + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int lo = (int)blockIdx.x * per, hi = min(n, lo + per);
+    const uint4 *xs = reinterpret_cast<const uint4 *>(smem_raw);  // staged tokens, bf16, padded rows
+    const int vec = rp.H / 8;
+    uint4 *dst = reinterpret_cast<uint4 *>(pp.x16);
+    for (int i = lo + (int)threadIdx.x; i < hi; i += (int)blockDim.x) dst[i] = coli_bf16x8_to_f16x8(xs[(i / vec) * (vec + 1) + i % vec]);
+  }
+  __threadfence();  // this CTA's logits are visible device-wide before its ticket is
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = (atomicAdd(ticket, 1u) == gridDim.x - 1) ? 1 : 0;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+    float *sm = reinterpret_cast<float *>(smem_raw);  // the staging area is free now
+    for (int t = warp; t < rp.T; t += nwarp) route_topk_token(rp, t, sm + (size_t)warp * 2 * rp.E, sm + (size_t)warp * 2 * rp.E + rp.E, lane);
+  }
+  __syncthreads();  // the routing this CTA wrote is read back below
+  permute_small_body(pp, max_items, psm);
+  if (threadIdx.x == 0) *ticket = 0u;
+}
+
+static bool permute_small_ok(const PermuteParams &p) { return p.T * p.k <= 1024 && p.k <= 32 && p.E <= 1024; }
+static int permute_max_items(const PermuteParams &p) {
+  const int nseg = p.nseg_routed + (p.has_shared ? 1 : 0);
+  return (p.T * p.k + (p.has_shared ? p.T : 0)) / p.rows_per_item + nseg;
+}
+
+int launch_decode_front(const RouteParams &rp, const PermuteParams &pp, unsigned int *ticket, cudaStream_t st) {
+  const size_t stage = (size_t)(rp.T + 8) * (rp.H + 8) * sizeof(__nv_bfloat16);
+  const size_t topk = (size_t)8 * 2 * rp.E * sizeof(float);
+  const size_t smem = stage > topk ? stage : topk;
+  if (!(rp.T >= 1 && rp.T <= 8 && rp.H % 8 == 0 && smem <= 180 * 1024 && rp.E <= 32 * kMaxSlots && rp.k <= 32 &&
+        rp.n_group <= 32 && (rp.n_group <= 1 || rp.E % rp.n_group == 0) && permute_small_ok(pp) && ticket != nullptr))
+    return -1;  // not applicable: the caller runs the separate stages
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (!coli_cuda_check(cudaFuncSetAttribute(k_decode_front, cudaFuncAttributeMaxDynamicSharedMemorySize, 180 * 1024),
+                         "decode front shared-memory attribute"))
+      return 0;
+    attr_set = true;
+  }
+  k_decode_front<<<(rp.E + 7) / 8, 256, smem, st>>>(rp, pp, permute_max_items(pp), ticket);
+  coli_count_launch(1);
+  return coli_cuda_check(cudaGetLastError(), "decode front launch") ? 1 : 0;
+}
+
 int launch_permute(const PermuteParams &p, cudaStream_t st) {
   if (p.T <= 0) return 1;
   if (p.E > 1024) {
@@ -603,9 +729,8 @@ int launch_permute(const PermuteParams &p, cudaStream_t st) {
     return 0;
   }
   const int nchunk = (p.T + 31) / 32;
-  const int nseg = p.nseg_routed + (p.has_shared ? 1 : 0);
-  const int max_items = (p.T * p.k + (p.has_shared ? p.T : 0)) / p.rows_per_item + nseg;
-  if (p.T * p.k <= 1024 && p.k <= 32) {
+  const int max_items = permute_max_items(p);
+  if (permute_small_ok(p)) {
     int conv = 0;
     if (p.x16) {
       const size_t n = (size_t)p.T * p.H / 8;

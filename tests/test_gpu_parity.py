@@ -404,3 +404,26 @@ def test_tracing_phases_and_launch_count(gpu_backend):
     blk.profile(False)
     assert calls == 3 and all(v > 0 for v in ms.values())
     blk.close()
+
+
+def test_decode_front_is_one_launch(gpu_backend):
+    """T <= 8: router, top-k and permutation share one launch; repeated calls stay exact."""
+    import torch
+    from speedycolibri_b200 import _lib
+
+    shape = CONFIGS["tiny"]
+    layer, packed = host_layer(shape)
+    blk = make_block(shape, upload_layer(shape, packed))
+    xh = synth.host_tokens(shape)
+    x = torch.from_numpy(xh.view(np.int16)).cuda().view(torch.bfloat16)
+    n0 = _lib.load().coli_b200_launch_count()
+    blk.forward(x)
+    torch.cuda.synchronize()
+    assert _lib.load().coli_b200_launch_count() - n0 == 4  # front end, gate/up, down, combine
+    want_idx, want_w = layer.route_tokens(xh)
+    for _ in range(3):  # the ticket word returns to zero after every launch
+        blk.forward(x)
+        idx, w = blk.last_routing(shape.T)
+        assert np.array_equal(idx, want_idx)
+        assert np.array_equal(w.view(np.uint32), want_w.view(np.uint32))
+    blk.close()
