@@ -663,7 +663,7 @@ extern "C" int coli_b200_moe_block_dev(ColiMoe *m, const void *x_dev, void *out_
   const int rows = T * k + (m->has_shared ? T : 0);
   const bool tc = use_tc_path(m->L.fmt, rows, m->nseg) && m->xg != nullptr;
   const int rpi = tc ? colib::TC_MAX_TOKENS : rows_per_item_for(m->L, rows, m->nseg);
-  const int max_items = rows / rpi + m->nseg;
+  const int max_items = max_work_items(rows, m->nseg, rpi);
   const bool prof = m->profiling;
 #define COLI_MARK(i)                                                         \
   do {                                                                       \
@@ -868,7 +868,7 @@ static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, cons
   if (rows_cap == 0 || n_seg == 0) return 1;
   const bool tc = use_tc_path(m->L.fmt, rows_expected, n_seg);
   const int rpi = tc ? colib::TC_MAX_TOKENS : rows_per_item_for(m->L, rows_expected, n_seg);
-  const int max_items = rows_cap / rpi + n_seg;
+  const int max_items = max_work_items(rows_cap, n_seg, rpi);
   if (!ensure_h(m, (size_t)rows_cap) || !ensure_items(m, max_items)) return 0;
   if (!colib::launch_items_from_counts(seg_count_dev, n_seg, rpi, m->seg_off, m->item_seg, m->item_row0, m->item_nrows,
                                        m->n_items, st))
@@ -1024,7 +1024,7 @@ static int run_host_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *u
   cudaStream_t st = ctx->stream;
   const int avg = (int)((total + count - 1) / count);
   const int rpi = avg <= 8 ? 8 : avg <= 16 ? 16 : 32;
-  const int max_items = (int)(total / rpi) + count;
+  const int max_items = max_work_items((int)total, count, rpi);
   const size_t xb = (size_t)total * D;
   // slots: 0 x f32 / y f32, 1 x f16, 2 h f16, 3 tables + counts + work list
   const size_t tbl_bytes = sizeof(WeightRef) * 3 * count + sizeof(int32_t) * (2 * count + 2 + 3 * (size_t)max_items + 1);

@@ -13,16 +13,33 @@ __global__ void __launch_bounds__(256) k_combine(CombineParams p, const __nv_bfl
   float acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
-  for (int kk = 0; kk < p.k; ++kk) {
-    const float w = p.topk_w[(size_t)t * p.k + kk];
-    const int row = p.slot[(size_t)t * p.k + kk];
-    if (row < 0) continue;  // that expert lives on another rank, which adds its own partial
-    const uint4 v = *reinterpret_cast<const uint4 *>(p.y + (size_t)row * p.H + c * 8);
-    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+  // batches of 8 experts: all slots and weights, then all rows, are requested before the first
+  // is used (a load-use loop would pay two memory round trips per expert); the sum itself runs
+  // in ascending kk as the reference's does
+  for (int k0 = 0; k0 < p.k; k0 += 8) {
+    float w[8];
+    int row[8];
+    uint4 v[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      acc[2 * i] = fmaf(w, __uint_as_float(u[i] << 16), acc[2 * i]);
-      acc[2 * i + 1] = fmaf(w, __uint_as_float(u[i] & 0xffff0000u), acc[2 * i + 1]);
+    for (int j = 0; j < 8; ++j) {
+      const bool in = k0 + j < p.k;
+      w[j] = in ? p.topk_w[(size_t)t * p.k + k0 + j] : 0.0f;
+      row[j] = in ? p.slot[(size_t)t * p.k + k0 + j] : -1;  // < 0: the expert lives on another rank, which adds its own partial
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      v[j] = make_uint4(0, 0, 0, 0);
+      if (row[j] >= 0) v[j] = *reinterpret_cast<const uint4 *>(p.y + (size_t)row[j] * p.H + c * 8);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (row[j] < 0) continue;
+      const uint32_t u[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[2 * i] = fmaf(w[j], __uint_as_float(u[i] << 16), acc[2 * i]);
+        acc[2 * i + 1] = fmaf(w[j], __uint_as_float(u[i] & 0xffff0000u), acc[2 * i + 1]);
+      }
     }
   }
   if (shared_y) {

@@ -45,6 +45,10 @@ struct WeightRef {
 };
 
 static inline int round_up(int a, int b) { return (a + b - 1) / b * b; }
+// Upper bound of the work items `rows` rows in at most `nseg` segments cut into: a segment of n
+// rows gives ceil(n / rpi) <= n / rpi + 1 items and at most min(nseg, rows) segments hold a row.
+// Kernel grids are sized from this bound, so a loose one costs idle CTAs on every decode step.
+static inline int max_work_items(int rows, int nseg, int rpi) { return rows / rpi + (rows < nseg ? rows : nseg); }
 
 // ---- error reporting -------------------------------------------------------------------------
 void coli_set_error(const char *fmt, ...);

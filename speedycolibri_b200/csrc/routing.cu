@@ -699,8 +699,7 @@ __global__ void __launch_bounds__(256) k_decode_front(RouteParams rp, PermutePar
 
 static bool permute_small_ok(const PermuteParams &p) { return p.T * p.k <= 1024 && p.k <= 32 && p.E <= 1024; }
 static int permute_max_items(const PermuteParams &p) {
-  const int nseg = p.nseg_routed + (p.has_shared ? 1 : 0);
-  return (p.T * p.k + (p.has_shared ? p.T : 0)) / p.rows_per_item + nseg;
+  return max_work_items(p.T * p.k + (p.has_shared ? p.T : 0), p.nseg_routed + (p.has_shared ? 1 : 0), p.rows_per_item);
 }
 
 int launch_decode_front(const RouteParams &rp, const PermuteParams &pp, unsigned int *ticket, cudaStream_t st) {
