@@ -194,7 +194,7 @@ class ShardedMoe:
 
         return 0 if self.gloo else torch.cuda.current_stream().cuda_stream
 
-    STAGES = ("topk", "shared", "all_gather", "gather_local", "experts", "combine_partial", "reduce_scatter", "finish")
+    STAGES = ("topk", "all_gather", "gather_local", "experts", "combine_partial", "reduce_scatter+shared", "finish")
 
     def __call__(self, x, out=None, timing=None):
         """`timing`: optional dict that receives per-stage milliseconds (CUDA events on the current
@@ -226,9 +226,6 @@ class ShardedMoe:
         mark()
         dist.all_gather_into_tensor(self.idx_all, self.idx, group=self.group)
         dist.all_gather_into_tensor(self.w_all, self.w, group=self.group)
-        if b.has_shared:  # replicated weights, own tokens; independent of the exchange
-            b.shared_dev(x, self.shared_y, st)
-        mark()
         if gather_x is not None:
             gather_x.wait()
         mark()
@@ -238,11 +235,18 @@ class ShardedMoe:
         mark()
         b.combine_partial_dev(self.y_rows, self.slot, self.w_all, self.partial, st)
         mark()
+        # The shared expert (replicated weights, own tokens) is independent of the exchange: it
+        # runs on the compute stream while NCCL reduces the partial sums on its own stream.
         if self.gloo:  # gloo has no reduce-scatter: all-reduce and keep the own slice
             dist.all_reduce(self.partial, group=self.group)
             self.mine.copy_(self.partial[self.rank * self.Tl:(self.rank + 1) * self.Tl])
+            if b.has_shared:
+                b.shared_dev(x, self.shared_y, st)
         else:
-            dist.reduce_scatter_tensor(self.mine, self.partial, group=self.group)
+            rs = dist.reduce_scatter_tensor(self.mine, self.partial, group=self.group, async_op=True)
+            if b.has_shared:
+                b.shared_dev(x, self.shared_y, st)
+            rs.wait()
         mark()
         b.finish_dev(self.mine, self.shared_y, out, st)
         mark()

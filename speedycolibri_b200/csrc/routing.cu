@@ -79,14 +79,19 @@ __global__ void __launch_bounds__(256) k_router_gemm(RouteParams p) {
     }
 }
 
-// Router GEMM, prefill shape: 128 tokens x 64 experts per CTA, 8 x 4 outputs per thread, k-chunks
-// of 32 staged with 16-byte loads and stored transposed as f32, so the inner loop is three
-// 128-bit shared loads per 32 FMAs.  Same arithmetic as above: each output is one thread's
-// k-ascending fmaf chain.  Needs H % 8 == 0.
-template <int BM>
-__global__ void __launch_bounds__(256) k_router_gemm_big(RouteParams p) {
-  constexpr int TMR = BM / 16;  // token rows per thread
+// Router GEMM, batched shapes: BM tokens x 64 experts per CTA of NT threads, (BM*16/NT) x 4
+// outputs per thread, k-chunks of 32 staged with 16-byte loads and stored transposed as f32, so
+// the inner loop is a few 128-bit shared loads per block of FMAs.  Same arithmetic as above: each
+// output is one thread's k-ascending fmaf chain.  Needs H % 8 == 0.  The chain makes the kernel
+// issue-bound with a fixed time per CTA, so the variants trade work per thread against the number
+// of CTAs: the launcher takes the largest tile that still covers the SMs.
+template <int BM, int NT>
+__global__ void __launch_bounds__(NT) k_router_gemm_big(RouteParams p) {
+  constexpr int TMR = BM * 16 / NT;  // token rows per thread
   constexpr int BN = 64, BK = 32, LDX = BM + 4, LDW = BN + 4;
+  constexpr int SR = NT / 4;                  // rows staged per pass (4 chunks of 8 k each)
+  constexpr int XP = (BM + SR - 1) / SR, WP = BN / SR;
+  static_assert(TMR >= 1 && BN % SR == 0, "tile / thread-count mismatch");
   __shared__ __align__(16) float xs[BK][LDX];
   __shared__ __align__(16) float ws[BK][LDW];
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // tx -> 4 experts, ty -> TMR tokens
@@ -96,40 +101,45 @@ __global__ void __launch_bounds__(256) k_router_gemm_big(RouteParams p) {
   for (int i = 0; i < TMR; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
-  // staging assignment: x tile = BM rows x 4 chunks of 8 k (64 rows per pass), w tile = 64 rows x 4 chunks
-  constexpr int XP = (BM + 63) / 64;
-  const int sr = threadIdx.x >> 2, sc = threadIdx.x & 3;
-  uint4 xv[XP], wv;
+  // staging assignment: the threads of a warp take consecutive rows of one 8-k chunk, so their
+  // transposed stores fall into consecutive banks
+  const int sr = threadIdx.x % SR, sc = threadIdx.x / SR;
+  uint4 xv[XP], wv[WP];
   auto fetch = [&](int k0) {  // global -> registers; issued one chunk ahead of its use
+    const int k = k0 + sc * 8;
 #pragma unroll
     for (int h = 0; h < XP; ++h) {
-      const int m = m0 + sr + 64 * h, k = k0 + sc * 8;
+      const int m = m0 + sr + SR * h;
       xv[h] = make_uint4(0, 0, 0, 0);
-      if (sr + 64 * h < BM && m < p.T && k < p.H) xv[h] = *reinterpret_cast<const uint4 *>(p.x + (size_t)m * p.H + k);
+      if (sr + SR * h < BM && m < p.T && k < p.H) xv[h] = *reinterpret_cast<const uint4 *>(p.x + (size_t)m * p.H + k);
     }
-    const int n = n0 + sr, k = k0 + sc * 8;
-    wv = make_uint4(0, 0, 0, 0);
-    if (n < p.E && k < p.H) wv = *reinterpret_cast<const uint4 *>(p.router_w + (size_t)n * p.H + k);
+#pragma unroll
+    for (int h = 0; h < WP; ++h) {
+      const int n = n0 + sr + SR * h;
+      wv[h] = make_uint4(0, 0, 0, 0);
+      if (n < p.E && k < p.H) wv[h] = *reinterpret_cast<const uint4 *>(p.router_w + (size_t)n * p.H + k);
+    }
   };
   fetch(0);
   for (int k0 = 0; k0 < p.H; k0 += BK) {
     __syncthreads();  // the previous chunk has been consumed
 #pragma unroll
     for (int h = 0; h < XP; ++h) {
-      if (sr + 64 * h >= BM) break;
+      if (sr + SR * h >= BM) break;
       const uint32_t u[4] = {xv[h].x, xv[h].y, xv[h].z, xv[h].w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        xs[sc * 8 + 2 * j][sr + 64 * h] = __uint_as_float(u[j] << 16);
-        xs[sc * 8 + 2 * j + 1][sr + 64 * h] = __uint_as_float(u[j] & 0xffff0000u);
+        xs[sc * 8 + 2 * j][sr + SR * h] = __uint_as_float(u[j] << 16);
+        xs[sc * 8 + 2 * j + 1][sr + SR * h] = __uint_as_float(u[j] & 0xffff0000u);
       }
     }
-    {
-      const uint32_t u[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+    for (int h = 0; h < WP; ++h) {
+      const uint32_t u[4] = {wv[h].x, wv[h].y, wv[h].z, wv[h].w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        ws[sc * 8 + 2 * j][sr] = __uint_as_float(u[j] << 16);
-        ws[sc * 8 + 2 * j + 1][sr] = __uint_as_float(u[j] & 0xffff0000u);
+        ws[sc * 8 + 2 * j][sr + SR * h] = __uint_as_float(u[j] << 16);
+        ws[sc * 8 + 2 * j + 1][sr + SR * h] = __uint_as_float(u[j] & 0xffff0000u);
       }
     }
     __syncthreads();
@@ -146,6 +156,10 @@ __global__ void __launch_bounds__(256) k_router_gemm_big(RouteParams p) {
           a[4 * q + 2] = v.z;
           a[4 * q + 3] = v.w;
         }
+      } else if (TMR == 2) {
+        const float2 v = *reinterpret_cast<const float2 *>(&xs[kk][ty * 2]);
+        a[0] = v.x;
+        a[TMR - 1] = v.y;
       } else {
 #pragma unroll
         for (int i = 0; i < TMR; ++i) a[i] = xs[kk][ty * TMR + i];
@@ -400,17 +414,21 @@ int launch_router(const RouteParams &p, cudaStream_t st) {
     k_router_decode<<<(p.E + 7) / 8, 256, dec_smem, st>>>(p);  // 256 threads stage the rows, T*8 of them walk the chains
     coli_count_launch(1);
   } else {
-    // the largest tile that still gives ~one CTA per SM; every variant has identical arithmetic
+    // the largest tile that still covers the SMs; every variant has identical arithmetic
     auto blocks = [&](int bm, int bn) { return (long)((p.T + bm - 1) / bm) * ((p.E + bn - 1) / bn); };
-    if (p.H % 8 == 0 && blocks(128, 64) >= 96) {
+    const long want = 120;
+    if (p.H % 8 == 0 && blocks(128, 64) >= want) {
       dim3 grid((p.E + 63) / 64, (p.T + 127) / 128);
-      k_router_gemm_big<128><<<grid, 256, 0, st>>>(p);
-    } else if (p.H % 8 == 0 && p.T >= 64) {  // one wave of 64x64 tiles: 8 x 4 register tiles keep the FMA pipe fed
+      k_router_gemm_big<128, 256><<<grid, 256, 0, st>>>(p);
+    } else if (p.H % 8 == 0 && blocks(64, 64) >= want) {
       dim3 grid((p.E + 63) / 64, (p.T + 63) / 64);
-      k_router_gemm_big<64><<<grid, 256, 0, st>>>(p);
-    } else if (p.H % 8 == 0 && p.T >= 32) {
+      k_router_gemm_big<64, 256><<<grid, 256, 0, st>>>(p);
+    } else if (p.H % 8 == 0 && blocks(32, 64) >= want) {
       dim3 grid((p.E + 63) / 64, (p.T + 31) / 32);
-      k_router_gemm_big<32><<<grid, 256, 0, st>>>(p);
+      k_router_gemm_big<32, 128><<<grid, 128, 0, st>>>(p);
+    } else if (p.H % 8 == 0 && p.T >= 16) {
+      dim3 grid((p.E + 63) / 64, (p.T + 15) / 16);
+      k_router_gemm_big<16, 128><<<grid, 128, 0, st>>>(p);
     } else if (blocks(32, 32) >= 96) {
       dim3 grid((p.E + 31) / 32, (p.T + 31) / 32);
       k_router_gemm<2, 2><<<grid, 256, 0, st>>>(p);
