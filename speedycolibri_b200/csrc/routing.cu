@@ -92,8 +92,11 @@ __global__ void __launch_bounds__(NT) k_router_gemm_big(RouteParams p) {
   constexpr int SR = NT / 4;                  // rows staged per pass (4 chunks of 8 k each)
   constexpr int XP = (BM + SR - 1) / SR, WP = BN / SR;
   static_assert(TMR >= 1 && BN % SR == 0, "tile / thread-count mismatch");
-  __shared__ __align__(16) float xs[BK][LDX];
-  __shared__ __align__(16) float ws[BK][LDW];
+  // two buffers of each staged tile: chunk i+1 is written while chunk i is multiplied, so one
+  // barrier per chunk suffices
+  extern __shared__ __align__(16) float rsm[];
+  float(*xs)[BK][LDX] = reinterpret_cast<float(*)[BK][LDX]>(rsm);                  // [2][BK][LDX]
+  float(*ws)[BK][LDW] = reinterpret_cast<float(*)[BK][LDW]>(rsm + 2 * BK * LDX);   // [2][BK][LDW]
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // tx -> 4 experts, ty -> TMR tokens
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   float acc[TMR][4];
@@ -120,17 +123,15 @@ __global__ void __launch_bounds__(NT) k_router_gemm_big(RouteParams p) {
       if (n < p.E && k < p.H) wv[h] = *reinterpret_cast<const uint4 *>(p.router_w + (size_t)n * p.H + k);
     }
   };
-  fetch(0);
-  for (int k0 = 0; k0 < p.H; k0 += BK) {
-    __syncthreads();  // the previous chunk has been consumed
+  auto stage = [&](int buf) {  // registers -> shared memory, bf16 -> f32, transposed
 #pragma unroll
     for (int h = 0; h < XP; ++h) {
       if (sr + SR * h >= BM) break;
       const uint32_t u[4] = {xv[h].x, xv[h].y, xv[h].z, xv[h].w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        xs[sc * 8 + 2 * j][sr + SR * h] = __uint_as_float(u[j] << 16);
-        xs[sc * 8 + 2 * j + 1][sr + SR * h] = __uint_as_float(u[j] & 0xffff0000u);
+        xs[buf][sc * 8 + 2 * j][sr + SR * h] = __uint_as_float(u[j] << 16);
+        xs[buf][sc * 8 + 2 * j + 1][sr + SR * h] = __uint_as_float(u[j] & 0xffff0000u);
       }
     }
 #pragma unroll
@@ -138,39 +139,49 @@ __global__ void __launch_bounds__(NT) k_router_gemm_big(RouteParams p) {
       const uint32_t u[4] = {wv[h].x, wv[h].y, wv[h].z, wv[h].w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        ws[sc * 8 + 2 * j][sr + SR * h] = __uint_as_float(u[j] << 16);
-        ws[sc * 8 + 2 * j + 1][sr + SR * h] = __uint_as_float(u[j] & 0xffff0000u);
+        ws[buf][sc * 8 + 2 * j][sr + SR * h] = __uint_as_float(u[j] << 16);
+        ws[buf][sc * 8 + 2 * j + 1][sr + SR * h] = __uint_as_float(u[j] & 0xffff0000u);
       }
     }
-    __syncthreads();
-    if (k0 + BK < p.H) fetch(k0 + BK);  // in flight while this chunk is multiplied
+  };
+  fetch(0);
+  stage(0);
+  __syncthreads();
+  if (BK < p.H) fetch(BK);
+  int buf = 0;
+  for (int k0 = 0; k0 < p.H; k0 += BK, buf ^= 1) {
 #pragma unroll 8
     for (int kk = 0; kk < BK; ++kk) {
       float a[TMR];
       if (TMR >= 4) {
 #pragma unroll
         for (int q = 0; q < TMR / 4; ++q) {
-          const float4 v = *reinterpret_cast<const float4 *>(&xs[kk][ty * TMR + 4 * q]);
+          const float4 v = *reinterpret_cast<const float4 *>(&xs[buf][kk][ty * TMR + 4 * q]);
           a[4 * q] = v.x;
           a[4 * q + 1] = v.y;
           a[4 * q + 2] = v.z;
           a[4 * q + 3] = v.w;
         }
       } else if (TMR == 2) {
-        const float2 v = *reinterpret_cast<const float2 *>(&xs[kk][ty * 2]);
+        const float2 v = *reinterpret_cast<const float2 *>(&xs[buf][kk][ty * 2]);
         a[0] = v.x;
         a[TMR - 1] = v.y;
       } else {
 #pragma unroll
-        for (int i = 0; i < TMR; ++i) a[i] = xs[kk][ty * TMR + i];
+        for (int i = 0; i < TMR; ++i) a[i] = xs[buf][kk][ty * TMR + i];
       }
-      const float4 b = *reinterpret_cast<const float4 *>(&ws[kk][tx * 4]);
+      const float4 b = *reinterpret_cast<const float4 *>(&ws[buf][kk][tx * 4]);
       const float bb[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
       for (int i = 0; i < TMR; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = __fmaf_rn(a[i], bb[j], acc[i][j]);
     }
+    if (k0 + BK < p.H) {
+      stage(buf ^ 1);  // chunk k0 + BK, fetched while this one was multiplied; that buffer was last read one barrier ago
+      if (k0 + 2 * BK < p.H) fetch(k0 + 2 * BK);
+    }
+    __syncthreads();
   }
 #pragma unroll
   for (int i = 0; i < TMR; ++i)
@@ -394,6 +405,20 @@ __global__ void __launch_bounds__(128) k_route_topk(RouteParams p) {
   route_topk_token(p, t, sm + (size_t)warp * 2 * p.E, sm + (size_t)warp * 2 * p.E + p.E, lane);
 }
 
+template <int BM, int NT>
+static bool launch_router_big(const RouteParams &p, dim3 grid, cudaStream_t st) {
+  constexpr size_t smem = (size_t)2 * 32 * ((BM + 4) + (64 + 4)) * sizeof(float);
+  static bool attr_set = false;
+  if (!attr_set && smem > 48 * 1024) {
+    if (!coli_cuda_check(cudaFuncSetAttribute(k_router_gemm_big<BM, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                         "router shared-memory attribute"))
+      return false;
+    attr_set = true;
+  }
+  k_router_gemm_big<BM, NT><<<grid, NT, smem, st>>>(p);
+  return true;
+}
+
 int launch_router(const RouteParams &p, cudaStream_t st) {
   if (p.T <= 0) return 1;
   if (p.E > 32 * kMaxSlots) {
@@ -419,16 +444,16 @@ int launch_router(const RouteParams &p, cudaStream_t st) {
     const long want = 120;
     if (p.H % 8 == 0 && blocks(128, 64) >= want) {
       dim3 grid((p.E + 63) / 64, (p.T + 127) / 128);
-      k_router_gemm_big<128, 256><<<grid, 256, 0, st>>>(p);
+      if (!launch_router_big<128, 256>(p, grid, st)) return 0;
     } else if (p.H % 8 == 0 && blocks(64, 64) >= want) {
       dim3 grid((p.E + 63) / 64, (p.T + 63) / 64);
-      k_router_gemm_big<64, 256><<<grid, 256, 0, st>>>(p);
+      if (!launch_router_big<64, 256>(p, grid, st)) return 0;
     } else if (p.H % 8 == 0 && blocks(32, 64) >= want) {
       dim3 grid((p.E + 63) / 64, (p.T + 31) / 32);
-      k_router_gemm_big<32, 128><<<grid, 128, 0, st>>>(p);
+      if (!launch_router_big<32, 128>(p, grid, st)) return 0;
     } else if (p.H % 8 == 0 && p.T >= 16) {
       dim3 grid((p.E + 63) / 64, (p.T + 15) / 16);
-      k_router_gemm_big<16, 128><<<grid, 128, 0, st>>>(p);
+      if (!launch_router_big<16, 128>(p, grid, st)) return 0;
     } else if (blocks(32, 32) >= 96) {
       dim3 grid((p.E + 31) / 32, (p.T + 31) / 32);
       k_router_gemm<2, 2><<<grid, 256, 0, st>>>(p);
