@@ -41,6 +41,20 @@ def measured_peaks():
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
 
 
+# DRAM bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum) of the expert kernels,
+# keyed by (workload, tokens, kernel).  The c3 figures are the c3s capture (same matrices, 1/8 of
+# the experts and tokens, so 1/8 of every stream) times 8: a full c3 launch holds too much on
+# the device for a multi-pass capture.  The captures are summarised under profiles/.
+NCU_TRAFFIC = {
+    ("c3", 4096, "gate_up"): (8 * (622756608 + 11324672), "profiles/k_ffn_tc_c3s_full.md, c3s capture x 8"),
+    ("c3", 4096, "down"): (8 * (293647872 + 23667200), "profiles/k_ffn_tc_c3s_full.md, c3s capture x 8"),
+    ("c3s", 512, "gate_up"): (622756608 + 11324672, "profiles/k_ffn_tc_c3s_full.md"),
+    ("c3s", 512, "down"): (293647872 + 23667200, "profiles/k_ffn_tc_c3s_full.md"),
+    ("c1", 8, "gate_up"): (92070144 + 2123008, "profiles/k_ffn_mm_c1_full.md"),
+    ("c1", 8, "down"): (46130688 + 72192, "profiles/k_ffn_mm_c1_full.md"),
+}
+
+
 class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
 
@@ -335,7 +349,8 @@ def run_ours(args):
         else:
             ach = kern[dom]["bytes"] / t_s / 1e9
             roofline = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"]}
-        roofline.update({"traffic": None, "kernel": dom, "kernel_ms": phases[dom], "peak_source": f"of {peaks['source']}",
+        traffic = NCU_TRAFFIC.get((shape.name, shape.T, dom))
+        roofline.update({"traffic": traffic[0] if traffic else None, "traffic_source": traffic[1] if traffic else None, "kernel": dom, "kernel_ms": phases[dom], "peak_source": f"of {peaks['source']}",
                          "algorithmic_bytes": kern[dom]["bytes"], "algorithmic_flops": kern[dom]["flops"],
                          "hbm_frac": kern[dom]["bytes"] / t_s / 1e9 / peaks["hbm_gbs"],
                          "tensor_frac_bf16": kern[dom]["flops"] / t_s / 1e12 / tc_peak, "active_experts": active})
@@ -361,7 +376,7 @@ def run_ours(args):
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-                "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "vs_baseline": None, "dtype": "f16", "data": "synthetic",
                 "config": config_dict(shape, world, {"l2": "weights streamed per step exceed the 126 MB L2"
                                                      if shape.bytes_moved(shape.E) > 4 * 126e6 else "working set may sit in L2"}),
                 "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks}
