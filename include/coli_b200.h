@@ -176,7 +176,8 @@ int coli_b200_moe_local_experts(const ColiMoe *moe);
 int coli_b200_moe_topk_dev(ColiMoe *moe, const void *x_dev, int T, int32_t *topk_idx_dev, float *topk_w_dev,
                            void *stream);
 /* For routing topk_idx_dev[T,k] over x_dev[T,H]: copy the rows of the (token, kk) pairs whose
- * expert is resident here into rows_dev (bf16, capacity T*k rows), expert-contiguous in ascending
+ * expert is resident here into rows_dev (2 bytes per element, capacity T*k rows; the encoding is
+ * the library's own -- the bf16 values held as f16 -- and only experts_dev reads it), expert-contiguous in ascending
  * expert id, tokens ascending inside an expert (moe.rs:1373-1387).  seg_count_dev[n_local]
  * receives the rows per resident expert, slot_dev[T*k] the row of each pair or -1. */
 int coli_b200_moe_gather_local_dev(ColiMoe *moe, const void *x_dev, const int32_t *topk_idx_dev, int T, void *rows_dev,
