@@ -11,9 +11,11 @@
 // * B operand (N side): up to 256 token rows x 64 k of f16 activations, copied by TMA
 //   (cp.async.bulk.tensor, 128-byte swizzle, no multicast) straight into the same layout.
 // * tcgen05.mma kind::f16 (f16 x f16 -> f32), issued by one thread, accumulates in TMEM; the
-//   gate and the up projection of the same 128 features use two accumulators (columns 0.. and
-//   256..) fed from the same token tile, so SiLU(g)*u is formed in the epilogue registers and
-//   only h is written.
+//   gate and the up projection of the same 128 features use two accumulators fed from the same
+//   token tile, so SiLU(g)*u is formed in the epilogue registers and only h is written.  The 512
+//   TMEM columns hold two such accumulator pairs when a tile has at most 128 tokens, so the
+//   epilogue of one tile drains while the MMAs of the next one run; a tile of up to 256 tokens
+//   takes all 512 columns.
 // * 4 epilogue warps read TMEM with tcgen05.ld (one lane = one feature), apply the per-tensor
 //   scale, the activation, and store h (f16 holding the bf16-rounded value) or y (bf16).
 // Roles are warp-specialised and synchronise through mbarriers only; the kernel is persistent
@@ -77,14 +79,15 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false when the barrier did not flip in time or another role gave up.
-// `sleep_ns` > 0 backs off between polls (for waits that normally last a whole main loop), so
-// that a waiting role does not take issue slots from the producer warps.
+// sleep_ns = 0 polls with test_wait (never suspends); 1 polls with try_wait, which the hardware
+// may suspend for a short while (stage-ring waits: no hot spin next to the producer warps, and
+// measured no slower); > 1 additionally sleeps between polls (waits that normally last a whole
+// main loop).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code,
                                           uint32_t sleep_ns = 0) {
   for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
-    // waits on the critical path of the stage ring poll without suspending; long waits suspend
     if (sleep_ns ? mbar_try_wait(bar, parity) : mbar_test_wait(bar, parity)) return true;
-    if (sleep_ns && i >= 8) __nanosleep(sleep_ns);
+    if (sleep_ns > 1 && i >= 8) __nanosleep(sleep_ns);
     if ((i & 63u) == 63u && *abort_flag) return false;
   }
   *abort_flag = 1;
@@ -224,8 +227,10 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
   const uint32_t full_a = smem_u32(bars), full_b = smem_u32(bars + STAGES), empty = smem_u32(bars + 2 * STAGES);
-  const uint32_t acc_full = smem_u32(bars + 3 * STAGES), acc_empty = smem_u32(bars + 3 * STAGES + 1);
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * STAGES + 2);
+  // two accumulator buffers (each: two accumulators of <= 128 token columns); a tile of more than
+  // 128 tokens takes both
+  const uint32_t acc_full = smem_u32(bars + 3 * STAGES), acc_empty = smem_u32(bars + 3 * STAGES + 2);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * STAGES + 4);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   volatile int *prod_ok = reinterpret_cast<volatile int *>(tmem_slot + 2);
 
@@ -243,8 +248,10 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
       mbar_init(full_b + 8 * s, 1);
       mbar_init(empty + 8 * s, 1);
     }
-    mbar_init(acc_full, 1);
-    mbar_init(acc_empty, TC_EPI_WARPS);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full + 8 * b, 1);
+      mbar_init(acc_empty + 8 * b, TC_EPI_WARPS);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -286,19 +293,31 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
   } else if (warp == 1) {
     // ---------------- MMA issue ----------------
     if (lane == 0) {
-      uint32_t it = 0, tix = 0;
+      uint32_t it = 0, small_units = 0;
+      uint32_t waits[2] = {0u, 0u};  // completed waits on each buffer's "drained" barrier
       bool alive = true;
-      for (int w = blockIdx.x; w < n_work && alive; w += gridDim.x, ++tix) {
+      for (int w = blockIdx.x; w < n_work && alive; w += gridDim.x) {
         const int item = w / n_ftiles;
         const int nrows = p.item_nrows[item];
         const int N = (nrows + TC_BOXN - 1) / TC_BOXN * TC_BOXN;
         const uint32_t idesc = umma_idesc(N);
-        if (!mbar_wait(acc_empty, (tix & 1u) ^ 1u, abort_flag, p.status, TC_ERR_MMA_WAIT)) break;
+        // Tiles of <= 128 tokens alternate between the two accumulator buffers, so the epilogue
+        // of one tile drains while the next tile's MMAs run; a wider tile needs both buffers.
+        const bool big = N > TC_MAX_TOKENS / 2;
+        const uint32_t buf = big ? 0u : (small_units++ & 1u);
+        bool ok = true;
+        for (uint32_t b = big ? 0u : buf; ok && b <= (big ? 1u : buf); ++b) {
+          ok = mbar_wait(acc_empty + 8 * b, (waits[b] & 1u) ^ 1u, abort_flag, p.status, TC_ERR_MMA_WAIT);
+          waits[b]++;
+        }
+        if (!ok) break;
+        const uint32_t acc0 = tmem_base + buf * TC_MAX_TOKENS;
+        const uint32_t acc1 = acc0 + (big ? TC_MAX_TOKENS : TC_MAX_TOKENS / 2);
         tc_fence_after();
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-          if (!mbar_wait(full_a + 8 * s, ph, abort_flag, p.status, TC_ERR_MMA_WAIT) ||
-              !mbar_wait(full_b + 8 * s, ph, abort_flag, p.status, TC_ERR_MMA_WAIT)) {
+          if (!mbar_wait(full_a + 8 * s, ph, abort_flag, p.status, TC_ERR_MMA_WAIT, 1) ||
+              !mbar_wait(full_b + 8 * s, ph, abort_flag, p.status, TC_ERR_MMA_WAIT, 1)) {
             alive = false;
             break;
           }
@@ -309,38 +328,43 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
           for (int k4 = 0; k4 < TC_BK / 16; ++k4) {
             const uint64_t bd = umma_smem_desc(b0 + k4 * 32);
             const uint32_t acc = (kb | k4) ? 1u : 0u;
-            umma_f16(tmem_base, umma_smem_desc(a0 + k4 * 32), bd, idesc, acc);
-            umma_f16(tmem_base + TC_MAX_TOKENS, umma_smem_desc(a0 + TC_A_BYTES + k4 * 32), bd, idesc, acc);
+            umma_f16(acc0, umma_smem_desc(a0 + k4 * 32), bd, idesc, acc);
+            umma_f16(acc1, umma_smem_desc(a0 + TC_A_BYTES + k4 * 32), bd, idesc, acc);
           }
           umma_commit(empty + 8 * s);  // the stage may be refilled once these MMAs have read it
         }
-        if (alive) umma_commit(acc_full);
+        if (alive) umma_commit(acc_full + 8 * buf);
       }
     }
   } else if (warp < 2 + TC_EPI_WARPS) {
     // ---------------- epilogue: TMEM -> registers -> global ----------------
     const int lg = warp & 3;  // TMEM lane group this warp may read
-    uint32_t tix = 0;
-    for (int w = blockIdx.x; w < n_work; w += gridDim.x, ++tix) {
+    uint32_t small_units = 0;
+    uint32_t fills[2] = {0u, 0u};  // completed waits on each buffer's "filled" barrier
+    for (int w = blockIdx.x; w < n_work; w += gridDim.x) {
       const int item = w / n_ftiles, ft = w % n_ftiles;
       const int seg = p.item_seg[item], row0 = p.item_row0[item], nrows = p.item_nrows[item];
       const int ex = p.seg_expert ? p.seg_expert[seg] : seg;
       const int N = (nrows + TC_BOXN - 1) / TC_BOXN * TC_BOXN;
       const float s0 = GATED ? p.gate[ex].g : p.down[ex].g;
       const float s1 = GATED ? p.up[ex].g : p.down[ex].g;
+      const bool big = N > TC_MAX_TOKENS / 2;  // same buffer walk as the MMA warp
+      const uint32_t buf = big ? 0u : (small_units++ & 1u);
       bool ok = true;
-      if (lane == 0) ok = mbar_wait(acc_full, tix & 1u, abort_flag, p.status, TC_ERR_EPI_WAIT, 256);
+      if (lane == 0) ok = mbar_wait(acc_full + 8 * buf, fills[buf] & 1u, abort_flag, p.status, TC_ERR_EPI_WAIT, 256);
+      fills[buf]++;
       ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
       if (!ok) break;
       tc_fence_after();
       const int f = ft * FT + lg * 32 + lane;  // accumulator 0; accumulator 1 is feature f + 128 of down
-      const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16);
+      const uint32_t tbase = tmem_base + buf * TC_MAX_TOKENS + ((uint32_t)(lg * 32) << 16);
+      const uint32_t acc1_off = big ? TC_MAX_TOKENS : TC_MAX_TOKENS / 2;
       __half *out_h = p.h + (size_t)row0 * Oout + f;
       __nv_bfloat16 *out_y = p.y + (size_t)row0 * Oout + f;
       for (int c0 = 0; c0 < N; c0 += 16) {
         uint32_t g[16], u[16];
         tmem_ld16(tbase + c0, g);
-        tmem_ld16(tbase + TC_MAX_TOKENS + c0, u);
+        tmem_ld16(tbase + acc1_off + c0, u);
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
@@ -359,7 +383,10 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty);
+      if (lane == 0) {
+        mbar_arrive(acc_empty + 8 * buf);
+        if (big) mbar_arrive(acc_empty + 8);
+      }
     }
   } else {
     // ---------------- weight producers: HBM -> registers -> f16 -> swizzled shared memory ----------------
@@ -399,7 +426,7 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
             // One thread polls the mbarrier for all producer warps and releases them through a
             // hardware named barrier: many warps polling one mbarrier word serialise in the
             // shared-memory pipe and each poll then costs hundreds of cycles.
-            if (pt == 0) *prod_ok = mbar_wait(empty + 8 * s, ph ^ 1u, abort_flag, p.status, TC_ERR_PROD_WAIT) ? 1 : 0;
+            if (pt == 0) *prod_ok = mbar_wait(empty + 8 * s, ph ^ 1u, abort_flag, p.status, TC_ERR_PROD_WAIT, 1) ? 1 : 0;
             asm volatile("bar.sync 1, %0;" ::"r"(TC_PROD_WARPS * 32) : "memory");
             ok = *prod_ok != 0;
             if (!ok) {
@@ -470,7 +497,7 @@ template <bool GATED>
 static int launch_tc(const TcParams &p, const void *rows_base, int rows_cap, int sm_count, cudaStream_t st) {
   constexpr int MATS = 2;
   constexpr int STAGES = 3;
-  const size_t smem = (size_t)STAGES * (MATS * TC_A_BYTES + TC_B_BYTES) + 1024 /*align*/ + 8 * (3 * STAGES + 2) + 16 + 64;
+  const size_t smem = (size_t)STAGES * (MATS * TC_A_BYTES + TC_B_BYTES) + 1024 /*align*/ + 8 * (3 * STAGES + 4) + 16 + 64;
   static bool attr_done = false;
   if (!attr_done) {
     if (!coli_cuda_check(cudaFuncSetAttribute(k_ffn_tc<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
