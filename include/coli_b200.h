@@ -50,8 +50,10 @@ int coli_cuda_device_at(int index);
 int coli_cuda_mem_info(int device, size_t *free_bytes, size_t *total_bytes);
 /* backend_cuda.h:46. */
 int coli_cuda_device_sync(int device);
-/* backend_cuda.h:31.  Only the plain SiLU SwiGLU (oai = 0, limit = 0) is implemented; after
- * any other setting the expert calls return 0. */
+/* backend_cuda.h:31; same three forms as backend_cuda.cu:380-392: oai != 0 clamped OpenAI-SwiGLU
+ * (math.rs:143-148), oai == 0 with limit > 0 SwiGLU under the asymmetric clamp (dsv4.rs:738-742),
+ * otherwise plain SiLU SwiGLU.  Process-wide; a ColiMoe handle keeps the setting it was created
+ * under, the host-pointer expert calls read it per call. */
 void coli_cuda_set_activation(int oai, float alpha, float limit);
 /* backend_cuda.h:48.  Resident tensors on `device` (< 0: all devices). */
 void coli_cuda_stats(int device, size_t *tensor_count, size_t *tensor_bytes);

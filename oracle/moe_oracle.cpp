@@ -201,7 +201,17 @@ void orc_matmul_qt(int fmt, const uint8_t *q, const void *s, float g, const floa
   });
 }
 
-// SwiGLU FFN of one expert over nr rows (moe.rs:1187-1230, SiLU arm).
+// Process-wide activation setting, as the reference keeps it (gpu::set_activation, moe.rs:103).
+static int g_orc_oai = 0;
+static float g_orc_alpha = 1.702f, g_orc_limit = 0.0f;
+void orc_set_activation(int oai, float alpha, float limit) {
+  g_orc_oai = oai;
+  g_orc_alpha = alpha;
+  g_orc_limit = limit;
+}
+float orc_act_combine(float g, float u, int oai, float alpha, float limit) { return coli_act_combine(g, u, oai, alpha, limit); }
+
+// Gated FFN of one expert over nr rows (moe.rs:1187-1230: SiLU, clamped and OpenAI arms).
 static void ffn(const OrcLayer *L, int ei, const float *x, int nr, float *out) {
   const int H = L->H, I = L->I;
   if (!L->gate_q[ei] || !L->up_q[ei] || !L->down_q[ei]) {
@@ -213,7 +223,7 @@ static void ffn(const OrcLayer *L, int ei, const float *x, int nr, float *out) {
   std::vector<float> g((size_t)nr * I), u((size_t)nr * I);
   orc_matmul_qt(L->fmt, L->gate_q[ei], L->gate_s[ei], gg, x, g.data(), nr, H, I);
   orc_matmul_qt(L->fmt, L->up_q[ei], L->up_s[ei], ug, x, u.data(), nr, H, I);
-  for (size_t j = 0; j < g.size(); ++j) g[j] = coli_siluf(g[j]) * u[j];
+  for (size_t j = 0; j < g.size(); ++j) g[j] = coli_act_combine(g[j], u[j], g_orc_oai, g_orc_alpha, g_orc_limit);
   orc_matmul_qt(L->fmt, L->down_q[ei], L->down_s[ei], dg, g.data(), out, nr, I, H);
 }
 

@@ -56,6 +56,8 @@ def lib() -> C.CDLL:
         L.orc_expf.restype, L.orc_expf.argtypes = f, [f]
         L.orc_sigmoidf.restype, L.orc_sigmoidf.argtypes = f, [f]
         L.orc_siluf.restype, L.orc_siluf.argtypes = f, [f]
+        L.orc_set_activation.restype, L.orc_set_activation.argtypes = None, [i, f, f]
+        L.orc_act_combine.restype, L.orc_act_combine.argtypes = f, [f, f, i, f, f]
         L.orc_expf_array.restype, L.orc_expf_array.argtypes = None, [P, P, C.c_int64]
         L.orc_quantize_nvfp4.restype, L.orc_quantize_nvfp4.argtypes = None, [P, i, i, P, P, C.POINTER(f)]
         L.orc_quantize_fp8_b128.restype, L.orc_quantize_fp8_b128.argtypes = None, [P, i, i, P, P]
@@ -79,6 +81,16 @@ def _p(a):
 
 def set_threads(n: int) -> None:
     lib().orc_set_threads(int(n))
+
+
+def set_activation(oai: int = 0, alpha: float = 1.702, limit: float = 0.0) -> None:
+    """Process-wide gate/up combine, as the reference keeps it (moe.rs:92-103): plain SwiGLU,
+    clamped SwiGLU (oai = 0, limit > 0) or clamped OpenAI-SwiGLU (oai = 1)."""
+    lib().orc_set_activation(int(oai), float(alpha), float(limit))
+
+
+def act_combine(g: float, u: float, oai: int, alpha: float, limit: float) -> float:
+    return float(lib().orc_act_combine(float(g), float(u), int(oai), float(alpha), float(limit)))
 
 
 def hardware_threads() -> int:

@@ -45,7 +45,8 @@ struct DeviceContext {
 std::mutex g_init_mu;
 DeviceContext *g_ctx[COLI_CUDA_MAX_DEVICES];
 int g_ndev = 0;
-int g_act_oai = 0;
+int g_act_oai = 0;  // process-wide gate/up combine, backend_cuda.cu:339-350
+float g_act_alpha = 1.702f;
 float g_act_limit = 0.0f;
 
 DeviceContext *find_ctx(int device) {
@@ -138,10 +139,11 @@ extern "C" int coli_cuda_device_sync(int device) {
   return coli_cuda_check(cudaDeviceSynchronize(), "device sync") ? 1 : 0;
 }
 extern "C" void coli_cuda_set_activation(int oai, float alpha, float limit) {
-  (void)alpha;
   g_act_oai = oai;
+  g_act_alpha = alpha;
   g_act_limit = limit;
 }
+static colib::ActParams current_activation() { return colib::ActParams{g_act_oai, g_act_alpha, g_act_limit}; }
 extern "C" void coli_cuda_stats(int device, size_t *tensor_count, size_t *tensor_bytes) {
   size_t n = 0, b = 0;
   for (int i = 0; i < g_ndev; ++i)
@@ -152,14 +154,6 @@ extern "C" void coli_cuda_stats(int device, size_t *tensor_count, size_t *tensor
   if (tensor_count) *tensor_count = n;
   if (tensor_bytes) *tensor_bytes = b;
 }
-static bool activation_supported() {
-  if (g_act_oai != 0 || g_act_limit > 0.0f) {
-    coli_set_error("only the plain SiLU SwiGLU activation is implemented (oai=%d limit=%g requested)", g_act_oai, g_act_limit);
-    return false;
-  }
-  return true;
-}
-
 // ---- resident weights ----------------------------------------------------------------------------
 static bool fmt_supported(int fmt) { return fmt == COLI_FMT_NVFP4 || fmt == COLI_FMT_FP8_B128 || fmt == COLI_FMT_E4M3_ROW; }
 
@@ -357,6 +351,7 @@ struct ColiMoe {
   __half *xg;   // gathered f16 rows for the tcgen05 path (null when max_tokens never reaches it)
   int *status;        // device status word of the tcgen05 kernels
   unsigned int *ticket;  // device word of the fused decode front end (zero between launches)
+  colib::ActParams act;  // the process-wide activation setting when the handle was created
   int sm_count;
   size_t h_rows_cap;  // rows the h scratch holds
   size_t ws_bytes;
@@ -437,7 +432,6 @@ extern "C" int coli_b200_moe_create(ColiMoe **out, const ColiMoeLayer *L, int ma
     coli_set_error("moe_create: missing router/expert tables or unsupported format %d", L->fmt);
     return 0;
   }
-  if (!activation_supported()) return 0;
   DeviceContext *ctx = find_ctx(L->device);
   if (!select_ctx(ctx)) return 0;
   std::lock_guard<std::mutex> lk(ctx->mu);
@@ -445,6 +439,7 @@ extern "C" int coli_b200_moe_create(ColiMoe **out, const ColiMoeLayer *L, int ma
   m->L = *L;
   m->ctx = ctx;
   m->max_tokens = max_tokens;
+  m->act = current_activation();
   m->ws_bytes = 0;
   m->profiling = false;
   m->phase_calls = 0;
@@ -699,6 +694,7 @@ extern "C" int coli_b200_moe_block_dev(ColiMoe *m, const void *x_dev, void *out_
     tp.h = m->h;
     tp.y = m->y;
     tp.status = m->status;
+    tp.act = m->act;
     if (!colib::launch_gate_up_tc(tp, m->xg, rows, m->sm_count, st)) return 0;
     COLI_MARK(3);
     if (!colib::launch_down_tc(tp, rows, m->sm_count, st)) return 0;
@@ -723,6 +719,7 @@ extern "C" int coli_b200_moe_block_dev(ColiMoe *m, const void *x_dev, void *out_
     fp.h = m->h;
     fp.y = m->y;
     fp.y32 = nullptr;
+    fp.act = m->act;
     if (!colib::launch_gate_up_small(fp, st)) return 0;
     COLI_MARK(3);
     if (!colib::launch_down_small(fp, st)) return 0;
@@ -889,6 +886,7 @@ static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, cons
     tp.h = m->h;
     tp.y = (__nv_bfloat16 *)y_dev;
     tp.status = m->status;
+    tp.act = m->act;
     return colib::launch_gate_up_tc(tp, rows_dev, rows_cap, m->sm_count, st) && colib::launch_down_tc(tp, rows_cap, m->sm_count, st);
   }
   colib::FfnParams fp;
@@ -911,6 +909,7 @@ static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, cons
   fp.h = m->h;
   fp.y = (__nv_bfloat16 *)y_dev;
   fp.y32 = nullptr;
+  fp.act = m->act;
   return colib::launch_ffn_small(fp, st);
 }
 
@@ -1001,7 +1000,6 @@ static int run_host_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *u
     coli_set_error("%s: null pointer or empty group", who);
     return 0;
   }
-  if (!activation_supported()) return 0;
   const int device = gates[0]->device, D = gates[0]->I, I = gates[0]->O, fmt = gates[0]->fmt;
   long total = 0;
   for (int c = 0; c < count; ++c) {
@@ -1070,6 +1068,7 @@ static int run_host_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *u
   fp.h = (__half *)ctx->buf[2];
   fp.y = nullptr;
   fp.y32 = (float *)ctx->buf[0];  // x f32 is dead once converted
+  fp.act = current_activation();
   if (!colib::launch_ffn_small(fp, st)) return 0;
   CK(cudaMemcpyAsync(y, ctx->buf[0], xb * sizeof(float), cudaMemcpyDeviceToHost, st), "expert output download");
   CK(cudaStreamSynchronize(st), "expert call sync");

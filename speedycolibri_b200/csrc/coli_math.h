@@ -108,6 +108,28 @@ CF_HD float coli_sigmoidf(float x) { return CF_DIV(1.0f, CF_ADD(1.0f, coli_expf(
 // x/(1+exp(-x)) — crates/colibri-engine/src/math.rs:129-132.
 CF_HD float coli_siluf(float x) { return CF_DIV(x, CF_ADD(1.0f, coli_expf(-x))); }
 
+// Gate/up combine of one element under the process-wide activation setting
+// (crates/colibri-backend/cuda/backend_cuda.cu:380-392 selects the same three ways):
+//   oai != 0            clamped OpenAI-SwiGLU, crates/colibri-engine/src/math.rs:143-148:
+//                       g = min(gate, limit), u = clamp(up, -limit, limit),
+//                       out = g / (1 + exp(-alpha g)) * (u + 1)
+//   oai == 0, limit > 0 SwiGLU under the asymmetric clamp, crates/colibri-engine/src/dsv4.rs:738-742:
+//                       out = silu(min(gate, limit)) * clamp(up, -limit, limit)
+//   otherwise           plain SwiGLU, silu(gate) * up (moe.rs:1187-1230)
+CF_HD float coli_act_combine(float gate, float up, int oai, float alpha, float limit) {
+  if (oai) {
+    const float g = gate < limit ? gate : limit;
+    const float u = up < -limit ? -limit : (up > limit ? limit : up);
+    return CF_MUL(CF_DIV(g, CF_ADD(1.0f, coli_expf(-CF_MUL(alpha, g)))), CF_ADD(u, 1.0f));
+  }
+  if (limit > 0.0f) {
+    const float g = gate < limit ? gate : limit;
+    const float u = up < -limit ? -limit : (up > limit ? limit : up);
+    return CF_MUL(coli_siluf(g), u);
+  }
+  return CF_MUL(coli_siluf(gate), up);
+}
+
 // bf16 <-> f32 — crates/colibri-core/src/dtype.rs:165-194 (RNE, NaN kept a NaN).
 CF_HD float coli_bf16_to_f32(uint16_t h) { return cf_bits_f32((uint32_t)h << 16); }
 CF_HD uint16_t coli_f32_to_bf16(float v) {

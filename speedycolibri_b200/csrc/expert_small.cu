@@ -312,7 +312,7 @@ __global__ void __launch_bounds__(SPLITK ? 256 : 64, SPLITK                  ? 1
         const size_t row = (size_t)(row0 + col);
         if (GATED) {
           const float gv = v[0][c] * s0, uv = v[MATS - 1][c] * s1;
-          const float hv = gv / (1.0f + __expf(-gv)) * uv;
+          const float hv = coli_act_fast(gv, uv, p.act);
           p.h[row * p.I + orow] = coli_f32_to_f16_via_bf16(hv);
         } else {
           if (p.y32)

@@ -372,7 +372,7 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
           if (col < nrows) {
             const float v0 = __uint_as_float(g[j]) * s0, v1 = __uint_as_float(u[j]) * s1;
             if (GATED) {
-              if (f < Oout) out_h[(size_t)col * Oout] = coli_f32_to_f16_via_bf16(__fdividef(v0, 1.0f + __expf(-v0)) * v1);
+              if (f < Oout) out_h[(size_t)col * Oout] = coli_f32_to_f16_via_bf16(coli_act_fast(v0, v1, p.act));
             } else {
               __nv_bfloat16 *dst = out_y + (size_t)col * Oout;
               if (f < Oout) *dst = __float2bfloat16_rn(v0);

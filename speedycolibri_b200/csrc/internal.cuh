@@ -121,6 +121,12 @@ int launch_items_from_counts(const int32_t *seg_count, int nseg, int rows_per_it
                              int32_t *item_seg, int32_t *item_row0, int32_t *item_nrows, int32_t *n_items,
                              cudaStream_t st);
 
+// Gate/up combine of the expert FFN (coli_math.h: coli_act_combine states the three forms).
+struct ActParams {
+  int oai;
+  float alpha, limit;
+};
+
 // expert_small.cu
 struct FfnParams {
   int fmt, H, I;
@@ -135,6 +141,7 @@ struct FfnParams {
   __half *h;                 // [rows, I] scratch
   __nv_bfloat16 *y;          // [rows, H] out (bf16), or
   float *y32;                // [rows, H] out (f32) when not null
+  ActParams act;
 };
 int launch_gate_up_small(const FfnParams &p, cudaStream_t st);  // h = silu(gate x) * (up x)
 int launch_down_small(const FfnParams &p, cudaStream_t st);     // y = down h
@@ -151,6 +158,7 @@ struct TcParams {
   __half *h;         // [rows, I]
   __nv_bfloat16 *y;  // [rows, H]
   int *status;       // device word: 0, or the code of the first bounded wait that gave up
+  ActParams act;
 };
 // x_rows: f16 [rows_cap, H] expert-contiguous rows (row index = position in the work list)
 int launch_gate_up_tc(const TcParams &p, const void *x_rows, int rows_cap, int sm_count, cudaStream_t st);
@@ -187,6 +195,19 @@ __device__ __forceinline__ uint32_t coli_bf16x2_to_f16x2(uint32_t w) {
 __device__ __forceinline__ uint4 coli_bf16x8_to_f16x8(uint4 v) {
   return make_uint4(coli_bf16x2_to_f16x2(v.x), coli_bf16x2_to_f16x2(v.y), coli_bf16x2_to_f16x2(v.z),
                     coli_bf16x2_to_f16x2(v.w));
+}
+// coli_act_combine with the fast exponential: silu(g) * u, or its clamped / OpenAI forms
+__device__ __forceinline__ float coli_act_fast(float g, float u, const ActParams &a) {
+  if (a.oai) {
+    g = fminf(g, a.limit);
+    u = fminf(fmaxf(u, -a.limit), a.limit);
+    return __fdividef(g, 1.0f + __expf(-a.alpha * g)) * (u + 1.0f);
+  }
+  if (a.limit > 0.0f) {
+    g = fminf(g, a.limit);
+    u = fminf(fmaxf(u, -a.limit), a.limit);
+  }
+  return __fdividef(g, 1.0f + __expf(-g)) * u;
 }
 // f32 -> (rounded to bf16) -> f16 bits, saturating
 __device__ __forceinline__ __half coli_f32_to_f16_via_bf16(float v) {

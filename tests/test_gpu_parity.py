@@ -427,3 +427,29 @@ def test_decode_front_is_one_launch(gpu_backend):
         assert np.array_equal(idx, want_idx)
         assert np.array_equal(w.view(np.uint32), want_w.view(np.uint32))
     blk.close()
+
+
+@pytest.mark.parametrize("act", [(1, 1.702, 0.2), (0, 0.0, 0.15)], ids=["swiglu_oai", "swiglu_clamped"])
+@pytest.mark.parametrize("name,T", [("tiny", 5), ("tiny_fp8", 19), ("mid", 433)])
+def test_block_other_activations(gpu_backend, orc, name, T, act):
+    """The process-wide activation setting (coli_cuda_set_activation): clamped OpenAI-SwiGLU and
+    the asymmetric-clamp SwiGLU, on the decode kernel (tiny*) and the tcgen05 kernel (mid).  The
+    limits are small enough that about half of the gate/up values are clamped."""
+    shape = CONFIGS[name].with_tokens(T)
+    L, packed = host_layer(shape)
+    x = synth.host_tokens(shape, T)
+    plain = L.moe_block(x)["out"]
+    try:
+        orc.set_activation(*act)
+        gpu_backend.set_activation(*act)
+        blk = make_block(shape, upload_layer(shape, packed))  # a handle keeps the setting it was created under
+        out = blk.moe(x)
+        blk.check()
+        want = L.moe_block(x)["out"]
+    finally:
+        orc.set_activation(0, 1.702, 0.0)
+        gpu_backend.set_activation(0, 0.0, 0.0)
+    assert rel_l2(want, plain) > 0.05, "the activation setting must change the result"
+    err = rel_l2(out, want)
+    assert err <= 5e-3, err
+    blk.close()

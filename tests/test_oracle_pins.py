@@ -325,3 +325,28 @@ def test_sharded_oracle_equals_single_node(orc):
     own = np.array([e % 2 for e in range(shape.E)], np.int32)
     sh = L.moe_block(xb, world=2, owner=own)["out_f32"]
     assert np.abs(sh - one).max() <= 1e-5 * max(1.0, np.abs(one).max())
+
+
+def test_swiglu_oai_shape(orc):
+    """crates/colibri-engine/src/math.rs:238-256 (swiglu_oai_shape)."""
+    alpha, limit = 1.702, 7.0
+    f = lambda g, u: orc.act_combine(g, u, 1, alpha, limit)
+    assert abs(f(0.0, 3.0)) < 1e-6
+    g, u = 1.5, 2.0
+    assert abs(f(g, u) - (g / (1.0 + math.exp(-alpha * g))) * (u + 1.0)) < 1e-6
+    clamped = (limit / (1.0 + math.exp(-alpha * limit))) * (limit + 1.0)
+    assert abs(f(100.0, 100.0) - clamped) < 1e-4
+    assert abs(f(2.0, -50.0) - (2.0 / (1.0 + math.exp(-alpha * 2.0))) * (-limit + 1.0)) < 1e-5
+
+
+def test_swiglu_clamp_is_asymmetric_and_is_not_oai(orc):
+    """crates/colibri-engine/src/dsv4.rs:752-764 (clamp_is_asymmetric_and_is_not_oai)."""
+    lim = 10.0
+    f = lambda g, u: orc.act_combine(g, u, 0, 0.0, lim)
+    assert abs(f(-50.0, 1.0)) < 1e-6
+    assert f(50.0, 1.0) == f(lim, 1.0)
+    assert f(1.0, 50.0) == f(1.0, lim)
+    assert f(1.0, -50.0) == f(1.0, -lim)
+    assert abs(f(2.0, 0.0)) < 1e-6
+    # limit = 0 and oai = 0 is the plain SiLU arm
+    assert orc.act_combine(50.0, 50.0, 0, 0.0, 0.0) == orc.lib().orc_siluf(50.0) * 50.0
