@@ -7,6 +7,7 @@
 namespace colib {
 
 __global__ void __launch_bounds__(256) k_combine(CombineParams p, const __nv_bfloat16 *shared_y) {
+  coli_grid_dependency_sync();
   const int t = blockIdx.y;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;  // 8-element column group
   if (c * 8 >= p.H) return;
@@ -75,9 +76,8 @@ int launch_combine(const CombineParams &p, cudaStream_t st) {
   }
   const __nv_bfloat16 *shared_y = p.has_shared ? p.shared_y : nullptr;
   dim3 grid((p.H / 8 + 255) / 256, p.T);
-  k_combine<<<grid, 256, 0, st>>>(p, shared_y);
   coli_count_launch(1);
-  return coli_cuda_check(cudaGetLastError(), "combine launch") ? 1 : 0;
+  return coli_cuda_check(launch_dependent(k_combine, grid, dim3(256), 0, st, p, shared_y), "combine launch") ? 1 : 0;
 }
 
 // out = bf16(partial + shared): the last step of the expert-parallel block

@@ -163,6 +163,7 @@ __global__ void __launch_bounds__(SPLITK ? 256 : 64, SPLITK                  ? 1
   constexpr int R = NB <= 2 ? 4 : 2;
   constexpr int PF = R - 1;
   extern __shared__ __align__(16) float red[];  // [W][MATS*NB*4][32]
+  coli_grid_dependency_sync();
   const int n_items = *p.n_items;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -376,10 +377,10 @@ static int launch_one(const FfnParams &p, bool gated, cudaStream_t st) {
     const int W = pick_w(KT);
     dim3 grid(row_tiles, p.max_items);
     const size_t sm = (size_t)W * (gated ? 2 : 1) * NB * 4 * 32 * sizeof(float);
-    if (gated)
-      k_ffn_mm<FMT, NB, true, true><<<grid, W * 32, sm, st>>>(p);
-    else
-      k_ffn_mm<FMT, NB, false, true><<<grid, W * 32, sm, st>>>(p);
+    const cudaError_t e = gated ? launch_dependent(k_ffn_mm<FMT, NB, true, true>, grid, dim3(W * 32), sm, st, p)
+                                : launch_dependent(k_ffn_mm<FMT, NB, false, true>, grid, dim3(W * 32), sm, st, p);
+    coli_count_launch(1);
+    return coli_cuda_check(e, "expert ffn launch") ? 1 : 0;
   } else {
     // two warps per CTA keep the per-SM share of tasks even; the grid covers what fits at once
     constexpr int W = 2;
@@ -396,13 +397,11 @@ static int launch_one(const FfnParams &p, bool gated, cudaStream_t st) {
     }
     const long max_ctas = ((long)row_tiles * p.max_items + W - 1) / W;
     const int grid = (int)(max_ctas < resident[gated ? 1 : 0] ? max_ctas : resident[gated ? 1 : 0]);
-    if (gated)
-      k_ffn_mm<FMT, NB, true, false><<<grid, W * 32, 0, st>>>(p);
-    else
-      k_ffn_mm<FMT, NB, false, false><<<grid, W * 32, 0, st>>>(p);
+    const cudaError_t e = gated ? launch_dependent(k_ffn_mm<FMT, NB, true, false>, dim3(grid), dim3(W * 32), 0, st, p)
+                                : launch_dependent(k_ffn_mm<FMT, NB, false, false>, dim3(grid), dim3(W * 32), 0, st, p);
+    coli_count_launch(1);
+    return coli_cuda_check(e, "expert ffn launch") ? 1 : 0;
   }
-  coli_count_launch(1);
-  return coli_cuda_check(cudaGetLastError(), "expert ffn launch") ? 1 : 0;
 }
 
 // rows_per_item the caller cut the work list with selects NB (8 * NB >= rows per item).

@@ -185,6 +185,31 @@ int launch_f32_to_f16_via_bf16(const float *src, __half *dst, size_t n, cudaStre
 // (crates/colibri-engine/src/linear.rs:199-220).
 int launch_matmul_f32_seq(const float *x, const float *w, float *y, int S, int I, int O, cudaStream_t st);
 
+// Programmatic dependent launch.  The kernels of the decode step are a few microseconds each, so
+// the launch latency between them is a visible share of the step: launched with this helper, a
+// kernel may be scheduled while its predecessor in the stream is still running; it must then
+// execute coli_grid_dependency_sync() before its first global-memory access, which returns once
+// the predecessor has completed and its writes are visible.  Launched the ordinary way (as the
+// profiled path does, with an event between kernels) the two device calls are no-ops.
+__device__ __forceinline__ void coli_grid_dependency_sync() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // let the successor be scheduled early too
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // bf16 pair (one 32-bit word) -> f16 pair, saturating at the largest finite f16
 __device__ __forceinline__ uint32_t coli_bf16x2_to_f16x2(uint32_t w) {
   const float lo = fminf(fmaxf(__uint_as_float(w << 16), -65504.0f), 65504.0f);

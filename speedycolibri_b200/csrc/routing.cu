@@ -714,6 +714,7 @@ __global__ void __launch_bounds__(256) k_decode_front(RouteParams rp, PermutePar
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ PermuteSmallSmem psm;
   __shared__ int is_last;
+  coli_grid_dependency_sync();
   router_decode_block(rp, smem_raw);
   if (pp.x16) {
     const int n = rp.T * (rp.H / 8);
@@ -759,9 +760,11 @@ int launch_decode_front(const RouteParams &rp, const PermuteParams &pp, unsigned
       return 0;
     attr_set = true;
   }
-  k_decode_front<<<(rp.E + 7) / 8, 256, smem, st>>>(rp, pp, permute_max_items(pp), ticket);
   coli_count_launch(1);
-  return coli_cuda_check(cudaGetLastError(), "decode front launch") ? 1 : 0;
+  return coli_cuda_check(launch_dependent(k_decode_front, dim3((rp.E + 7) / 8), dim3(256), smem, st, rp, pp, permute_max_items(pp), ticket),
+                         "decode front launch")
+             ? 1
+             : 0;
 }
 
 int launch_permute(const PermuteParams &p, cudaStream_t st) {
