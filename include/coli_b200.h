@@ -105,6 +105,17 @@ int coli_cuda_expert_mlp_nvfp4(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCud
 /* backend_cuda.h:104-105 (fmt 4 per-row scaled e4m3; this library also accepts fmt 8). */
 int coli_cuda_expert_mlp_fp8(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down, float *y,
                              const float *x, int S);
+/* backend_cuda.h:107-109 and 136-140: the format-agnostic forms of the calls above.  Accepted
+ * formats are the ones this library keeps resident (4, 5, 8); the reference's f32 / int8 / int2
+ * expert tensors are declined with 0. */
+int coli_cuda_expert_mlp(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down, float *y, const float *x, int S);
+int coli_cuda_expert_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups, ColiCudaTensor *const *downs,
+                           const int *rows, int count, float *y, const float *x);
+/* backend_cuda.h:127-129: y[S,O] = x[S,I] @ W[O,I]^T for an NVFP4 matrix (host f32 in and out,
+ * synchronous).  The first call copies the container into HBM through *tensor, later calls reuse
+ * the handle; x is rounded to bf16 on the device as in the expert calls. */
+int coli_cuda_matmul_nvfp4(ColiCudaTensor **tensor, float *y, const float *x, const void *weights, const void *bscale,
+                           float gscale, int S, int I, int O, int device);
 /* backend_cuda.h:134-140 / backend_cuda.cu:4410-4792: packed group of same-shaped experts; x and
  * y hold sum(rows) consecutive [D] HOST f32 rows in call order. */
 int coli_cuda_expert_group_nvfp4(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,

@@ -222,3 +222,46 @@ class F32Matmul:
         if self.slot.value:
             _lib_().coli_cuda_tensor_free(self.slot)
             self.slot = C.c_void_p()
+
+
+def expert_mlp(gate: CudaTensor, up: CudaTensor, down: CudaTensor, x: np.ndarray) -> np.ndarray:
+    """coli_cuda_expert_mlp (backend_cuda.h:107-109): any resident expert format."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    y = np.empty_like(x)
+    _check(_lib_().coli_cuda_expert_mlp(gate.handle, up.handle, down.handle, _np_ptr(y), _np_ptr(x), x.shape[0]),
+           "coli_cuda_expert_mlp")
+    return y
+
+
+def expert_group(gates, ups, downs, rows, x: np.ndarray) -> np.ndarray:
+    """coli_cuda_expert_group (backend_cuda.h:136-140): x holds sum(rows) rows in expert order."""
+    n = len(rows)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    y = np.empty_like(x)
+    mk = lambda ts: (C.c_void_p * n)(*[t.handle for t in ts])
+    r = (C.c_int * n)(*[int(v) for v in rows])
+    _check(_lib_().coli_cuda_expert_group(mk(gates), mk(ups), mk(downs), r, n, _np_ptr(y), _np_ptr(x)), "coli_cuda_expert_group")
+    return y
+
+
+class Nvfp4Matmul:
+    """coli_cuda_matmul_nvfp4 (backend_cuda.h:127-129): y = x @ W^T for one NVFP4 matrix given as the
+    container's host arrays; the slot keeps the HBM copy between calls."""
+
+    def __init__(self, nibbles: np.ndarray, bscale: np.ndarray, gscale: float, O: int, I: int, device: int = 0):
+        self.nib = np.ascontiguousarray(nibbles, dtype=np.uint8)
+        self.bs = np.ascontiguousarray(bscale, dtype=np.uint8)
+        self.g, self.O, self.I, self.device = float(gscale), O, I, device
+        self.slot = C.c_void_p()
+
+    def __call__(self, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        y = np.empty((x.shape[0], self.O), np.float32)
+        _check(_lib_().coli_cuda_matmul_nvfp4(C.byref(self.slot), _np_ptr(y), _np_ptr(x), _np_ptr(self.nib), _np_ptr(self.bs),
+                                              self.g, x.shape[0], self.I, self.O, self.device), "coli_cuda_matmul_nvfp4")
+        return y
+
+    def free(self):
+        if self.slot.value:
+            _lib_().coli_cuda_tensor_free(self.slot)
+            self.slot = C.c_void_p()

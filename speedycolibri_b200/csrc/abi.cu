@@ -1089,6 +1089,103 @@ extern "C" int coli_cuda_expert_mlp_fp8(ColiCudaTensor *gate, ColiCudaTensor *up
   return run_host_group(&gate, &up, &down, &S, 1, y, x, COLI_FMT_E4M3_ROW, COLI_FMT_FP8_B128, "expert_mlp_fp8");
 }
 
+// The format-agnostic forms of the two calls above (backend_cuda.h:107-109, 136-140): any resident
+// expert format this library holds (NVFP4, e4m3 per row, e4m3 128x128); the reference's int8 /
+// int2 / f32 experts are not resident formats here and are declined.
+extern "C" int coli_cuda_expert_mlp(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down, float *y, const float *x,
+                                    int S) {
+  const int fmt = gate ? gate->fmt : -1;
+  if (!fmt_supported(fmt)) {
+    coli_set_error("expert_mlp: format %d is not a resident expert format of this library", fmt);
+    return 0;
+  }
+  return run_host_group(&gate, &up, &down, &S, 1, y, x, fmt, fmt, "expert_mlp");
+}
+extern "C" int coli_cuda_expert_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups, ColiCudaTensor *const *downs,
+                                      const int *rows, int count, float *y, const float *x) {
+  const int fmt = (gates && count > 0 && gates[0]) ? gates[0]->fmt : -1;
+  if (!fmt_supported(fmt)) {
+    coli_set_error("expert_group: format %d is not a resident expert format of this library", fmt);
+    return 0;
+  }
+  return run_host_group(gates, ups, downs, rows, count, y, x, fmt, fmt, "expert_group");
+}
+
+// y[S,O] = x[S,I] @ W[O,I]^T for one resident quantised matrix: the down-projection kernel with
+// the whole input as a single segment.
+static int run_host_matmul(ColiCudaTensor *w, float *y, const float *x, int S, const char *who) {
+  if (!w || !x || !y || S < 1 || !fmt_supported(w->fmt)) {
+    coli_set_error("%s: null pointer, empty input or a format that is not resident here", who);
+    return 0;
+  }
+  if (w->I % 8) {
+    coli_set_error("%s: I=%d must be a multiple of 8", who, w->I);
+    return 0;
+  }
+  DeviceContext *ctx = find_ctx(w->device);
+  if (!select_ctx(ctx)) return 0;
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  cudaStream_t st = ctx->stream;
+  const int I = w->I, O = w->O;
+  const int rpi = S <= 8 ? 8 : S <= 16 ? 16 : 32;
+  const int max_items = max_work_items(S, 1, rpi);
+  const size_t xb = (size_t)S * I, yb = (size_t)S * O;
+  // slots: 0 x f32, 1 x f16, 2 y f32, 3 table + count + work list
+  const size_t tbl_bytes = sizeof(WeightRef) + sizeof(int32_t) * (1 + 2 + 3 * (size_t)max_items + 1);
+  if (!reserve(ctx, 0, xb * sizeof(float)) || !reserve(ctx, 1, xb * sizeof(__half)) || !reserve(ctx, 2, yb * sizeof(float)) ||
+      !reserve(ctx, 3, tbl_bytes))
+    return 0;
+  const WeightRef ref{w->q, w->s, w->gscale, 0};
+  WeightRef *d_tbl = (WeightRef *)ctx->buf[3];
+  int32_t *d_cnt = (int32_t *)(d_tbl + 1);
+  int32_t *d_off = d_cnt + 1;
+  int32_t *d_iseg = d_off + 2;
+  int32_t *d_irow = d_iseg + max_items;
+  int32_t *d_inr = d_irow + max_items;
+  int32_t *d_nit = d_inr + max_items;
+  CK(cudaMemcpyAsync(ctx->buf[0], x, xb * sizeof(float), cudaMemcpyHostToDevice, st), "matmul input upload");
+  CK(cudaMemcpyAsync(d_tbl, &ref, sizeof(WeightRef), cudaMemcpyHostToDevice, st), "matmul table upload");
+  CK(cudaMemcpyAsync(d_cnt, &S, sizeof(int32_t), cudaMemcpyHostToDevice, st), "matmul row count upload");
+  CK(cudaStreamSynchronize(st), "matmul upload sync");  // ref and S are locals
+  if (!colib::launch_f32_to_f16_via_bf16((const float *)ctx->buf[0], (__half *)ctx->buf[1], xb, st)) return 0;
+  if (!colib::launch_items_from_counts(d_cnt, 1, rpi, d_off, d_iseg, d_irow, d_inr, d_nit, st)) return 0;
+  colib::FfnParams fp;
+  fp.fmt = w->fmt;
+  fp.H = O;  // the kernel's "down" form contracts over its I and writes H features per row
+  fp.I = I;
+  fp.gate = fp.up = fp.down = d_tbl;
+  fp.seg_expert = nullptr;
+  fp.item_seg = d_iseg;
+  fp.item_row0 = d_irow;
+  fp.item_nrows = d_inr;
+  fp.n_items = d_nit;
+  fp.max_items = max_items;
+  fp.rows_per_item = rpi;
+  fp.items_expected = max_items;
+  fp.x = nullptr;
+  fp.row_token = nullptr;
+  fp.h = (__half *)ctx->buf[1];
+  fp.y = nullptr;
+  fp.y32 = (float *)ctx->buf[2];
+  fp.act = current_activation();
+  if (!colib::launch_down_small(fp, st)) return 0;
+  CK(cudaMemcpyAsync(y, ctx->buf[2], yb * sizeof(float), cudaMemcpyDeviceToHost, st), "matmul output download");
+  CK(cudaStreamSynchronize(st), "matmul sync");
+  return 1;
+}
+
+// backend_cuda.h:127-129 (backend_cuda.cu:3102-3128): the first call copies the weight into HBM
+// through *tensor, later calls reuse it.
+extern "C" int coli_cuda_matmul_nvfp4(ColiCudaTensor **tensor, float *y, const float *x, const void *weights, const void *bscale,
+                                      float gscale, int S, int I, int O, int device) {
+  if (!tensor) {
+    coli_set_error("coli_cuda_matmul_nvfp4: null tensor slot");
+    return 0;
+  }
+  if (!coli_cuda_tensor_wrap_nvfp4(tensor, weights, bscale, gscale, I, O, device)) return 0;
+  return run_host_matmul(*tensor, y, x, S, "coli_cuda_matmul_nvfp4");
+}
+
 // Router GEMM through the generic matmul entry (fmt 0 only): gpu.rs:2219-2249 -> backend_cuda.cu:3063-3075.
 extern "C" int coli_cuda_matmul(ColiCudaTensor **tensor, float *y, const float *x, const void *weights,
                                 const float *scales, int fmt, int S, int I, int O, int device) {

@@ -453,3 +453,46 @@ def test_block_other_activations(gpu_backend, orc, name, T, act):
     err = rel_l2(out, want)
     assert err <= 5e-3, err
     blk.close()
+
+
+def test_generic_expert_calls_and_nvfp4_matmul(gpu_backend, orc):
+    """coli_cuda_expert_mlp / coli_cuda_expert_group (format taken from the handles) and
+    coli_cuda_matmul_nvfp4 (one matrix, slot reused between calls)."""
+    shape = CONFIGS["tiny_sig"]
+    L, packed = host_layer(shape)
+    layer = upload_layer(shape, packed)
+    rng = np.random.default_rng(5)
+    rows = [2, 7]
+    x = synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(rng.standard_normal((sum(rows), shape.H)).astype(np.float32)))
+    e = layer.experts[1]
+    y = gpu_backend.expert_mlp(e.gate, e.up, e.down, x[:4])
+    want = L.expert_ffn(1, x[:4])
+    assert np.abs(y - want).max() <= 1e-2 * np.abs(want).max()
+    es = [layer.experts[i] for i in (4, 1)]
+    y = gpu_backend.expert_group([t.gate for t in es], [t.up for t in es], [t.down for t in es], rows, x)
+    off = 0
+    for ei, r in zip((4, 1), rows):
+        want = L.expert_ffn(ei, x[off:off + r])
+        assert np.abs(y[off:off + r] - want).max() <= 1e-2 * np.abs(want).max()
+        off += r
+    # a single NVFP4 matrix, ragged K and O, every row-count arm of the kernel
+    O, I = 72, 200
+    w = (rng.standard_normal((O, I)) * 0.05).astype(np.float32)
+    nib, bs, g = orc.quantize_nvfp4(w)
+    mm = gpu_backend.Nvfp4Matmul(nib, bs, g, O, I)
+    for S in (1, 8, 9, 33, 70):
+        xs = synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(rng.standard_normal((S, I)).astype(np.float32)))
+        got = mm(xs)
+        want = orc.matmul_qt(FMT_NVFP4, nib, bs, g, xs, O)
+        assert np.abs(got - want).max() <= 2e-3 * np.abs(want).max(), S
+    mm.free()
+    from speedycolibri_b200.backend import CudaError, F32Matmul
+    f32 = F32Matmul(rng.standard_normal((8, 16)).astype(np.float32))
+    f32(np.zeros((1, 16), np.float32))
+    with pytest.raises(CudaError):  # an f32 tensor is not a resident expert format: declined, not computed
+        import ctypes as C
+        from speedycolibri_b200 import _lib
+        from speedycolibri_b200.backend import _check
+        yb = np.zeros((1, 16), np.float32)
+        _check(_lib.load().coli_cuda_expert_mlp(f32.slot, f32.slot, f32.slot, yb.ctypes.data, yb.ctypes.data, 1), "coli_cuda_expert_mlp")
+    f32.free()
