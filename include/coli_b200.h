@@ -116,6 +116,16 @@ int coli_cuda_expert_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *
  * the handle; x is rounded to bf16 on the device as in the expert calls. */
 int coli_cuda_matmul_nvfp4(ColiCudaTensor **tensor, float *y, const float *x, const void *weights, const void *bscale,
                            float gscale, int S, int I, int O, int device);
+/* backend_cuda.h:131-132, 152-160: gateless ReLU^2 NVFP4 experts, y = down(relu(up x)^2)
+ * (moe.rs:1189-1199).  x, y: host f32, sum(rows) consecutive rows of up->I values in call order.
+ * The three forms differ only in how the reference batches its launches; here all run the whole
+ * group in two launches.  `exact` is accepted and has no effect: a row's result never depends on
+ * the other rows of a call. */
+int coli_cuda_expert_mlp_nvfp4_relu2(ColiCudaTensor *up, ColiCudaTensor *down, float *y, const float *x, int S, int exact);
+int coli_cuda_expert_group_nvfp4_relu2(ColiCudaTensor *const *ups, ColiCudaTensor *const *downs, const int *rows, int count,
+                                       float *y, const float *x);
+int coli_cuda_expert_seg_nvfp4_relu2(ColiCudaTensor *const *ups, ColiCudaTensor *const *downs, const int *rows, int count,
+                                     float *y, const float *x);
 /* backend_cuda.h:134-140 / backend_cuda.cu:4410-4792: packed group of same-shaped experts; x and
  * y hold sum(rows) consecutive [D] HOST f32 rows in call order. */
 int coli_cuda_expert_group_nvfp4(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,

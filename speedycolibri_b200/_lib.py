@@ -87,6 +87,9 @@ SIGNATURES = {
     "coli_cuda_expert_mlp": (_i, [_P, _P, _P, _P, _P, _i]),
     "coli_cuda_expert_group": (_i, [_PP, _PP, _PP, C.POINTER(_i), _i, _P, _P]),
     "coli_cuda_matmul_nvfp4": (_i, [_PP, _P, _P, _P, _P, _f, _i, _i, _i, _i]),
+    "coli_cuda_expert_mlp_nvfp4_relu2": (_i, [_P, _P, _P, _P, _i, _i]),
+    "coli_cuda_expert_group_nvfp4_relu2": (_i, [_PP, _PP, C.POINTER(_i), _i, _P, _P]),
+    "coli_cuda_expert_seg_nvfp4_relu2": (_i, [_PP, _PP, C.POINTER(_i), _i, _P, _P]),
     "coli_b200_moe_create": (_i, [_PP, C.POINTER(ColiMoeLayer), _i]),
     "coli_b200_moe_destroy": (None, [_P]),
     "coli_b200_moe_workspace_bytes": (_sz, [_P]),

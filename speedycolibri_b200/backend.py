@@ -265,3 +265,25 @@ class Nvfp4Matmul:
         if self.slot.value:
             _lib_().coli_cuda_tensor_free(self.slot)
             self.slot = C.c_void_p()
+
+
+def expert_group_relu2(ups, downs, rows, x: np.ndarray, seg: bool = False) -> np.ndarray:
+    """coli_cuda_expert_group_nvfp4_relu2 / coli_cuda_expert_seg_nvfp4_relu2 (backend_cuda.h:152-160):
+    gateless experts, y = down(relu(up x)^2); x holds sum(rows) rows in expert order."""
+    n = len(rows)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    y = np.empty_like(x)
+    mk = lambda ts: (C.c_void_p * n)(*[t.handle for t in ts])
+    r = (C.c_int * n)(*[int(v) for v in rows])
+    fn = _lib_().coli_cuda_expert_seg_nvfp4_relu2 if seg else _lib_().coli_cuda_expert_group_nvfp4_relu2
+    _check(fn(mk(ups), mk(downs), r, n, _np_ptr(y), _np_ptr(x)), "coli_cuda_expert_group_nvfp4_relu2")
+    return y
+
+
+def expert_mlp_relu2(up: CudaTensor, down: CudaTensor, x: np.ndarray, exact: bool = False) -> np.ndarray:
+    """coli_cuda_expert_mlp_nvfp4_relu2 (backend_cuda.h:131-132)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    y = np.empty_like(x)
+    _check(_lib_().coli_cuda_expert_mlp_nvfp4_relu2(up.handle, down.handle, _np_ptr(y), _np_ptr(x), x.shape[0], int(exact)),
+           "coli_cuda_expert_mlp_nvfp4_relu2")
+    return y

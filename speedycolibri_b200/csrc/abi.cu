@@ -719,6 +719,7 @@ extern "C" int coli_b200_moe_block_dev(ColiMoe *m, const void *x_dev, void *out_
     fp.h = m->h;
     fp.y = m->y;
     fp.y32 = nullptr;
+    fp.relu2_out = nullptr;
     fp.act = m->act;
     if (!colib::launch_gate_up_small(fp, st)) return 0;
     COLI_MARK(3);
@@ -909,6 +910,7 @@ static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, cons
   fp.h = m->h;
   fp.y = (__nv_bfloat16 *)y_dev;
   fp.y32 = nullptr;
+  fp.relu2_out = nullptr;
   fp.act = m->act;
   return colib::launch_ffn_small(fp, st);
 }
@@ -1068,6 +1070,7 @@ static int run_host_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *u
   fp.h = (__half *)ctx->buf[2];
   fp.y = nullptr;
   fp.y32 = (float *)ctx->buf[0];  // x f32 is dead once converted
+  fp.relu2_out = nullptr;
   fp.act = current_activation();
   if (!colib::launch_ffn_small(fp, st)) return 0;
   CK(cudaMemcpyAsync(y, ctx->buf[0], xb * sizeof(float), cudaMemcpyDeviceToHost, st), "expert output download");
@@ -1087,6 +1090,113 @@ extern "C" int coli_cuda_expert_mlp_nvfp4(ColiCudaTensor *gate, ColiCudaTensor *
 extern "C" int coli_cuda_expert_mlp_fp8(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down, float *y,
                                         const float *x, int S) {
   return run_host_group(&gate, &up, &down, &S, 1, y, x, COLI_FMT_E4M3_ROW, COLI_FMT_FP8_B128, "expert_mlp_fp8");
+}
+
+// Gateless ReLU^2 experts (Nemotron-H): y = down(relu(up x)^2), moe.rs:1189-1199;
+// backend_cuda.h:131-160.  Two launches for the whole group: the up projection with the
+// activation in its epilogue, then the down projection.  x, y hold sum(rows) rows of up->I
+// values in call order.
+static int run_host_group_relu2(ColiCudaTensor *const *ups, ColiCudaTensor *const *downs, const int *rows, int count,
+                                float *y, const float *x, const char *who) {
+  if (!ups || !downs || !rows || !x || !y || count < 1 || !ups[0]) {
+    coli_set_error("%s: null pointer or empty group", who);
+    return 0;
+  }
+  const int device = ups[0]->device, D = ups[0]->I, I = ups[0]->O;
+  long total = 0;
+  for (int c = 0; c < count; ++c) {
+    ColiCudaTensor *u = ups[c], *d = downs[c];
+    if (!u || !d || rows[c] < 1 || u->fmt != COLI_FMT_NVFP4 || d->fmt != COLI_FMT_NVFP4 || u->device != device ||
+        d->device != device || u->I != D || u->O != I || d->I != I || d->O != D) {
+      coli_set_error("%s: expert %d has a mismatched format, shape or device", who, c);
+      return 0;
+    }
+    total += rows[c];
+  }
+  if (D % 8 || I % 8) {
+    coli_set_error("%s: D=%d and I=%d must be multiples of 8", who, D, I);
+    return 0;
+  }
+  DeviceContext *ctx = find_ctx(device);
+  if (!select_ctx(ctx)) return 0;
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  cudaStream_t st = ctx->stream;
+  const int avg = (int)((total + count - 1) / count);
+  const int rpi = avg <= 8 ? 8 : avg <= 16 ? 16 : 32;
+  const int max_items = max_work_items((int)total, count, rpi);
+  const size_t xb = (size_t)total * D;
+  // slots: 0 x f32 / y f32, 1 x f16, 2 h f16, 3 tables + counts + work list
+  const size_t tbl_bytes = sizeof(WeightRef) * 2 * count + sizeof(int32_t) * (2 * count + 2 + 3 * (size_t)max_items + 1);
+  if (!reserve(ctx, 0, xb * sizeof(float)) || !reserve(ctx, 1, xb * sizeof(__half)) ||
+      !reserve(ctx, 2, (size_t)total * I * sizeof(__half)) || !reserve(ctx, 3, tbl_bytes))
+    return 0;
+  std::vector<WeightRef> tbl(2 * (size_t)count);
+  for (int c = 0; c < count; ++c) {
+    tbl[c] = WeightRef{ups[c]->q, ups[c]->s, ups[c]->gscale, 0};
+    tbl[count + c] = WeightRef{downs[c]->q, downs[c]->s, downs[c]->gscale, 0};
+  }
+  WeightRef *d_tbl = (WeightRef *)ctx->buf[3];
+  int32_t *d_cnt = (int32_t *)(d_tbl + 2 * (size_t)count);
+  int32_t *d_off = d_cnt + count;
+  int32_t *d_iseg = d_off + count + 1;
+  int32_t *d_irow = d_iseg + max_items;
+  int32_t *d_inr = d_irow + max_items;
+  int32_t *d_nit = d_inr + max_items;
+  CK(cudaMemcpyAsync(ctx->buf[0], x, xb * sizeof(float), cudaMemcpyHostToDevice, st), "expert input upload");
+  CK(cudaMemcpyAsync(d_tbl, tbl.data(), sizeof(WeightRef) * tbl.size(), cudaMemcpyHostToDevice, st), "expert table upload");
+  CK(cudaMemcpyAsync(d_cnt, rows, sizeof(int32_t) * count, cudaMemcpyHostToDevice, st), "row count upload");
+  CK(cudaStreamSynchronize(st), "expert upload sync");  // tbl is a local; rows/x belong to the caller
+  if (!colib::launch_f32_to_f16_via_bf16((const float *)ctx->buf[0], (__half *)ctx->buf[1], xb, st)) return 0;
+  if (!colib::launch_items_from_counts(d_cnt, count, rpi, d_off, d_iseg, d_irow, d_inr, d_nit, st)) return 0;
+  colib::FfnParams fp;
+  fp.fmt = COLI_FMT_NVFP4;
+  fp.seg_expert = nullptr;
+  fp.item_seg = d_iseg;
+  fp.item_row0 = d_irow;
+  fp.item_nrows = d_inr;
+  fp.n_items = d_nit;
+  fp.max_items = max_items;
+  fp.rows_per_item = rpi;
+  fp.items_expected = max_items;
+  fp.x = nullptr;
+  fp.row_token = nullptr;
+  fp.y = nullptr;
+  fp.act = current_activation();
+  // up: rows [total, D] -> relu^2 -> h [total, I]   (the kernel's "down" form: contracts its I, writes its H)
+  fp.H = I;
+  fp.I = D;
+  fp.gate = fp.up = fp.down = d_tbl;
+  fp.h = (__half *)ctx->buf[1];
+  fp.y32 = nullptr;
+  fp.relu2_out = (__half *)ctx->buf[2];
+  if (!colib::launch_down_small(fp, st)) return 0;
+  // down: h [total, I] -> y [total, D]
+  fp.H = D;
+  fp.I = I;
+  fp.gate = fp.up = fp.down = d_tbl + count;
+  fp.h = (__half *)ctx->buf[2];
+  fp.y32 = (float *)ctx->buf[0];  // x f32 is dead once converted
+  fp.relu2_out = nullptr;
+  if (!colib::launch_down_small(fp, st)) return 0;
+  CK(cudaMemcpyAsync(y, ctx->buf[0], xb * sizeof(float), cudaMemcpyDeviceToHost, st), "expert output download");
+  CK(cudaStreamSynchronize(st), "expert call sync");
+  return 1;
+}
+// `exact` asks the reference for per-row kernels so that results do not depend on S
+// (gpu.rs:122-146); here a row's result never depends on the other rows of the call, so the flag
+// changes nothing.
+extern "C" int coli_cuda_expert_mlp_nvfp4_relu2(ColiCudaTensor *up, ColiCudaTensor *down, float *y, const float *x, int S,
+                                                int exact) {
+  (void)exact;
+  return run_host_group_relu2(&up, &down, &S, 1, y, x, "expert_mlp_nvfp4_relu2");
+}
+extern "C" int coli_cuda_expert_group_nvfp4_relu2(ColiCudaTensor *const *ups, ColiCudaTensor *const *downs, const int *rows,
+                                                  int count, float *y, const float *x) {
+  return run_host_group_relu2(ups, downs, rows, count, y, x, "expert_group_nvfp4_relu2");
+}
+extern "C" int coli_cuda_expert_seg_nvfp4_relu2(ColiCudaTensor *const *ups, ColiCudaTensor *const *downs, const int *rows,
+                                                int count, float *y, const float *x) {
+  return run_host_group_relu2(ups, downs, rows, count, y, x, "expert_seg_nvfp4_relu2");
 }
 
 // The format-agnostic forms of the two calls above (backend_cuda.h:107-109, 136-140): any resident
@@ -1167,6 +1277,7 @@ static int run_host_matmul(ColiCudaTensor *w, float *y, const float *x, int S, c
   fp.h = (__half *)ctx->buf[1];
   fp.y = nullptr;
   fp.y32 = (float *)ctx->buf[2];
+  fp.relu2_out = nullptr;
   fp.act = current_activation();
   if (!colib::launch_down_small(fp, st)) return 0;
   CK(cudaMemcpyAsync(y, ctx->buf[2], yb * sizeof(float), cudaMemcpyDeviceToHost, st), "matmul output download");

@@ -316,10 +316,14 @@ __global__ void __launch_bounds__(SPLITK ? 256 : 64, SPLITK                  ? 1
           const float hv = coli_act_fast(gv, uv, p.act);
           p.h[row * p.I + orow] = coli_f32_to_f16_via_bf16(hv);
         } else {
-          if (p.y32)
+          if (p.relu2_out) {
+            const float r = fmaxf(v[0][c] * s0, 0.0f);
+            p.relu2_out[row * p.H + orow] = coli_f32_to_f16_via_bf16(r * r);
+          } else if (p.y32) {
             p.y32[row * p.H + orow] = v[0][c] * s0;
-          else
+          } else {
             p.y[row * p.H + orow] = __float2bfloat16_rn(v[0][c] * s0);
+          }
         }
       }
     };

@@ -141,6 +141,8 @@ struct FfnParams {
   __half *h;                 // [rows, I] scratch
   __nv_bfloat16 *y;          // [rows, H] out (bf16), or
   float *y32;                // [rows, H] out (f32) when not null
+  __half *relu2_out;         // down form only, when not null: write relu(v)^2 (rounded to bf16, held in
+                             // f16) here instead of y -- the first half of a gateless ReLU^2 expert
   ActParams act;
 };
 int launch_gate_up_small(const FfnParams &p, cudaStream_t st);  // h = silu(gate x) * (up x)

@@ -496,3 +496,38 @@ def test_generic_expert_calls_and_nvfp4_matmul(gpu_backend, orc):
         yb = np.zeros((1, 16), np.float32)
         _check(_lib.load().coli_cuda_expert_mlp(f32.slot, f32.slot, f32.slot, yb.ctypes.data, yb.ctypes.data, 1), "coli_cuda_expert_mlp")
     f32.free()
+
+
+def test_gateless_relu2_experts(gpu_backend, orc):
+    """Gateless ReLU^2 experts, y = down(relu(up x)^2): moe.rs:1189-1199 restated with the oracle's
+    matmul (the reference's own check is moe.rs:3386-3455: same composition, same tolerance class)."""
+    shape = CONFIGS["tiny_sig"]
+    L, packed = host_layer(shape)
+    layer = upload_layer(shape, packed)
+    rng = np.random.default_rng(17)
+
+    def want_ffn(ei, x):
+        _gate, up, down = packed["experts"][ei]  # each (codes, scales, tensor scale)
+        u = orc.matmul_qt(FMT_NVFP4, up[0], up[1], up[2], x, shape.I)
+        r = np.maximum(u, np.float32(0.0))
+        return orc.matmul_qt(FMT_NVFP4, down[0], down[1], down[2], (r * r).astype(np.float32), shape.H)
+
+    for S in (1, 9, 40):
+        x = synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(rng.standard_normal((S, shape.H)).astype(np.float32)))
+        e = layer.experts[2]
+        want = want_ffn(2, x)
+        assert np.abs(want).max() > 0
+        for exact in (False, True):
+            y = gpu_backend.expert_mlp_relu2(e.up, e.down, x, exact)
+            assert np.abs(y - want).max() <= 1e-2 * np.abs(want).max()
+    rows = [5, 1, 12]
+    ids = (6, 0, 3)
+    x = synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(rng.standard_normal((sum(rows), shape.H)).astype(np.float32)))
+    es = [layer.experts[i] for i in ids]
+    for seg in (False, True):
+        y = gpu_backend.expert_group_relu2([t.up for t in es], [t.down for t in es], rows, x, seg=seg)
+        off = 0
+        for ei, r in zip(ids, rows):
+            want = want_ffn(ei, x[off:off + r])
+            assert np.abs(y[off:off + r] - want).max() <= 1e-2 * np.abs(want).max()
+            off += r
