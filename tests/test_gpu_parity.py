@@ -531,3 +531,28 @@ def test_gateless_relu2_experts(gpu_backend, orc):
             want = want_ffn(ei, x[off:off + r])
             assert np.abs(y[off:off + r] - want).max() <= 1e-2 * np.abs(want).max()
             off += r
+
+
+def test_layer_loaded_from_container(gpu_backend, orc, tmp_path):
+    """Experts written in the reference's container form (nibbles ++ scales blob + .g sidecar),
+    loaded into HBM by name, give the same block output as the oracle on the same weights."""
+    from speedycolibri_b200 import container
+    from speedycolibri_b200.moe import Layer
+
+    shape = CONFIGS["tiny"]
+    L, packed = host_layer(shape)
+    tensors = {}
+    for e, p in enumerate(packed["experts"]):
+        tensors.update(container.expert_tensors(2, e, p))
+    tensors.update(container.expert_tensors(2, "shared", packed["shared"]))
+    container.write_safetensors(str(tmp_path / "layer.safetensors"), tensors)
+    experts, shared, _fmt = container.load_layer(container.Shards(str(tmp_path)), 2, shape.H, shape.I, shape.E, shared_id="shared")
+    layer = Layer(router=packed["router"], experts=experts, router_bias=packed["select_bias"], logit_bias=packed["logit_bias"],
+                  shared=shared)
+    blk = make_block(shape, layer)
+    x = synth.host_tokens(shape, shape.T)
+    out, idx, w = blk.moe(x, want_routing=True)
+    want = L.moe_block(x)
+    assert np.array_equal(idx, want["idx"]) and np.array_equal(w.view(np.uint32), want["w"].view(np.uint32))
+    assert rel_l2(out, want["out"]) <= 5e-3
+    blk.close()
