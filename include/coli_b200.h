@@ -179,6 +179,12 @@ int coli_b200_moe_block(ColiMoe *moe, const void *x, void *out, int T, int32_t *
  * stream, coli_b200_moe_stream() gives the handle's own).  One handle's workspace serves one
  * call at a time: calls on different streams must not overlap. */
 int coli_b200_moe_block_dev(ColiMoe *moe, const void *x_dev, void *out_dev, int T, void *stream);
+/* The layer step around the block (forward.rs:376-393), all on device pointers and asynchronous
+ * on `stream`: x = bf16(rmsnorm(resid, post_ln_w, eps)) (math.rs:8-20, mean square in f64), then
+ * resid += moe_block(x), the add fused into the combine so the block output is not rounded first.
+ * resid_dev: f32 [T,H], updated in place; post_ln_w_dev: f32 [H].  H must be a multiple of 8.
+ * No reference C symbol corresponds to it: the reference runs these steps on the host. */
+int coli_b200_moe_layer_step_dev(ColiMoe *moe, float *resid_dev, const float *post_ln_w_dev, float eps, int T, void *stream);
 /* Synchronise the device and return 1 if every kernel launched through this handle since the
  * last check ran to completion, 0 (with an error text) if one abandoned a bounded device-side
  * wait.  The host-pointer call above performs this check itself. */

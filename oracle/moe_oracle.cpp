@@ -201,6 +201,15 @@ void orc_matmul_qt(int fmt, const uint8_t *q, const void *s, float g, const floa
   });
 }
 
+// RMSNorm of one row: mean square accumulated left to right in f64, the scale and the products in
+// f32, (x * r) * w (math.rs:8-20).
+void orc_rmsnorm(float *out, const float *x, const float *w, int d, float eps) {
+  double ms = 0.0;
+  for (int k = 0; k < d; ++k) ms += (double)x[k] * (double)x[k];
+  const float r = 1.0f / sqrtf((float)(ms / (double)d) + eps);
+  for (int k = 0; k < d; ++k) out[k] = x[k] * r * w[k];
+}
+
 // Process-wide activation setting, as the reference keeps it (gpu::set_activation, moe.rs:103).
 static int g_orc_oai = 0;
 static float g_orc_alpha = 1.702f, g_orc_limit = 0.0f;

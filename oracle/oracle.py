@@ -56,6 +56,7 @@ def lib() -> C.CDLL:
         L.orc_expf.restype, L.orc_expf.argtypes = f, [f]
         L.orc_sigmoidf.restype, L.orc_sigmoidf.argtypes = f, [f]
         L.orc_siluf.restype, L.orc_siluf.argtypes = f, [f]
+        L.orc_rmsnorm.restype, L.orc_rmsnorm.argtypes = None, [P, P, P, i, f]
         L.orc_set_activation.restype, L.orc_set_activation.argtypes = None, [i, f, f]
         L.orc_act_combine.restype, L.orc_act_combine.argtypes = f, [f, f, i, f, f]
         L.orc_expf_array.restype, L.orc_expf_array.argtypes = None, [P, P, C.c_int64]
@@ -91,6 +92,16 @@ def set_activation(oai: int = 0, alpha: float = 1.702, limit: float = 0.0) -> No
 
 def act_combine(g: float, u: float, oai: int, alpha: float, limit: float) -> float:
     return float(lib().orc_act_combine(float(g), float(u), int(oai), float(alpha), float(limit)))
+
+
+def rmsnorm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
+    """Row-wise RMSNorm, math.rs:8-20."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    out = np.empty_like(x)
+    for r in range(x.shape[0]):
+        lib().orc_rmsnorm(out[r].ctypes.data, x[r].ctypes.data, w.ctypes.data, x.shape[1], float(eps))
+    return out
 
 
 def hardware_threads() -> int:

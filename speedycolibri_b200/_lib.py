@@ -95,6 +95,7 @@ SIGNATURES = {
     "coli_b200_moe_workspace_bytes": (_sz, [_P]),
     "coli_b200_moe_block": (_i, [_P, _P, _P, _i, _P, _P]),
     "coli_b200_moe_block_dev": (_i, [_P, _P, _P, _i, _P]),
+    "coli_b200_moe_layer_step_dev": (_i, [_P, _P, _P, _f, _i, _P]),
     "coli_b200_moe_check": (_i, [_P]),
     "coli_b200_moe_last_routing": (_i, [_P, _i, _P, _P]),
     "coli_b200_moe_local_experts": (_i, [_P]),

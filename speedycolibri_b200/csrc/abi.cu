@@ -642,9 +642,11 @@ static colib::PermuteParams permute_params(ColiMoe *m, const void *x_dev, int T,
   return pp;
 }
 
-extern "C" int coli_b200_moe_block_dev(ColiMoe *m, const void *x_dev, void *out_dev, int T, void *stream) {
+// The block on device pointers.  out_dev: bf16 [T,H] block output; or, when resid_io is given,
+// resid_io[T,H] (f32) += block output without an intermediate rounding (out_dev unused).
+static int moe_block_impl(ColiMoe *m, const void *x_dev, void *out_dev, float *resid_io, int T, void *stream) {
   if (!check_T(m, T, "moe_block_dev")) return 0;
-  if (!x_dev || !out_dev) {
+  if (!x_dev || (!out_dev && !resid_io)) {
     coli_set_error("moe_block_dev: null pointer");
     return 0;
   }
@@ -736,7 +738,8 @@ extern "C" int coli_b200_moe_block_dev(ColiMoe *m, const void *x_dev, void *out_
   cp.slot = m->slot;
   cp.topk_w = m->topk_w;
   cp.out = (__nv_bfloat16 *)out_dev;
-  cp.out32 = nullptr;
+  cp.out32 = resid_io;
+  cp.resid = resid_io;
   if (!colib::launch_combine(cp, st)) return 0;
   COLI_MARK(5);
 #undef COLI_MARK
@@ -750,6 +753,35 @@ extern "C" int coli_b200_moe_block_dev(ColiMoe *m, const void *x_dev, void *out_
     m->phase_calls++;
   }
   return 1;
+}
+
+extern "C" int coli_b200_moe_block_dev(ColiMoe *m, const void *x_dev, void *out_dev, int T, void *stream) {
+  if (!out_dev) {
+    coli_set_error("moe_block_dev: null pointer");
+    return 0;
+  }
+  return moe_block_impl(m, x_dev, out_dev, nullptr, T, stream);
+}
+
+// The step around the block in the reference's layer loop (forward.rs:376-393): post-attention
+// RMSNorm of the f32 residual stream (math.rs:8-20), the MoE block on the normed rows rounded to
+// bf16, and the residual add, which is fused into the combine so that the block output is never
+// rounded on its way into the stream.
+extern "C" int coli_b200_moe_layer_step_dev(ColiMoe *m, float *resid_dev, const float *post_ln_w_dev, float eps, int T,
+                                            void *stream) {
+  if (!check_T(m, T, "moe_layer_step_dev")) return 0;
+  if (!resid_dev || !post_ln_w_dev) {
+    coli_set_error("moe_layer_step_dev: null pointer");
+    return 0;
+  }
+  if (!m->all_resident) {
+    coli_set_error("moe_layer_step_dev: not every expert is resident on this rank");
+    return 0;
+  }
+  if (T == 0) return 1;
+  cudaStream_t st = pick_stream(m, stream);
+  if (!colib::launch_rmsnorm_bf16(resid_dev, post_ln_w_dev, eps, m->x_stage, T, m->L.H, st)) return 0;
+  return moe_block_impl(m, m->x_stage, nullptr, resid_dev, T, stream);
 }
 
 // Synchronises the device and reports whether any kernel of this handle gave up on a bounded wait.
@@ -960,6 +992,7 @@ extern "C" int coli_b200_moe_combine_partial_dev(ColiMoe *m, const void *y_rows_
   cp.topk_w = topk_w_dev;
   cp.out = nullptr;
   cp.out32 = partial_dev;
+  cp.resid = nullptr;
   return colib::launch_combine(cp, pick_stream(m, stream));
 }
 

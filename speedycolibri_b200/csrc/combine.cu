@@ -52,7 +52,19 @@ __global__ void __launch_bounds__(256) k_combine(CombineParams p, const __nv_bfl
       acc[2 * i + 1] += __uint_as_float(u[i] & 0xffff0000u);
     }
   }
-  if (p.out32) {  // f32 partial sum of this rank's experts; summed across ranks before the final rounding
+  if (p.resid) {  // x += moe(x): the residual add of the layer, in f32 (forward.rs:391-393)
+    const float4 *r4 = reinterpret_cast<const float4 *>(p.resid + (size_t)t * p.H + c * 8);
+    const float4 a = r4[0], b = r4[1];
+    acc[0] = a.x + acc[0];
+    acc[1] = a.y + acc[1];
+    acc[2] = a.z + acc[2];
+    acc[3] = a.w + acc[3];
+    acc[4] = b.x + acc[4];
+    acc[5] = b.y + acc[5];
+    acc[6] = b.z + acc[6];
+    acc[7] = b.w + acc[7];
+  }
+  if (p.out32) {  // f32 out: the partial sum of this rank's experts, or the new residual stream
     float4 *o32 = reinterpret_cast<float4 *>(p.out32 + (size_t)t * p.H + c * 8);
     o32[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
     o32[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
@@ -112,6 +124,43 @@ int launch_finish(const float *partial, const __nv_bfloat16 *shared_y, __nv_bflo
   k_finish<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(partial, shared_y, out, n8);
   coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "finish launch") ? 1 : 0;
+}
+
+// One warp per token row.  Lane partial sums in f64, combined by a shuffle tree: not the
+// reference's left-to-right order, but 53-bit partials of 24-bit squares differ from it by less
+// than the f32 rounding of the mean in all but ~1e-9 of rows.
+__global__ void __launch_bounds__(256) k_rmsnorm_bf16(const float *x, const float *w, float eps, __nv_bfloat16 *out, int T, int H) {
+  const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (row >= T) return;
+  const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)row * H);
+  const float4 *wr = reinterpret_cast<const float4 *>(w);
+  double ms = 0.0;
+  for (int i = lane; i < H / 4; i += 32) {
+    const float4 v = xr[i];
+    ms += (double)v.x * (double)v.x + (double)v.y * (double)v.y + (double)v.z * (double)v.z + (double)v.w * (double)v.w;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ms += __shfl_xor_sync(0xffffffffu, ms, off);
+  const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float)(ms / (double)H), eps)));
+  uint2 *o = reinterpret_cast<uint2 *>(out + (size_t)row * H);
+  for (int i = lane; i < H / 4; i += 32) {
+    const float4 v = xr[i], g = wr[i];
+    const uint32_t a = __bfloat16_as_ushort(__float2bfloat16_rn(__fmul_rn(__fmul_rn(v.x, r), g.x)));
+    const uint32_t b = __bfloat16_as_ushort(__float2bfloat16_rn(__fmul_rn(__fmul_rn(v.y, r), g.y)));
+    const uint32_t c = __bfloat16_as_ushort(__float2bfloat16_rn(__fmul_rn(__fmul_rn(v.z, r), g.z)));
+    const uint32_t d = __bfloat16_as_ushort(__float2bfloat16_rn(__fmul_rn(__fmul_rn(v.w, r), g.w)));
+    o[i] = make_uint2(a | (b << 16), c | (d << 16));
+  }
+}
+int launch_rmsnorm_bf16(const float *x, const float *w, float eps, __nv_bfloat16 *out, int T, int H, cudaStream_t st) {
+  if (T <= 0) return 1;
+  if (H % 4) {
+    coli_set_error("rmsnorm: H=%d must be a multiple of 4", H);
+    return 0;
+  }
+  k_rmsnorm_bf16<<<(T + 7) / 8, 256, 0, st>>>(x, w, eps, out, T, H);
+  coli_count_launch(1);
+  return coli_cuda_check(cudaGetLastError(), "rmsnorm launch") ? 1 : 0;
 }
 
 __global__ void k_f32_to_bf16(const float *src, __nv_bfloat16 *dst, size_t n) {

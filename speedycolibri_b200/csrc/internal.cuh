@@ -175,11 +175,17 @@ struct CombineParams {
   const int32_t *slot;            // [T*k]
   const float *topk_w;            // [T*k]
   __nv_bfloat16 *out;             // [T,H] bf16 result, or
-  float *out32;                   // [T,H] f32 partial sum (no rounding, no shared add) when not null
+  float *out32;                   // [T,H] f32 result when not null: the partial sum of this rank's experts
+                                  // (has_shared = 0), or with `resid` the layer's new residual stream
+  const float *resid;             // [T,H] f32 residual stream added to the block output (forward.rs:391-393);
+                                  // may alias out32 (every element is read and written by one thread)
 };
 int launch_combine(const CombineParams &p, cudaStream_t st);
 int launch_finish(const float *partial, const __nv_bfloat16 *shared_y, __nv_bfloat16 *out, int T, int H, cudaStream_t st);
 int launch_f32_to_bf16(const float *src, __nv_bfloat16 *dst, size_t n, cudaStream_t st);
+// out[t] = bf16(x[t] * r_t * w), r_t = 1 / sqrt(mean(x[t]^2) + eps) with the mean square accumulated
+// in f64 (math.rs:8-20); H must be a multiple of 4
+int launch_rmsnorm_bf16(const float *x, const float *w, float eps, __nv_bfloat16 *out, int T, int H, cudaStream_t st);
 // activations for the expert GEMMs: the bf16 value (rounding f32 to bf16 first), held in f16
 int launch_bf16_to_f16(const __nv_bfloat16 *src, __half *dst, size_t n, cudaStream_t st);
 int launch_f32_to_f16_via_bf16(const float *src, __half *dst, size_t n, cudaStream_t st);

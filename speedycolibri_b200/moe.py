@@ -125,6 +125,18 @@ class MoeBlock:
                "coli_b200_moe_block_dev")
         return out
 
+    def layer_step(self, resid, post_ln_w, eps: float, stream=None):
+        """The layer step around the block (forward.rs:376-393), in place on the f32 residual stream:
+        resid += moe_block(bf16(rmsnorm(resid, post_ln_w, eps))).  torch f32 CUDA [T,H] and [H]."""
+        import torch
+
+        assert resid.dtype == torch.float32 and resid.is_cuda and resid.is_contiguous()
+        assert post_ln_w.dtype == torch.float32 and post_ln_w.is_cuda and post_ln_w.numel() == resid.shape[1]
+        st = torch.cuda.current_stream(resid.device).cuda_stream if stream is None else stream
+        _check(_lib_().coli_b200_moe_layer_step_dev(self.handle, resid.data_ptr(), post_ln_w.data_ptr(), float(eps), resid.shape[0], st),
+               "coli_b200_moe_layer_step_dev")
+        return resid
+
     def check(self) -> None:
         """Synchronise and raise if a kernel of this handle abandoned a bounded device-side wait."""
         _check(_lib_().coli_b200_moe_check(self.handle), "coli_b200_moe_check")

@@ -556,3 +556,31 @@ def test_layer_loaded_from_container(gpu_backend, orc, tmp_path):
     assert np.array_equal(idx, want["idx"]) and np.array_equal(w.view(np.uint32), want["w"].view(np.uint32))
     assert rel_l2(out, want["out"]) <= 5e-3
     blk.close()
+
+
+@pytest.mark.parametrize("name,T", [("tiny", 5), ("tiny_sig", 37), ("mid", 433)])
+def test_layer_step_rmsnorm_block_residual(gpu_backend, orc, name, T):
+    """coli_b200_moe_layer_step_dev against the reference's layer loop (forward.rs:376-393) restated
+    with the oracle: nrm = rmsnorm(x) (math.rs:8-20), tmp = moe(bf16(nrm)), x += tmp."""
+    import torch
+
+    shape = CONFIGS[name].with_tokens(T)
+    L, packed = host_layer(shape)
+    blk = make_block(shape, upload_layer(shape, packed))
+    rng = np.random.default_rng(T)
+    resid = (rng.standard_normal((T, shape.H)) * 3.0).astype(np.float32)
+    w = (1.0 + 0.1 * rng.standard_normal(shape.H)).astype(np.float32)
+    eps = 1e-5
+    nrm_bits = synth.f32_to_bf16_bits(orc.rmsnorm(resid, w, eps))
+    want = L.moe_block(nrm_bits)
+    r = torch.from_numpy(resid.copy()).cuda()
+    blk.layer_step(r, torch.from_numpy(w).cuda(), eps)
+    blk.check()
+    idx, rw = blk.last_routing(T)
+    assert np.array_equal(idx, want["idx"]) and np.array_equal(rw.view(np.uint32), want["w"].view(np.uint32)), \
+        "the normed rows must round to the same bf16 values, or the routing differs"
+    delta = r.cpu().numpy().astype(np.float64) - resid.astype(np.float64)
+    ref = synth.bf16_bits_to_f32(want["out"]).astype(np.float64)
+    err = np.linalg.norm(delta - ref) / np.linalg.norm(ref)
+    assert err <= 5e-3, err
+    blk.close()

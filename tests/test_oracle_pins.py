@@ -350,3 +350,11 @@ def test_swiglu_clamp_is_asymmetric_and_is_not_oai(orc):
     assert abs(f(2.0, 0.0)) < 1e-6
     # limit = 0 and oai = 0 is the plain SiLU arm
     assert orc.act_combine(50.0, 50.0, 0, 0.0, 0.0) == orc.lib().orc_siluf(50.0) * 50.0
+
+
+def test_rmsnorm_gives_unit_rms_with_unit_weight(orc):
+    """crates/colibri-engine/src/math.rs:185-195."""
+    out = orc.rmsnorm(np.array([[3.0, 4.0]], np.float32), np.array([1.0, 1.0], np.float32), 0.0)[0]
+    rms = math.sqrt((out[0] * out[0] + out[1] * out[1]) / 2.0)
+    assert abs(rms - 1.0) < 1e-5
+    assert abs(out[1] / out[0] - 4.0 / 3.0) < 1e-5
