@@ -9,8 +9,8 @@ import threading
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_HERE, "csrc")
 LIB_PATH = os.path.join(_HERE, "libcoli_b200.so")
-SOURCES = ["abi.cu", "routing.cu", "layout.cu", "expert_small.cu", "expert_tc.cu", "combine.cu"]
-HEADERS = ["internal.cuh", "coli_math.h", os.path.join("..", "..", "include", "coli_b200.h")]
+SOURCES = ["abi.cu", "routing.cu", "layout.cu", "expert_small.cu", "expert_tc.cu", "expert_tc_tmem.cu", "combine.cu"]
+HEADERS = ["internal.cuh", "tc_common.cuh", "coli_math.h", os.path.join("..", "..", "include", "coli_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-ffp-contract=off", "-shared",

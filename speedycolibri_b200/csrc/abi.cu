@@ -406,6 +406,12 @@ extern "C" void *coli_b200_moe_stream(ColiMoe *m) { return m ? (void *)m->ctx->s
 // The tcgen05 path takes over from 8 rows per segment on average (NVFP4 only): below that the
 // register-level kernel re-reads so few token rows per weight tile that it wins; a pure function of
 // (rows, segments, format) so that kernel selection never depends on data or addresses.
+// Which tcgen05 kernel: the one with the weight operand in tensor memory takes tiles of at most
+// 128 tokens and wins while segments are about that long; longer segments amortise the
+// shared-memory weight tiles of the other kernel over 256 tokens.  A function of shapes only.
+static bool use_tct(int rows, int nseg) {
+  return rows <= 160 * (nseg > 0 ? nseg : 1);
+}
 static bool use_tc_path(int fmt, int rows, int nseg) {
   return fmt == COLI_FMT_NVFP4 && nseg > 0 && rows / nseg >= 8;
 }
@@ -659,7 +665,8 @@ static int moe_block_impl(ColiMoe *m, const void *x_dev, void *out_dev, float *r
   const int k = m->L.k;
   const int rows = T * k + (m->has_shared ? T : 0);
   const bool tc = use_tc_path(m->L.fmt, rows, m->nseg) && m->xg != nullptr;
-  const int rpi = tc ? colib::TC_MAX_TOKENS : rows_per_item_for(m->L, rows, m->nseg);
+  const bool tct = tc && use_tct(rows, m->nseg);
+  const int rpi = tc ? (tct ? colib::TCT_MAX_TOKENS : colib::TC_MAX_TOKENS) : rows_per_item_for(m->L, rows, m->nseg);
   const int max_items = max_work_items(rows, m->nseg, rpi);
   const bool prof = m->profiling;
 #define COLI_MARK(i)                                                         \
@@ -697,9 +704,10 @@ static int moe_block_impl(ColiMoe *m, const void *x_dev, void *out_dev, float *r
     tp.y = m->y;
     tp.status = m->status;
     tp.act = m->act;
-    if (!colib::launch_gate_up_tc(tp, m->xg, rows, m->sm_count, st)) return 0;
+    if (!(tct ? colib::launch_gate_up_tct(tp, m->xg, rows, m->sm_count, st) : colib::launch_gate_up_tc(tp, m->xg, rows, m->sm_count, st)))
+      return 0;
     COLI_MARK(3);
-    if (!colib::launch_down_tc(tp, rows, m->sm_count, st)) return 0;
+    if (!(tct ? colib::launch_down_tct(tp, rows, m->sm_count, st) : colib::launch_down_tc(tp, rows, m->sm_count, st))) return 0;
   } else {
     colib::FfnParams fp;
     fp.fmt = m->L.fmt;
@@ -897,7 +905,8 @@ static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, cons
                         void *y_dev, cudaStream_t st) {
   if (rows_cap == 0 || n_seg == 0) return 1;
   const bool tc = use_tc_path(m->L.fmt, rows_expected, n_seg);
-  const int rpi = tc ? colib::TC_MAX_TOKENS : rows_per_item_for(m->L, rows_expected, n_seg);
+  const bool tct = tc && use_tct(rows_expected, n_seg);
+  const int rpi = tc ? (tct ? colib::TCT_MAX_TOKENS : colib::TC_MAX_TOKENS) : rows_per_item_for(m->L, rows_expected, n_seg);
   const int max_items = max_work_items(rows_cap, n_seg, rpi);
   if (!ensure_h(m, (size_t)rows_cap) || !ensure_items(m, max_items)) return 0;
   if (!colib::launch_items_from_counts(seg_count_dev, n_seg, rpi, m->seg_off, m->item_seg, m->item_row0, m->item_nrows,
@@ -920,6 +929,7 @@ static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, cons
     tp.y = (__nv_bfloat16 *)y_dev;
     tp.status = m->status;
     tp.act = m->act;
+    if (tct) return colib::launch_gate_up_tct(tp, rows_dev, rows_cap, m->sm_count, st) && colib::launch_down_tct(tp, rows_cap, m->sm_count, st);
     return colib::launch_gate_up_tc(tp, rows_dev, rows_cap, m->sm_count, st) && colib::launch_down_tc(tp, rows_cap, m->sm_count, st);
   }
   colib::FfnParams fp;

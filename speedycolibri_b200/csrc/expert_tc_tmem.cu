@@ -1,0 +1,373 @@
+// Expert FFN for segments of up to 160 rows per tile on the 5th-generation tensor cores, with the
+// weight operand in TENSOR MEMORY.
+//
+// Same formulation as expert_tc.cu (features on the MMA's M = 128, the ragged token count on its
+// N), but the decoded weights never pass through shared memory:
+// * A operand: 16 producer warps stream the packed NVFP4 bytes from HBM with 128-bit loads (one
+//   thread = one weight row = one TMEM lane), convert them to f16 in registers and write 64 k per
+//   stage straight into a ring of six 32-column TMEM slots with tcgen05.st.  A stage holds two
+//   weight tiles (gate + up of the same 128 features, or two adjacent 128-feature tiles of down),
+//   so the ring is three stages deep.
+// * B operand: up to 160 token rows x 64 k of f16 activations per stage, copied by TMA
+//   (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into an 8-deep shared-memory ring and
+//   shared by both weight tiles of the stage.
+// * tcgen05.mma kind::f16 with A from tensor memory and B through a shared-memory descriptor,
+//   two accumulators of 160 columns; the epilogue forms act(g, u) or writes the two down tiles.
+// Why: with both operands in shared memory an MMA of 128 x 128 x 16 fetches 8 KB per 64 cycles,
+// the whole shared-memory bandwidth of an SM, before a single decoded weight is stored there
+// (expert_tc.cu tops out near half of the tensor peak at 128 tokens per expert).  Here shared
+// memory carries only the token tiles: 16 KB written + 32 KB read per 512 cycles of MMA.
+// TMEM budget: 2 x 160 accumulator columns + 6 x 32 weight columns = 512, which is why this
+// kernel takes tiles of at most 160 tokens (a layer with 128 rows per expert on average has
+// nearly all of its segments under that); wider segments are cut into several work items.
+//
+// Roles are warp-specialised and synchronise through mbarriers only; the kernel is persistent.
+// Every barrier wait is bounded: on a time-out the CTA raises a status word, stops issuing work,
+// waits for its own copies and frees its TMEM before returning.
+#include "tc_common.cuh"
+
+namespace colib {
+
+constexpr int TT_A_STAGES = 3;               // stages of the TMEM weight ring (2 slots of 32 columns each)
+constexpr int TT_B_STAGES = 6;               // shared-memory ring of token tiles; also the number of stage barriers
+constexpr int TT_ACC_COLS = TCT_MAX_TOKENS;  // columns per accumulator
+constexpr int TT_A_COL0 = 2 * TT_ACC_COLS;   // weight ring: columns 320..511
+static_assert(TT_A_COL0 + TT_A_STAGES * 64 <= 512 && TT_ACC_COLS % 32 == 0, "TMEM budget");
+constexpr int TT_PROD_WARPS = 16;
+constexpr int TT_MMA2_WARP = 2 + TC_EPI_WARPS + TT_PROD_WARPS;       // the second MMA-issuing warp
+constexpr int TT_THREADS = 32 * (TT_MMA2_WARP + 1);                  // 736
+constexpr int TT_B_BYTES = TCT_MAX_TOKENS * TC_BK * 2;               // 16 KiB
+constexpr int TT_NBARS = 2 * TT_B_STAGES + 2;
+static_assert(TT_B_STAGES % TT_A_STAGES == 0, "a stage barrier serves both rings");
+
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The MMAs of one 64-k stage into ONE accumulator and the commit that releases the stage's
+// operands, as one instruction sequence: four k steps of 16 (8 TMEM columns of f16 weights, 32
+// bytes = 2 descriptor units of tokens per step).
+__device__ __forceinline__ void tt_issue_stage(uint32_t acc, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate_first,
+                                               uint32_t bar) {
+  asm volatile(
+      "{\n"
+      ".reg .pred pf, pt;\n"
+      ".reg .b64 bd;\n"
+      ".reg .b32 a;\n"
+      "setp.ne.b32 pf, %4, 0;\n"
+      "setp.eq.b32 pt, %4, %4;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, pf;\n"
+      "add.s64 bd, %2, 2;\n"
+      "add.u32 a, %1, 8;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], bd, %3, pt;\n"
+      "add.s64 bd, %2, 4;\n"
+      "add.u32 a, %1, 16;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], bd, %3, pt;\n"
+      "add.s64 bd, %2, 6;\n"
+      "add.u32 a, %1, 24;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], bd, %3, pt;\n"
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%5];\n"
+      "}\n"
+      ::"r"(acc), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate_first), "r"(bar)
+      : "memory");
+}
+// 32 consecutive columns of this thread's lane
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
+      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+      "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+      "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// The 64 weights (32 packed bytes) and 4 block-scale bytes of one row for one 64-k stage.
+struct TtPacked {
+  uint4 q0, q1;
+  uint32_t sc;
+};
+__device__ __forceinline__ TtPacked tt_load_packed(const WeightRef &w, int Op, int row, int kb) {
+  TtPacked r;
+  r.q0 = make_uint4(0, 0, 0, 0);
+  r.q1 = r.q0;
+  r.sc = 0;
+  if (row < Op) {
+    const size_t base = (size_t)(kb >> 1) * Op + row;
+    const uint8_t *qp = w.q + base * 64 + (kb & 1) * 32;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.q0.x), "=r"(r.q0.y), "=r"(r.q0.z), "=r"(r.q0.w)
+                 : "l"(qp));
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.q1.x), "=r"(r.q1.y), "=r"(r.q1.z), "=r"(r.q1.w)
+                 : "l"(qp + 16));
+    asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(r.sc) : "l"(w.s + base * 8 + (kb & 1) * 4));
+  }
+  return r;
+}
+// Convert one stage of one row and hand it to the tensor core through 32 TMEM columns.
+__device__ __forceinline__ void tt_emit_stage(const TtPacked &pk, uint32_t taddr) {
+  uint32_t r[32];
+  uint32_t m0, m1, m2, m3;
+  tc_scales(pk.sc, m0, m1);
+  tc_scales(pk.sc >> 16, m2, m3);
+  const uint32_t w[8] = {pk.q0.x, pk.q0.y, pk.q0.z, pk.q0.w, pk.q1.x, pk.q1.y, pk.q1.z, pk.q1.w};
+  const uint32_t m[4] = {m0, m1, m2, m3};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint4 o = tc_dequant_word(w[j], m[j >> 1]);
+    r[4 * j] = o.x;
+    r[4 * j + 1] = o.y;
+    r[4 * j + 2] = o.z;
+    r[4 * j + 3] = o.w;
+  }
+  tmem_st32(taddr, r);
+  tmem_st_wait();
+}
+
+// GATED: the two weight tiles of a stage are gate and up of the same 128 features, result
+// h = act(g, u).  Otherwise: two adjacent 128-feature tiles of the down projection, result y.
+template <bool GATED>
+__global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant__ CUtensorMap tmap, TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + TT_B_STAGES * TT_B_BYTES);
+  // One "filled" and one "drained" barrier per stage of the token ring serve both operands: the
+  // issuing threads then pay one wait and one commit per stage.  filled[s]: 8 producer warps + the
+  // TMA thread's expect_tx arrival.  drained[s]: the commits of the two issuing threads.  The
+  // weight ring is half as deep, so a producer about to fill stage `it` waits for drained of
+  // stage it - TT_A_STAGES.
+  const uint32_t full_s = smem_u32(bars), empty_s = smem_u32(bars + TT_B_STAGES);
+  const uint32_t acc_full = smem_u32(bars + TT_NBARS - 2), acc_empty = smem_u32(bars + TT_NBARS - 1);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + TT_NBARS);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int K = GATED ? p.H : p.I, Oout = GATED ? p.I : p.H;
+  const int Op = (Oout + 15) & ~15;
+  const int KB = ((K + 127) >> 7) * 2;      // 64-wide k blocks, covering the zero-padded k tiles
+  const int FT = GATED ? TC_BM : 2 * TC_BM;  // output features per tile
+  const int n_ftiles = (Oout + FT - 1) / FT;
+  const int n_work = *p.n_items * n_ftiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TT_B_STAGES; ++s) {
+      mbar_init(full_s + 8 * s, 9);
+      mbar_init(empty_s + 8 * s, 2);
+    }
+    mbar_init(acc_full, 2);
+    mbar_init(acc_empty, TC_EPI_WARPS);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA: token tiles ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool alive = true;
+      for (int w = blockIdx.x; w < n_work && alive; w += gridDim.x) {
+        const int item = w / n_ftiles;
+        const int row0 = p.item_row0[item], nrows = p.item_nrows[item];
+        const int N = (nrows + TC_BOXN - 1) / TC_BOXN * TC_BOXN;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const uint32_t s = it % TT_B_STAGES, ph = (it / TT_B_STAGES) & 1u;
+          if (!mbar_wait(empty_s + 8 * s, ph ^ 1u, abort_flag, p.status, TC_ERR_TMA_WAIT, 32)) {
+            alive = false;
+            break;
+          }
+          const uint32_t dst = smem_u32(smem + s * TT_B_BYTES);
+          mbar_expect_tx(full_s + 8 * s, (uint32_t)N * TC_BK * 2);
+          for (int j = 0; j < N / TC_BOXN; ++j)
+            tma_load_2d(dst + j * (TC_BOXN * TC_BK * 2), &tmap, kb * TC_BK, row0 + j * TC_BOXN, full_s + 8 * s);
+        }
+      }
+      if (!alive) {
+        // copies already issued still land in this CTA's shared memory: give them time before exit
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1 || warp == TT_MMA2_WARP) {
+    // ---------------- MMA issue: warp 1 feeds accumulator 0, the extra warp accumulator 1 ----------------
+    if (lane == 0) {
+      const uint32_t which = warp == 1 ? 0u : 1u;
+      uint32_t tix = 0;
+      bool alive = true;
+      const uint64_t bdesc_ring = umma_smem_desc(smem_u32(smem));  // token-tile stage 0; stages are TT_B_BYTES apart
+      const uint32_t acc = tmem_base + which * TT_ACC_COLS;
+      const uint32_t a_ring = tmem_base + TT_A_COL0 + which * 32;
+      // ring positions as counters: this thread's instruction stream is the critical path of the
+      // kernel, so no division or modulo per stage
+      uint32_t sa = 0, sb = 0, phb = 0;
+      for (int w = blockIdx.x; w < n_work && alive; w += gridDim.x, ++tix) {
+        const int item = w / n_ftiles;
+        const int nrows = p.item_nrows[item];
+        const int N = (nrows + TC_BOXN - 1) / TC_BOXN * TC_BOXN;
+        const uint32_t idesc = umma_idesc(N);
+        if (!mbar_wait(acc_empty, (tix & 1u) ^ 1u, abort_flag, p.status, TC_ERR_MMA_WAIT, 1)) break;
+        tc_fence_after();
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(full_s + 8 * sb, phb, abort_flag, p.status, TC_ERR_MMA_WAIT, 1)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+          // both issuers commit: the rings are refilled once both accumulators have read them
+          tt_issue_stage(acc, a_ring + sa * 64, bdesc_ring + (uint64_t)(sb * (TT_B_BYTES >> 4)), idesc, kb ? 1u : 0u, empty_s + 8 * sb);
+          sa = sa == TT_A_STAGES - 1 ? 0u : sa + 1;
+          if (++sb == TT_B_STAGES) {
+            sb = 0;
+            phb ^= 1u;
+          }
+        }
+        if (alive) umma_commit(acc_full);
+      }
+    }
+  } else if (warp < 2 + TC_EPI_WARPS) {
+    // ---------------- epilogue: TMEM -> registers -> global ----------------
+    const int lg = warp & 3;  // TMEM lane group this warp may read
+    uint32_t tix = 0;
+    for (int w = blockIdx.x; w < n_work; w += gridDim.x, ++tix) {
+      const int item = w / n_ftiles, ft = w % n_ftiles;
+      const int seg = p.item_seg[item], row0 = p.item_row0[item], nrows = p.item_nrows[item];
+      const int ex = p.seg_expert ? p.seg_expert[seg] : seg;
+      const int N = (nrows + TC_BOXN - 1) / TC_BOXN * TC_BOXN;
+      const float s0 = GATED ? p.gate[ex].g : p.down[ex].g;
+      const float s1 = GATED ? p.up[ex].g : p.down[ex].g;
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait(acc_full, tix & 1u, abort_flag, p.status, TC_ERR_EPI_WAIT, 256);
+      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+      if (!ok) break;
+      tc_fence_after();
+      const int f = ft * FT + lg * 32 + lane;  // accumulator 0; accumulator 1 is feature f + 128 of down
+      const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16);
+      __half *out_h = p.h + (size_t)row0 * Oout + f;
+      __nv_bfloat16 *out_y = p.y + (size_t)row0 * Oout + f;
+      for (int c0 = 0; c0 < N; c0 += 16) {
+        uint32_t g[16], u[16];
+        tmem_ld16(tbase + c0, g);
+        tmem_ld16(tbase + TT_ACC_COLS + c0, u);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int col = c0 + j;
+          if (col < nrows) {
+            const float v0 = __uint_as_float(g[j]) * s0, v1 = __uint_as_float(u[j]) * s1;
+            if (GATED) {
+              if (f < Oout) out_h[(size_t)col * Oout] = coli_f32_to_f16_via_bf16(coli_act_fast(v0, v1, p.act));
+            } else {
+              __nv_bfloat16 *dst = out_y + (size_t)col * Oout;
+              if (f < Oout) *dst = __float2bfloat16_rn(v0);
+              if (f + TC_BM < Oout) dst[TC_BM] = __float2bfloat16_rn(v1);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty);
+    }
+  } else {
+    // ---------------- weight producers: HBM -> registers -> f16 -> tensor memory ----------------
+    // four groups of four warps (128 lanes = 128 weight rows each): group g fills weight tile
+    // (g & 1) of the stages whose index has parity (g >> 1)
+    const int grp = (warp - 2 - TC_EPI_WARPS) >> 2;
+    const int mtx = grp & 1, par = grp >> 1;
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may write
+    const int row = quarter * 32 + lane;
+    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + TT_A_COL0 + mtx * 32;
+    uint32_t it0 = 0;
+    bool alive = true;
+    auto stage = [&](const TtPacked &pk, uint32_t it) -> bool {
+      const uint32_t sa = it % TT_A_STAGES;
+      bool ok = true;
+      if (it >= (uint32_t)TT_A_STAGES) {  // the weight slot was last read by stage it - TT_A_STAGES
+        const uint32_t u = it - TT_A_STAGES;
+        if (lane == 0) ok = mbar_wait(empty_s + 8 * (u % TT_B_STAGES), (u / TT_B_STAGES) & 1u, abort_flag, p.status, TC_ERR_PROD_WAIT, 1);
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        if (!ok) return false;
+        tc_fence_after();
+      }
+      tt_emit_stage(pk, taddr + sa * 64);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full_s + 8 * (it % TT_B_STAGES));
+      return true;
+    };
+    for (int w = blockIdx.x; w < n_work && alive; w += gridDim.x, it0 += KB) {
+      const int item = w / n_ftiles, ft = w % n_ftiles;
+      const int seg = p.item_seg[item];
+      const int ex = p.seg_expert ? p.seg_expert[seg] : seg;
+      const WeightRef wr = GATED ? (mtx ? p.up[ex] : p.gate[ex]) : p.down[ex];
+      const int grow = GATED ? ft * TC_BM + row : ft * FT + mtx * TC_BM + row;
+      // this group's k blocks of the tile: those whose global stage index it0 + kb has parity `par`
+      const int kb0 = (int)((par - it0) & 1u);
+      TtPacked pa, pb;
+      pa.q0 = make_uint4(0, 0, 0, 0);
+      pa.q1 = pa.q0;
+      pa.sc = 0;
+      pb = pa;
+      if (kb0 < KB) pa = tt_load_packed(wr, Op, grow, kb0);
+      if (kb0 + 2 < KB) pb = tt_load_packed(wr, Op, grow, kb0 + 2);
+      // two register sets alternate (kb, kb+2 | kb+4, kb+6 | ...): the bytes of the next two stages
+      // of this group are in flight while one is converted, and no set is refilled before it is used
+      for (int kb = kb0; kb < KB && alive; kb += 4) {
+        alive = stage(pa, it0 + kb);
+        if (kb + 4 < KB) pa = tt_load_packed(wr, Op, grow, kb + 4);
+        if (alive && kb + 2 < KB) alive = stage(pb, it0 + kb + 2);
+        if (kb + 6 < KB) pb = tt_load_packed(wr, Op, grow, kb + 6);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+template <bool GATED>
+static int launch_tct(const TcParams &p, const void *rows_base, int rows_cap, int sm_count, cudaStream_t st) {
+  const size_t smem = (size_t)TT_B_STAGES * TT_B_BYTES + 1024 /*align*/ + 8 * TT_NBARS + 16 + 64;
+  static bool attr_done = false;
+  if (!attr_done) {
+    if (!coli_cuda_check(cudaFuncSetAttribute(k_ffn_tct<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                         "tcgen05 kernel shared-memory attribute"))
+      return 0;
+    attr_done = true;
+  }
+  CUtensorMap map;
+  if (!make_rows_map(&map, rows_base, rows_cap, GATED ? p.H : p.I)) return 0;
+  const int FT = GATED ? TC_BM : 2 * TC_BM;
+  const int n_ftiles = ((GATED ? p.I : p.H) + FT - 1) / FT;
+  const long max_work = (long)p.max_items * n_ftiles;
+  const int grid = (int)(max_work < sm_count ? max_work : sm_count);
+  if (grid <= 0) return 1;
+  k_ffn_tct<GATED><<<grid, TT_THREADS, smem, st>>>(map, p);
+  coli_count_launch(1);
+  return coli_cuda_check(cudaGetLastError(), "tcgen05 expert ffn launch") ? 1 : 0;
+}
+
+int launch_gate_up_tct(const TcParams &p, const void *x_rows, int rows_cap, int sm_count, cudaStream_t st) {
+  return launch_tct<true>(p, x_rows, rows_cap, sm_count, st);
+}
+int launch_down_tct(const TcParams &p, int rows_cap, int sm_count, cudaStream_t st) {
+  return launch_tct<false>(p, p.h, rows_cap, sm_count, st);
+}
+
+}  // namespace colib

@@ -165,6 +165,11 @@ struct TcParams {
 // x_rows: f16 [rows_cap, H] expert-contiguous rows (row index = position in the work list)
 int launch_gate_up_tc(const TcParams &p, const void *x_rows, int rows_cap, int sm_count, cudaStream_t st);
 int launch_down_tc(const TcParams &p, int rows_cap, int sm_count, cudaStream_t st);
+// expert_tc_tmem.cu — the same two stages with the weight operand in tensor memory; tiles of at
+// most TCT_MAX_TOKENS rows (the work list must be cut with that many rows per item)
+constexpr int TCT_MAX_TOKENS = 160;
+int launch_gate_up_tct(const TcParams &p, const void *x_rows, int rows_cap, int sm_count, cudaStream_t st);
+int launch_down_tct(const TcParams &p, int rows_cap, int sm_count, cudaStream_t st);
 
 // combine.cu
 struct CombineParams {
