@@ -46,10 +46,10 @@ def measured_peaks():
 # the experts and tokens, so 1/8 of every stream) times 8: a full c3 launch holds too much on
 # the device for a multi-pass capture.  The captures are summarised under profiles/.
 NCU_TRAFFIC = {
-    ("c3", 4096, "gate_up"): (8 * (622756608 + 11324672), "profiles/k_ffn_tc_c3s_full.md, c3s capture x 8"),
-    ("c3", 4096, "down"): (8 * (293647872 + 23667200), "profiles/k_ffn_tc_c3s_full.md, c3s capture x 8"),
-    ("c3s", 512, "gate_up"): (622756608 + 11324672, "profiles/k_ffn_tc_c3s_full.md"),
-    ("c3s", 512, "down"): (293647872 + 23667200, "profiles/k_ffn_tc_c3s_full.md"),
+    ("c3", 4096, "gate_up"): (8 * (663724800 + 11862528), "profiles/k_ffn_tct_c3s_full.md, c3s capture x 8"),
+    ("c3", 4096, "down"): (8 * (304030720 + 24761344), "profiles/k_ffn_tct_c3s_full.md, c3s capture x 8"),
+    ("c3s", 512, "gate_up"): (663724800 + 11862528, "profiles/k_ffn_tct_c3s_full.md"),
+    ("c3s", 512, "down"): (304030720 + 24761344, "profiles/k_ffn_tct_c3s_full.md"),
     ("c1", 8, "gate_up"): (92070144 + 2123008, "profiles/k_ffn_mm_c1_full.md"),
     ("c1", 8, "down"): (46130688 + 72192, "profiles/k_ffn_mm_c1_full.md"),
 }
