@@ -9,14 +9,16 @@
 //   weight tiles (gate + up of the same 128 features, or two adjacent 128-feature tiles of down),
 //   so the ring is three stages deep.
 // * B operand: up to 160 token rows x 64 k of f16 activations per stage, copied by TMA
-//   (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into an 8-deep shared-memory ring and
+//   (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a 6-deep shared-memory ring and
 //   shared by both weight tiles of the stage.
 // * tcgen05.mma kind::f16 with A from tensor memory and B through a shared-memory descriptor,
-//   two accumulators of 160 columns; the epilogue forms act(g, u) or writes the two down tiles.
+//   two accumulators of 160 columns, each fed by its own issuing thread (the instruction stream
+//   of a single issuing thread, not the tensor core, bounded the first version of this kernel);
+//   the epilogue forms act(g, u) or writes the two down tiles.
 // Why: with both operands in shared memory an MMA of 128 x 128 x 16 fetches 8 KB per 64 cycles,
 // the whole shared-memory bandwidth of an SM, before a single decoded weight is stored there
 // (expert_tc.cu tops out near half of the tensor peak at 128 tokens per expert).  Here shared
-// memory carries only the token tiles: 16 KB written + 32 KB read per 512 cycles of MMA.
+// memory carries only the token tiles: 16-20 KB written + twice that read per stage.
 // TMEM budget: 2 x 160 accumulator columns + 6 x 32 weight columns = 512, which is why this
 // kernel takes tiles of at most 160 tokens (a layer with 128 rows per expert on average has
 // nearly all of its segments under that); wider segments are cut into several work items.
@@ -36,17 +38,10 @@ static_assert(TT_A_COL0 + TT_A_STAGES * 64 <= 512 && TT_ACC_COLS % 32 == 0, "TME
 constexpr int TT_PROD_WARPS = 16;
 constexpr int TT_MMA2_WARP = 2 + TC_EPI_WARPS + TT_PROD_WARPS;       // the second MMA-issuing warp
 constexpr int TT_THREADS = 32 * (TT_MMA2_WARP + 1);                  // 736
-constexpr int TT_B_BYTES = TCT_MAX_TOKENS * TC_BK * 2;               // 16 KiB
+constexpr int TT_B_BYTES = TCT_MAX_TOKENS * TC_BK * 2;               // 20 KiB
 constexpr int TT_NBARS = 2 * TT_B_STAGES + 2;
 static_assert(TT_B_STAGES % TT_A_STAGES == 0, "a stage barrier serves both rings");
 
-// D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
 // The MMAs of one 64-k stage into ONE accumulator and the commit that releases the stage's
 // operands, as one instruction sequence: four k steps of 16 (8 TMEM columns of f16 weights, 32
 // bytes = 2 descriptor units of tokens per step).
