@@ -27,6 +27,7 @@ class MoeShape:
     shared: bool = True
     select_bias_std: float = 0.0   # sigmoid selection bias ~ N(0, std)
     zipf_s: float = 0.0            # > 0: additive logit bias giving Zipf(s) expert popularity
+    block_spread: float = 0.0      # > 0: every 128x128 weight block is scaled by exp(N(0, spread)) (host generation)
     note: str = ""
 
     def with_tokens(self, T: int) -> "MoeShape":
@@ -80,5 +81,11 @@ CONFIGS = {
     # prefill-sized segments (tcgen05 path), small enough for host generation
     "mid": MoeShape("mid", H=512, E=8, k=2, I=256, T=512, norm_topk=True),
     "mid_ragged": MoeShape("mid_ragged", H=320, E=6, k=2, I=192, T=333, shared=False),
+    # FP8 on the tcgen05 path: block scales that differ by orders of magnitude inside a row block,
+    # ragged K / feature counts, and the per-row scaled form
+    "mid_fp8": MoeShape("mid_fp8", H=512, E=8, k=2, I=256, T=512, fmt=FMT_FP8_B128, block_spread=1.5),
+    "mid_fp8_ragged": MoeShape("mid_fp8_ragged", H=320, E=6, k=2, I=192, T=333, shared=False, fmt=FMT_FP8_B128,
+                               block_spread=1.5),
+    "mid_fp8row": MoeShape("mid_fp8row", H=256, E=4, k=2, I=128, T=100, fmt=FMT_E4M3_ROW, block_spread=1.0),
     "tiny_zipf": MoeShape("tiny_zipf", H=64, E=16, k=4, I=32, T=70, shared=False, zipf_s=1.2),
 }

@@ -403,17 +403,18 @@ extern "C" int coli_b200_moe_phase_ms(ColiMoe *m, float *ms, int *calls) {
 }
 extern "C" void *coli_b200_moe_stream(ColiMoe *m) { return m ? (void *)m->ctx->stream : nullptr; }
 
-// The tcgen05 path takes over from 8 rows per segment on average (NVFP4 only): below that the
-// register-level kernel re-reads so few token rows per weight tile that it wins; a pure function of
-// (rows, segments, format) so that kernel selection never depends on data or addresses.
+// The tcgen05 path takes over from 8 rows per segment on average: below that the register-level
+// kernel re-reads so few token rows per weight tile that it wins; a pure function of (rows,
+// segments, format) so that kernel selection never depends on data or addresses.
 // Which tcgen05 kernel: the one with the weight operand in tensor memory takes tiles of at most
-// 128 tokens and wins while segments are about that long; longer segments amortise the
-// shared-memory weight tiles of the other kernel over 256 tokens.  A function of shapes only.
-static bool use_tct(int rows, int nseg) {
-  return rows <= 160 * (nseg > 0 ? nseg : 1);
+// 160 tokens and wins while segments are about that long; longer NVFP4 segments amortise the
+// shared-memory weight tiles of the other kernel over 256 tokens.  The FP8 formats exist in the
+// tensor-memory kernel only (longer segments are cut into several of its tiles).
+static bool use_tct(int fmt, int rows, int nseg) {
+  return fmt != COLI_FMT_NVFP4 || rows <= 160 * (nseg > 0 ? nseg : 1);
 }
 static bool use_tc_path(int fmt, int rows, int nseg) {
-  return fmt == COLI_FMT_NVFP4 && nseg > 0 && rows / nseg >= 8;
+  return (fmt == COLI_FMT_NVFP4 || fmt == COLI_FMT_FP8_B128 || fmt == COLI_FMT_E4M3_ROW) && nseg > 0 && rows / nseg >= 8;
 }
 
 static int rows_per_item_for(const ColiMoeLayer &L, int rows, int nseg) {
@@ -665,7 +666,7 @@ static int moe_block_impl(ColiMoe *m, const void *x_dev, void *out_dev, float *r
   const int k = m->L.k;
   const int rows = T * k + (m->has_shared ? T : 0);
   const bool tc = use_tc_path(m->L.fmt, rows, m->nseg) && m->xg != nullptr;
-  const bool tct = tc && use_tct(rows, m->nseg);
+  const bool tct = tc && use_tct(m->L.fmt, rows, m->nseg);
   const int rpi = tc ? (tct ? colib::TCT_MAX_TOKENS : colib::TC_MAX_TOKENS) : rows_per_item_for(m->L, rows, m->nseg);
   const int max_items = max_work_items(rows, m->nseg, rpi);
   const bool prof = m->profiling;
@@ -689,6 +690,7 @@ static int moe_block_impl(ColiMoe *m, const void *x_dev, void *out_dev, float *r
   COLI_MARK(2);
   if (tc) {
     colib::TcParams tp;
+    tp.fmt = m->L.fmt;
     tp.H = m->L.H;
     tp.I = m->L.I;
     tp.gate = m->gate;
@@ -905,7 +907,7 @@ static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, cons
                         void *y_dev, cudaStream_t st) {
   if (rows_cap == 0 || n_seg == 0) return 1;
   const bool tc = use_tc_path(m->L.fmt, rows_expected, n_seg);
-  const bool tct = tc && use_tct(rows_expected, n_seg);
+  const bool tct = tc && use_tct(m->L.fmt, rows_expected, n_seg);
   const int rpi = tc ? (tct ? colib::TCT_MAX_TOKENS : colib::TC_MAX_TOKENS) : rows_per_item_for(m->L, rows_expected, n_seg);
   const int max_items = max_work_items(rows_cap, n_seg, rpi);
   if (!ensure_h(m, (size_t)rows_cap) || !ensure_items(m, max_items)) return 0;
@@ -914,6 +916,7 @@ static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, cons
     return 0;
   if (tc) {
     colib::TcParams tp;
+    tp.fmt = m->L.fmt;
     tp.H = m->L.H;
     tp.I = m->L.I;
     tp.gate = g;

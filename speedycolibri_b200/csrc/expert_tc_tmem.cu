@@ -125,9 +125,96 @@ __device__ __forceinline__ void tt_emit_stage(const TtPacked &pk, uint32_t taddr
   tmem_st_wait();
 }
 
+// 16 consecutive columns of this thread's lane
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+// FP8 (e4m3 codes, one byte per weight): the 64 codes of one row for one 64-k stage and the
+// multiplier of the stage.  A weight is code x scale[row block][k-tile] (convert.rs:731-741, f32);
+// the accumulator runs over all of K inside tensor memory, so the scale cannot be applied per
+// k-tile to partial sums as the register-level kernel does.  Instead each 128-row tile is
+// normalised by the largest scale of its row block: the stage's codes are multiplied by
+// TT_FP8_HEADROOM x scale / max scale (an f16 in (0, 16], one rounding of 2^-11 relative per weight)
+// and the epilogue multiplies the finished sum by max scale / TT_FP8_HEADROOM in f32.  The
+// headroom keeps products of small codes with small relative scales out of the f16 subnormals.
+// Per-row scales (linear.rs:93-109) need no multiplier: the epilogue thread owns one row.
+constexpr float TT_FP8_HEADROOM = 16.0f;
+struct TtPacked8 {
+  uint4 q[4];
+  uint32_t mult;  // f16 multiplier in both halves
+};
+__device__ __forceinline__ uint32_t tt_f16x2_both(float v) {
+  const __half2 h = __float2half2_rn(v);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+__device__ __forceinline__ TtPacked8 tt_zero_packed8() {
+  TtPacked8 r;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) r.q[j] = make_uint4(0, 0, 0, 0);
+  r.mult = 0;
+  return r;
+}
+// `norm` = TT_FP8_HEADROOM / max scale of the row block (block-scaled form), `srow` = that block's
+// row of the scale grid; both unused for per-row scales.
+template <int FMT>
+__device__ __forceinline__ TtPacked8 tt_load_packed8(const WeightRef &w, int Op, int row, int kb, const float *srow, float norm) {
+  TtPacked8 r = tt_zero_packed8();
+  if (row < Op) {
+    const uint8_t *qp = w.q + ((size_t)(kb >> 1) * Op + row) * 128 + (kb & 1) * 64;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(r.q[j].x), "=r"(r.q[j].y), "=r"(r.q[j].z), "=r"(r.q[j].w)
+                   : "l"(qp + 16 * j));
+    r.mult = FMT == COLI_FMT_FP8_B128 ? tt_f16x2_both(__ldg(srow + (kb >> 1)) * norm) : 0x3c003c00u /* 1.0 */;
+  }
+  return r;
+}
+__device__ __forceinline__ void tt_cvt_e4m3x4(uint32_t w, uint32_t &p0, uint32_t &p1) {
+  asm("{ .reg .b16 h0, h1;\n"
+      "  mov.b32 {h0, h1}, %2;\n"
+      "  cvt.rn.f16x2.e4m3x2 %0, h0;\n"
+      "  cvt.rn.f16x2.e4m3x2 %1, h1; }\n"
+      : "=r"(p0), "=r"(p1)
+      : "r"(w));
+}
+template <int FMT>
+__device__ __forceinline__ void tt_emit_stage(const TtPacked8 &pk, uint32_t taddr) {
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    uint32_t r[16];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const uint4 v = pk.q[2 * half + j];
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        tt_cvt_e4m3x4(w[i], r[8 * j + 2 * i], r[8 * j + 2 * i + 1]);
+        if (FMT == COLI_FMT_FP8_B128) {
+          r[8 * j + 2 * i] = tc_hmul2(r[8 * j + 2 * i], pk.mult);
+          r[8 * j + 2 * i + 1] = tc_hmul2(r[8 * j + 2 * i + 1], pk.mult);
+        }
+      }
+    }
+    tmem_st16(taddr + 16 * half, r);
+  }
+  tmem_st_wait();
+}
+// Largest scale of one row block over all k-tiles (every thread of a tile computes the same value).
+__device__ __forceinline__ float tt_block_scale_max(const float *srow, int KT) {
+  float m = 0.0f;
+  for (int kt = 0; kt < KT; ++kt) m = fmaxf(m, __ldg(srow + kt));
+  return m;
+}
+
 // GATED: the two weight tiles of a stage are gate and up of the same 128 features, result
 // h = act(g, u).  Otherwise: two adjacent 128-feature tiles of the down projection, result y.
-template <bool GATED>
+template <bool GATED, int FMT>
 __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant__ CUtensorMap tmap, TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -240,14 +327,25 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
       const int seg = p.item_seg[item], row0 = p.item_row0[item], nrows = p.item_nrows[item];
       const int ex = p.seg_expert ? p.seg_expert[seg] : seg;
       const int N = (nrows + TC_BOXN - 1) / TC_BOXN * TC_BOXN;
-      const float s0 = GATED ? p.gate[ex].g : p.down[ex].g;
-      const float s1 = GATED ? p.up[ex].g : p.down[ex].g;
+      const int f = ft * FT + lg * 32 + lane;  // accumulator 0; accumulator 1 is feature f + 128 of down
+      const WeightRef w0 = GATED ? p.gate[ex] : p.down[ex], w1 = GATED ? p.up[ex] : p.down[ex];
+      float s0 = w0.g, s1 = w1.g;
+      if (FMT == COLI_FMT_FP8_B128) {
+        // undo the per-tile normalisation of the producers (both tiles of a stage are 128-row aligned)
+        const int KT = KB >> 1;
+        const int rb0 = (ft * FT) >> 7, rb1 = GATED ? rb0 : rb0 + 1, nrb = (Oout + 127) >> 7;
+        s0 = tt_block_scale_max(reinterpret_cast<const float *>(w0.s) + (size_t)rb0 * KT, KT) * (1.0f / TT_FP8_HEADROOM);
+        s1 = rb1 < nrb ? tt_block_scale_max(reinterpret_cast<const float *>(w1.s) + (size_t)rb1 * KT, KT) * (1.0f / TT_FP8_HEADROOM) : 0.0f;
+      } else if (FMT == COLI_FMT_E4M3_ROW) {
+        const int f1 = GATED ? f : f + TC_BM;
+        s0 = f < Oout ? __ldg(reinterpret_cast<const float *>(w0.s) + f) : 0.0f;
+        s1 = f1 < Oout ? __ldg(reinterpret_cast<const float *>(w1.s) + f1) : 0.0f;
+      }
       bool ok = true;
       if (lane == 0) ok = mbar_wait(acc_full, tix & 1u, abort_flag, p.status, TC_ERR_EPI_WAIT, 256);
       ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
       if (!ok) break;
       tc_fence_after();
-      const int f = ft * FT + lg * 32 + lane;  // accumulator 0; accumulator 1 is feature f + 128 of down
       const uint32_t tbase = tmem_base + ((uint32_t)(lg * 32) << 16);
       __half *out_h = p.h + (size_t)row0 * Oout + f;
       __nv_bfloat16 *out_y = p.y + (size_t)row0 * Oout + f;
@@ -286,7 +384,7 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + TT_A_COL0 + mtx * 32;
     uint32_t it0 = 0;
     bool alive = true;
-    auto stage = [&](const TtPacked &pk, uint32_t it) -> bool {
+    auto stage = [&](const auto &pk, uint32_t it) -> bool {
       const uint32_t sa = it % TT_A_STAGES;
       bool ok = true;
       if (it >= (uint32_t)TT_A_STAGES) {  // the weight slot was last read by stage it - TT_A_STAGES
@@ -296,7 +394,10 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
         if (!ok) return false;
         tc_fence_after();
       }
-      tt_emit_stage(pk, taddr + sa * 64);
+      if constexpr (FMT == COLI_FMT_NVFP4)
+        tt_emit_stage(pk, taddr + sa * 64);
+      else
+        tt_emit_stage<FMT>(pk, taddr + sa * 64);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(full_s + 8 * (it % TT_B_STAGES));
@@ -310,20 +411,39 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
       const int grow = GATED ? ft * TC_BM + row : ft * FT + mtx * TC_BM + row;
       // this group's k blocks of the tile: those whose global stage index it0 + kb has parity `par`
       const int kb0 = (int)((par - it0) & 1u);
-      TtPacked pa, pb;
-      pa.q0 = make_uint4(0, 0, 0, 0);
-      pa.q1 = pa.q0;
-      pa.sc = 0;
-      pb = pa;
-      if (kb0 < KB) pa = tt_load_packed(wr, Op, grow, kb0);
-      if (kb0 + 2 < KB) pb = tt_load_packed(wr, Op, grow, kb0 + 2);
       // two register sets alternate (kb, kb+2 | kb+4, kb+6 | ...): the bytes of the next two stages
       // of this group are in flight while one is converted, and no set is refilled before it is used
-      for (int kb = kb0; kb < KB && alive; kb += 4) {
-        alive = stage(pa, it0 + kb);
-        if (kb + 4 < KB) pa = tt_load_packed(wr, Op, grow, kb + 4);
-        if (alive && kb + 2 < KB) alive = stage(pb, it0 + kb + 2);
-        if (kb + 6 < KB) pb = tt_load_packed(wr, Op, grow, kb + 6);
+      if constexpr (FMT == COLI_FMT_NVFP4) {
+        TtPacked pa, pb;
+        pa.q0 = make_uint4(0, 0, 0, 0);
+        pa.q1 = pa.q0;
+        pa.sc = 0;
+        pb = pa;
+        if (kb0 < KB) pa = tt_load_packed(wr, Op, grow, kb0);
+        if (kb0 + 2 < KB) pb = tt_load_packed(wr, Op, grow, kb0 + 2);
+        for (int kb = kb0; kb < KB && alive; kb += 4) {
+          alive = stage(pa, it0 + kb);
+          if (kb + 4 < KB) pa = tt_load_packed(wr, Op, grow, kb + 4);
+          if (alive && kb + 2 < KB) alive = stage(pb, it0 + kb + 2);
+          if (kb + 6 < KB) pb = tt_load_packed(wr, Op, grow, kb + 6);
+        }
+      } else {
+        const float *srow = nullptr;
+        float norm = 0.0f;
+        if (FMT == COLI_FMT_FP8_B128 && grow < Op) {
+          const int KT = KB >> 1;
+          srow = reinterpret_cast<const float *>(wr.s) + (size_t)(grow >> 7) * KT;
+          norm = TT_FP8_HEADROOM / tt_block_scale_max(srow, KT);
+        }
+        TtPacked8 pa = tt_zero_packed8(), pb = pa;
+        if (kb0 < KB) pa = tt_load_packed8<FMT>(wr, Op, grow, kb0, srow, norm);
+        if (kb0 + 2 < KB) pb = tt_load_packed8<FMT>(wr, Op, grow, kb0 + 2, srow, norm);
+        for (int kb = kb0; kb < KB && alive; kb += 4) {
+          alive = stage(pa, it0 + kb);
+          if (kb + 4 < KB) pa = tt_load_packed8<FMT>(wr, Op, grow, kb + 4, srow, norm);
+          if (alive && kb + 2 < KB) alive = stage(pb, it0 + kb + 2);
+          if (kb + 6 < KB) pb = tt_load_packed8<FMT>(wr, Op, grow, kb + 6, srow, norm);
+        }
       }
     }
   }
@@ -336,12 +456,12 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
   }
 }
 
-template <bool GATED>
+template <bool GATED, int FMT>
 static int launch_tct(const TcParams &p, const void *rows_base, int rows_cap, int sm_count, cudaStream_t st) {
   const size_t smem = (size_t)TT_B_STAGES * TT_B_BYTES + 1024 /*align*/ + 8 * TT_NBARS + 16 + 64;
   static bool attr_done = false;
   if (!attr_done) {
-    if (!coli_cuda_check(cudaFuncSetAttribute(k_ffn_tct<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+    if (!coli_cuda_check(cudaFuncSetAttribute(k_ffn_tct<GATED, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                          "tcgen05 kernel shared-memory attribute"))
       return 0;
     attr_done = true;
@@ -353,16 +473,29 @@ static int launch_tct(const TcParams &p, const void *rows_base, int rows_cap, in
   const long max_work = (long)p.max_items * n_ftiles;
   const int grid = (int)(max_work < sm_count ? max_work : sm_count);
   if (grid <= 0) return 1;
-  k_ffn_tct<GATED><<<grid, TT_THREADS, smem, st>>>(map, p);
+  k_ffn_tct<GATED, FMT><<<grid, TT_THREADS, smem, st>>>(map, p);
   coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "tcgen05 expert ffn launch") ? 1 : 0;
 }
+template <bool GATED>
+static int launch_tct_fmt(const TcParams &p, const void *rows_base, int rows_cap, int sm_count, cudaStream_t st) {
+  switch (p.fmt) {
+    case COLI_FMT_NVFP4:
+      return launch_tct<GATED, COLI_FMT_NVFP4>(p, rows_base, rows_cap, sm_count, st);
+    case COLI_FMT_FP8_B128:
+      return launch_tct<GATED, COLI_FMT_FP8_B128>(p, rows_base, rows_cap, sm_count, st);
+    case COLI_FMT_E4M3_ROW:
+      return launch_tct<GATED, COLI_FMT_E4M3_ROW>(p, rows_base, rows_cap, sm_count, st);
+  }
+  coli_set_error("tcgen05 expert ffn: unsupported weight format %d", p.fmt);
+  return 0;
+}
 
 int launch_gate_up_tct(const TcParams &p, const void *x_rows, int rows_cap, int sm_count, cudaStream_t st) {
-  return launch_tct<true>(p, x_rows, rows_cap, sm_count, st);
+  return launch_tct_fmt<true>(p, x_rows, rows_cap, sm_count, st);
 }
 int launch_down_tct(const TcParams &p, int rows_cap, int sm_count, cudaStream_t st) {
-  return launch_tct<false>(p, p.h, rows_cap, sm_count, st);
+  return launch_tct_fmt<false>(p, p.h, rows_cap, sm_count, st);
 }
 
 }  // namespace colib

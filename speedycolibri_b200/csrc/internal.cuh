@@ -149,9 +149,10 @@ int launch_gate_up_small(const FfnParams &p, cudaStream_t st);  // h = silu(gate
 int launch_down_small(const FfnParams &p, cudaStream_t st);     // y = down h
 int launch_ffn_small(const FfnParams &p, cudaStream_t st);      // both
 
-// expert_tc.cu — tcgen05 path for prefill-sized segments (NVFP4)
+// expert_tc.cu — tcgen05 path for prefill-sized segments
 constexpr int TC_MAX_TOKENS = 256;  // token rows per tile = rows per work item on this path
 struct TcParams {
+  int fmt;  // COLI_FMT_NVFP4 (both kernels); COLI_FMT_FP8_B128 / COLI_FMT_E4M3_ROW (tensor-memory kernel only)
   int H, I;
   const WeightRef *gate, *up, *down;
   const int32_t *seg_expert;

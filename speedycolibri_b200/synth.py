@@ -69,7 +69,14 @@ def host_dense_weight(shape: MoeShape, which: str, expert: int) -> np.ndarray:
     """f32 [O,K] ~N(0, 0.02): gate/up are [I,H], down is [H,I] (convert.rs expert_oi)."""
     O, K = (shape.H, shape.I) if which == "down" else (shape.I, shape.H)
     rng = np.random.Generator(np.random.Philox(tensor_seed(shape.name, which, expert)))
-    return (rng.standard_normal((O, K)) * WEIGHT_STD).astype(np.float32)
+    w = (rng.standard_normal((O, K)) * WEIGHT_STD).astype(np.float32)
+    if shape.block_spread > 0.0:
+        # magnitudes that differ from one 128x128 block to the next (quantisation scales then do too)
+        srng = np.random.Generator(np.random.Philox(tensor_seed(shape.name, which + "_spread", expert)))
+        nb_o, nb_k = (O + 127) // 128, (K + 127) // 128
+        mult = np.exp(shape.block_spread * srng.standard_normal((nb_o, nb_k))).astype(np.float32)
+        w = w * np.repeat(np.repeat(mult, 128, axis=0), 128, axis=1)[:O, :K]
+    return w
 
 
 # ---- device (torch) generation: any shape, needs the GPU ------------------------------------------

@@ -5,13 +5,20 @@ import numpy as np
 
 from oracle import oracle
 from speedycolibri_b200 import synth
-from speedycolibri_b200.configs import FMT_NVFP4, MoeShape
+from speedycolibri_b200.configs import FMT_E4M3_ROW, FMT_NVFP4, MoeShape
 
 
 def quantize_host(shape: MoeShape, w: np.ndarray):
     """(q, s, g) in the reference's container layout, via the oracle's quantisers."""
     if shape.fmt == FMT_NVFP4:
         return oracle.quantize_nvfp4(w)
+    if shape.fmt == FMT_E4M3_ROW:
+        # per-row scaled e4m3 (linear.rs:93-109); the reference holds no encoder for it, so the rule
+        # of the 128x128 form is applied per row: scale = amax / 448, code = e4m3(w / scale)
+        sc = np.maximum(np.abs(w).max(axis=1) / 448.0, 1e-30).astype(np.float32)
+        enc = np.frompyfunc(lambda v: oracle.lib().orc_f32_to_e4m3(float(v)), 1, 1)
+        codes = enc((w / sc[:, None]).astype(np.float32)).astype(np.uint8)
+        return codes, sc, 1.0
     codes, sc = oracle.quantize_fp8_b128(w)
     return codes, sc, 1.0
 

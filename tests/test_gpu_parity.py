@@ -135,10 +135,13 @@ def test_block_small_shapes(gpu_backend, orc, name, T):
     blk.close()
 
 
-@pytest.mark.parametrize("name,T", [("mid", 512), ("mid", 433), ("mid_ragged", 333), ("mid_ragged", 1000)])
+@pytest.mark.parametrize("name,T", [("mid", 512), ("mid", 433), ("mid_ragged", 333), ("mid_ragged", 1000),
+                                    ("mid_fp8", 512), ("mid_fp8", 97), ("mid_fp8_ragged", 333), ("mid_fp8_ragged", 1000),
+                                    ("mid_fp8row", 100)])
 def test_block_prefill_segments_tcgen05(gpu_backend, orc, name, T):
-    """Segments of >= 48 rows take the tcgen05 path (TMA token tiles, TMEM accumulators): ragged
-    segment lengths, K and feature counts that are not multiples of the tile, > 256 rows per expert."""
+    """Segments of >= 8 rows on average take the tcgen05 path (TMA token tiles, TMEM accumulators):
+    ragged segment lengths, K and feature counts that are not multiples of the tile, > 256 rows per
+    expert; NVFP4 and both FP8 forms (block scales spread over orders of magnitude, per-row scales)."""
     shape = CONFIGS[name].with_tokens(T)
     L, packed = host_layer(shape)
     blk = make_block(shape, upload_layer(shape, packed))
