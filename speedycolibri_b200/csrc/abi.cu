@@ -413,6 +413,11 @@ extern "C" void *coli_b200_moe_stream(ColiMoe *m) { return m ? (void *)m->ctx->s
 static bool use_tct(int fmt, int rows, int nseg) {
   return fmt != COLI_FMT_NVFP4 || rows <= 160 * (nseg > 0 ? nseg : 1);
 }
+// Tile width of the tensor-memory kernel: short tiles (and a weight ring twice as deep) while the
+// average segment fits one of them with room to spare, the full width otherwise.
+static int tct_tile_tokens(int rows, int nseg) {
+  return rows <= 48 * (nseg > 0 ? nseg : 1) ? colib::TCT_SHORT_TOKENS : colib::TCT_MAX_TOKENS;
+}
 static bool use_tc_path(int fmt, int rows, int nseg) {
   return (fmt == COLI_FMT_NVFP4 || fmt == COLI_FMT_FP8_B128 || fmt == COLI_FMT_E4M3_ROW) && nseg > 0 && rows / nseg >= 8;
 }
@@ -667,7 +672,7 @@ static int moe_block_impl(ColiMoe *m, const void *x_dev, void *out_dev, float *r
   const int rows = T * k + (m->has_shared ? T : 0);
   const bool tc = use_tc_path(m->L.fmt, rows, m->nseg) && m->xg != nullptr;
   const bool tct = tc && use_tct(m->L.fmt, rows, m->nseg);
-  const int rpi = tc ? (tct ? colib::TCT_MAX_TOKENS : colib::TC_MAX_TOKENS) : rows_per_item_for(m->L, rows, m->nseg);
+  const int rpi = tc ? (tct ? tct_tile_tokens(rows, m->nseg) : colib::TC_MAX_TOKENS) : rows_per_item_for(m->L, rows, m->nseg);
   const int max_items = max_work_items(rows, m->nseg, rpi);
   const bool prof = m->profiling;
 #define COLI_MARK(i)                                                         \
@@ -702,6 +707,7 @@ static int moe_block_impl(ColiMoe *m, const void *x_dev, void *out_dev, float *r
     tp.item_nrows = m->item_nrows;
     tp.n_items = m->n_items;
     tp.max_items = max_items;
+    tp.tile_tokens = rpi;
     tp.h = m->h;
     tp.y = m->y;
     tp.status = m->status;
@@ -908,7 +914,7 @@ static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, cons
   if (rows_cap == 0 || n_seg == 0) return 1;
   const bool tc = use_tc_path(m->L.fmt, rows_expected, n_seg);
   const bool tct = tc && use_tct(m->L.fmt, rows_expected, n_seg);
-  const int rpi = tc ? (tct ? colib::TCT_MAX_TOKENS : colib::TC_MAX_TOKENS) : rows_per_item_for(m->L, rows_expected, n_seg);
+  const int rpi = tc ? (tct ? tct_tile_tokens(rows_expected, n_seg) : colib::TC_MAX_TOKENS) : rows_per_item_for(m->L, rows_expected, n_seg);
   const int max_items = max_work_items(rows_cap, n_seg, rpi);
   if (!ensure_h(m, (size_t)rows_cap) || !ensure_items(m, max_items)) return 0;
   if (!colib::launch_items_from_counts(seg_count_dev, n_seg, rpi, m->seg_off, m->item_seg, m->item_row0, m->item_nrows,
@@ -928,6 +934,7 @@ static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, cons
     tp.item_nrows = m->item_nrows;
     tp.n_items = m->n_items;
     tp.max_items = max_items;
+    tp.tile_tokens = rpi;
     tp.h = m->h;
     tp.y = (__nv_bfloat16 *)y_dev;
     tp.status = m->status;

@@ -30,17 +30,26 @@
 
 namespace colib {
 
-constexpr int TT_A_STAGES = 3;               // stages of the TMEM weight ring (2 slots of 32 columns each)
-constexpr int TT_B_STAGES = 6;               // shared-memory ring of token tiles; also the number of stage barriers
-constexpr int TT_ACC_COLS = TCT_MAX_TOKENS;  // columns per accumulator
-constexpr int TT_A_COL0 = 2 * TT_ACC_COLS;   // weight ring: columns 320..511
-static_assert(TT_A_COL0 + TT_A_STAGES * 64 <= 512 && TT_ACC_COLS % 32 == 0, "TMEM budget");
+// TMEM budget (512 columns): two accumulators of ACC columns (= the most token rows of a tile) and a
+// weight ring of 64 columns per stage (gate + up, or two down tiles, of 64 k).  ACC = 160 leaves 3
+// stages; ACC = 64, for layers whose segments are short, leaves 6: the hand-over of a weight
+// stage (fill -> store wait -> barrier -> MMA -> commit -> barrier) is a latency chain of a few
+// thousand cycles, so the stage rate of a tile with few tokens grows with the depth of this ring.
+template <int ACC>
+struct TtBudget {
+  static constexpr int A_STAGES = (512 - 2 * ACC) / 64;
+  static constexpr int A_COL0 = 2 * ACC;
+  static_assert(ACC % 32 == 0 && A_STAGES >= 3 && A_COL0 + A_STAGES * 64 <= 512, "TMEM budget");
+  // shared-memory ring of token tiles (ACC rows x 64 k of f16 per stage); its depth is also the
+  // number of stage barriers (a ring twice as deep was measured and changed nothing)
+  static constexpr int B_BYTES = ACC * TC_BK * 2;
+  static constexpr int B_STAGES = 6;
+  static constexpr int NBARS = 2 * B_STAGES + 2;
+  static_assert(B_STAGES % A_STAGES == 0 && B_BYTES % 1024 == 0, "a stage barrier serves both rings");
+};
 constexpr int TT_PROD_WARPS = 16;
 constexpr int TT_MMA2_WARP = 2 + TC_EPI_WARPS + TT_PROD_WARPS;       // the second MMA-issuing warp
 constexpr int TT_THREADS = 32 * (TT_MMA2_WARP + 1);                  // 736
-constexpr int TT_B_BYTES = TCT_MAX_TOKENS * TC_BK * 2;               // 20 KiB
-constexpr int TT_NBARS = 2 * TT_B_STAGES + 2;
-static_assert(TT_B_STAGES % TT_A_STAGES == 0, "a stage barrier serves both rings");
 
 // The MMAs of one 64-k stage into ONE accumulator and the commit that releases the stage's
 // operands, as one instruction sequence: four k steps of 16 (8 TMEM columns of f16 weights, 32
@@ -214,8 +223,10 @@ __device__ __forceinline__ float tt_block_scale_max(const float *srow, int KT) {
 
 // GATED: the two weight tiles of a stage are gate and up of the same 128 features, result
 // h = act(g, u).  Otherwise: two adjacent 128-feature tiles of the down projection, result y.
-template <bool GATED, int FMT>
+template <bool GATED, int FMT, int ACC>
 __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant__ CUtensorMap tmap, TcParams p) {
+  constexpr int TT_A_STAGES = TtBudget<ACC>::A_STAGES, TT_A_COL0 = TtBudget<ACC>::A_COL0, TT_ACC_COLS = ACC;
+  constexpr int TT_B_STAGES = TtBudget<ACC>::B_STAGES, TT_B_BYTES = TtBudget<ACC>::B_BYTES, TT_NBARS = TtBudget<ACC>::NBARS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + TT_B_STAGES * TT_B_BYTES);
@@ -456,12 +467,12 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
   }
 }
 
-template <bool GATED, int FMT>
+template <bool GATED, int FMT, int ACC>
 static int launch_tct(const TcParams &p, const void *rows_base, int rows_cap, int sm_count, cudaStream_t st) {
-  const size_t smem = (size_t)TT_B_STAGES * TT_B_BYTES + 1024 /*align*/ + 8 * TT_NBARS + 16 + 64;
+  const size_t smem = (size_t)TtBudget<ACC>::B_STAGES * TtBudget<ACC>::B_BYTES + 1024 /*align*/ + 8 * TtBudget<ACC>::NBARS + 16 + 64;
   static bool attr_done = false;
   if (!attr_done) {
-    if (!coli_cuda_check(cudaFuncSetAttribute(k_ffn_tct<GATED, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+    if (!coli_cuda_check(cudaFuncSetAttribute(k_ffn_tct<GATED, FMT, ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                          "tcgen05 kernel shared-memory attribute"))
       return 0;
     attr_done = true;
@@ -473,19 +484,27 @@ static int launch_tct(const TcParams &p, const void *rows_base, int rows_cap, in
   const long max_work = (long)p.max_items * n_ftiles;
   const int grid = (int)(max_work < sm_count ? max_work : sm_count);
   if (grid <= 0) return 1;
-  k_ffn_tct<GATED, FMT><<<grid, TT_THREADS, smem, st>>>(map, p);
+  k_ffn_tct<GATED, FMT, ACC><<<grid, TT_THREADS, smem, st>>>(map, p);
   coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "tcgen05 expert ffn launch") ? 1 : 0;
+}
+template <bool GATED, int FMT>
+static int launch_tct_acc(const TcParams &p, const void *rows_base, int rows_cap, int sm_count, cudaStream_t st) {
+  if (p.tile_tokens == TCT_SHORT_TOKENS) return launch_tct<GATED, FMT, TCT_SHORT_TOKENS>(p, rows_base, rows_cap, sm_count, st);
+  if (p.tile_tokens == TCT_MAX_TOKENS) return launch_tct<GATED, FMT, TCT_MAX_TOKENS>(p, rows_base, rows_cap, sm_count, st);
+  coli_set_error("tcgen05 expert ffn: the work list must be cut with %d or %d rows per item, not %d", TCT_SHORT_TOKENS, TCT_MAX_TOKENS,
+                 p.tile_tokens);
+  return 0;
 }
 template <bool GATED>
 static int launch_tct_fmt(const TcParams &p, const void *rows_base, int rows_cap, int sm_count, cudaStream_t st) {
   switch (p.fmt) {
     case COLI_FMT_NVFP4:
-      return launch_tct<GATED, COLI_FMT_NVFP4>(p, rows_base, rows_cap, sm_count, st);
+      return launch_tct_acc<GATED, COLI_FMT_NVFP4>(p, rows_base, rows_cap, sm_count, st);
     case COLI_FMT_FP8_B128:
-      return launch_tct<GATED, COLI_FMT_FP8_B128>(p, rows_base, rows_cap, sm_count, st);
+      return launch_tct_acc<GATED, COLI_FMT_FP8_B128>(p, rows_base, rows_cap, sm_count, st);
     case COLI_FMT_E4M3_ROW:
-      return launch_tct<GATED, COLI_FMT_E4M3_ROW>(p, rows_base, rows_cap, sm_count, st);
+      return launch_tct_acc<GATED, COLI_FMT_E4M3_ROW>(p, rows_base, rows_cap, sm_count, st);
   }
   coli_set_error("tcgen05 expert ffn: unsupported weight format %d", p.fmt);
   return 0;

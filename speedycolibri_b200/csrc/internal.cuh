@@ -158,6 +158,7 @@ struct TcParams {
   const int32_t *seg_expert;
   const int32_t *item_seg, *item_row0, *item_nrows, *n_items;
   int max_items;
+  int tile_tokens;   // rows per item the work list was cut with: TC_MAX_TOKENS, TCT_MAX_TOKENS or TCT_SHORT_TOKENS
   __half *h;         // [rows, I]
   __nv_bfloat16 *y;  // [rows, H]
   int *status;       // device word: 0, or the code of the first bounded wait that gave up
@@ -169,6 +170,9 @@ int launch_down_tc(const TcParams &p, int rows_cap, int sm_count, cudaStream_t s
 // expert_tc_tmem.cu — the same two stages with the weight operand in tensor memory; tiles of at
 // most TCT_MAX_TOKENS rows (the work list must be cut with that many rows per item)
 constexpr int TCT_MAX_TOKENS = 160;
+// ... or with TCT_SHORT_TOKENS rows per item, for layers whose segments are short: narrower
+// accumulators leave tensor memory for a weight ring twice as deep (TcParams::tile_tokens says which)
+constexpr int TCT_SHORT_TOKENS = 64;
 int launch_gate_up_tct(const TcParams &p, const void *x_rows, int rows_cap, int sm_count, cudaStream_t st);
 int launch_down_tct(const TcParams &p, int rows_cap, int sm_count, cudaStream_t st);
 
