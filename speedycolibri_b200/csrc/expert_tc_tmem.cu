@@ -104,12 +104,10 @@ __device__ __forceinline__ TtPacked tt_load_packed(const WeightRef &w, int Op, i
   if (row < Op) {
     const size_t base = (size_t)(kb >> 1) * Op + row;
     const uint8_t *qp = w.q + base * 64 + (kb & 1) * 32;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r.q0.x), "=r"(r.q0.y), "=r"(r.q0.z), "=r"(r.q0.w)
+    // one 256-bit load: the 32-byte sector of this row and stage is requested from L2 once
+    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r.q0.x), "=r"(r.q0.y), "=r"(r.q0.z), "=r"(r.q0.w), "=r"(r.q1.x), "=r"(r.q1.y), "=r"(r.q1.z), "=r"(r.q1.w)
                  : "l"(qp));
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r.q1.x), "=r"(r.q1.y), "=r"(r.q1.z), "=r"(r.q1.w)
-                 : "l"(qp + 16));
     asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(r.sc) : "l"(w.s + base * 8 + (kb & 1) * 4));
   }
   return r;
@@ -175,11 +173,13 @@ __device__ __forceinline__ TtPacked8 tt_load_packed8(const WeightRef &w, int Op,
   TtPacked8 r = tt_zero_packed8();
   if (row < Op) {
     const uint8_t *qp = w.q + ((size_t)(kb >> 1) * Op + row) * 128 + (kb & 1) * 64;
+    // 256-bit loads: each 32-byte sector of this row and stage is requested from L2 once
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                   : "=r"(r.q[j].x), "=r"(r.q[j].y), "=r"(r.q[j].z), "=r"(r.q[j].w)
-                   : "l"(qp + 16 * j));
+    for (int j = 0; j < 2; ++j)
+      asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                   : "=r"(r.q[2 * j].x), "=r"(r.q[2 * j].y), "=r"(r.q[2 * j].z), "=r"(r.q[2 * j].w), "=r"(r.q[2 * j + 1].x),
+                     "=r"(r.q[2 * j + 1].y), "=r"(r.q[2 * j + 1].z), "=r"(r.q[2 * j + 1].w)
+                   : "l"(qp + 32 * j));
     r.mult = FMT == COLI_FMT_FP8_B128 ? tt_f16x2_both(__ldg(srow + (kb >> 1)) * norm) : 0x3c003c00u /* 1.0 */;
   }
   return r;
