@@ -50,6 +50,8 @@ NCU_TRAFFIC = {
     ("c3", 4096, "down"): (8 * (304030720 + 24761344), "profiles/k_ffn_tct_c3s_full.md, c3s capture x 8"),
     ("c3s", 512, "gate_up"): (663724800 + 11862528, "profiles/k_ffn_tct_c3s_full.md"),
     ("c3s", 512, "down"): (304030720 + 24761344, "profiles/k_ffn_tct_c3s_full.md"),
+    ("c2", 512, "gate_up"): (424864512 + 3916288, "profiles/k_ffn_tct_c2_full.md"),
+    ("c2", 512, "down"): (210126336 + 5060352, "profiles/k_ffn_tct_c2_full.md"),
     ("c1", 8, "gate_up"): (92070144 + 2123008, "profiles/k_ffn_mm_c1_full.md"),
     ("c1", 8, "down"): (46130688 + 72192, "profiles/k_ffn_mm_c1_full.md"),
 }
