@@ -3,11 +3,11 @@
 //
 // Same formulation as expert_tc.cu (features on the MMA's M = 128, the ragged token count on its
 // N), but the decoded weights never pass through shared memory:
-// * A operand: 16 producer warps stream the packed NVFP4 bytes from HBM with 128-bit loads (one
-//   thread = one weight row = one TMEM lane), convert them to f16 in registers and write 64 k per
-//   stage straight into a ring of six 32-column TMEM slots with tcgen05.st.  A stage holds two
-//   weight tiles (gate + up of the same 128 features, or two adjacent 128-feature tiles of down),
-//   so the ring is three stages deep.
+// * A operand: 16 producer warps stream the packed NVFP4 or FP8 bytes from HBM with 256-bit loads
+//   (one thread = one weight row = one TMEM lane), convert them to f16 in registers and write 64 k
+//   per stage straight into a ring of 32-column TMEM slots with tcgen05.st.  A stage holds two
+//   weight tiles (gate + up of the same 128 features, or two adjacent 128-feature tiles of down);
+//   the ring is three stages deep beside 160-column accumulators, six beside 64-column ones.
 // * B operand: up to 160 token rows x 64 k of f16 activations per stage, copied by TMA
 //   (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a 6-deep shared-memory ring and
 //   shared by both weight tiles of the stage.
@@ -22,6 +22,7 @@
 // TMEM budget: 2 x 160 accumulator columns + 6 x 32 weight columns = 512, which is why this
 // kernel takes tiles of at most 160 tokens (a layer with 128 rows per expert on average has
 // nearly all of its segments under that); wider segments are cut into several work items.
+// Layers with short segments run a second instantiation with 2 x 64 + 12 x 32 columns.
 //
 // Roles are warp-specialised and synchronise through mbarriers only; the kernel is persistent.
 // Every barrier wait is bounded: on a time-out the CTA raises a status word, stops issuing work,
