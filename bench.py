@@ -132,24 +132,6 @@ def config_dict(shape, world, extra=None):
 # ---------------------------------------------------------------------------------------------------
 # reference arm: the CPU restatement on the host cores
 # ---------------------------------------------------------------------------------------------------
-def host_sample_layer(shape, x_bits, oracle):
-    """Oracle layer holding only the experts the sample tokens route to (generated on the host)."""
-    from speedycolibri_b200 import synth
-    from tests.helpers import host_packed_expert
-
-    router = synth.host_router(shape)
-    sb, lb = synth.select_bias(shape), synth.zipf_logit_bias(shape)
-    probe = oracle.Layer(shape.H, shape.E, shape.k, shape.I, shape.score, shape.norm_topk, shape.routed_scale,
-                         shape.n_group, shape.topk_group, shape.fmt, router, [None] * shape.E, None, sb, lb)
-    idx, _ = probe.route_tokens(x_bits)
-    needed = sorted(set(idx.reshape(-1).tolist()))
-    experts = [host_packed_expert(shape, e) if e in needed else None for e in range(shape.E)]
-    shared = host_packed_expert(shape, shape.E) if shape.shared else None
-    L = oracle.Layer(shape.H, shape.E, shape.k, shape.I, shape.score, shape.norm_topk, shape.routed_scale,
-                     shape.n_group, shape.topk_group, shape.fmt, router, experts, shared, sb, lb)
-    return L, len(needed)
-
-
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -165,7 +147,9 @@ def run_reference(args):
     n_tok = max(1, min(shape.T, int(args.ref_tokens) if args.ref_tokens else max(1, int(2.0 / max(per_token_gflop, 1e-3)))))
     x = synth.host_tokens(shape, n_tok)
     t0 = time.perf_counter()
-    L, n_active = host_sample_layer(shape, x, oracle)
+    from oracle.layers import host_sample_layer
+
+    L, n_active = host_sample_layer(shape, x)
     setup_s = time.perf_counter() - t0
     for _ in range(args.warmup):
         L.moe_block(x)
@@ -191,7 +175,7 @@ def cpu_baseline_sample(shape, layer, x_dev, idx_all, n_tok):
     """Time the oracle on the first n_tok tokens with the experts exported from the GPU run."""
     import torch
     from oracle import oracle
-    from tests.helpers import oracle_layer_from_device
+    from oracle.layers import oracle_layer_from_device
 
     cores = oracle.hardware_threads()
     oracle.set_threads(cores)

@@ -32,6 +32,7 @@ extern "C" {
 #define COLI_FMT_F32 0
 #define COLI_FMT_E4M3_ROW 4
 #define COLI_FMT_NVFP4 5
+#define COLI_FMT_MXFP4 6
 #define COLI_FMT_FP8_B128 8
 
 /* Opaque, persistent HBM copy of one quantised matrix (backend_cuda.h:24). */
@@ -57,6 +58,24 @@ int coli_cuda_device_sync(int device);
 void coli_cuda_set_activation(int oai, float alpha, float limit);
 /* backend_cuda.h:48.  Resident tensors on `device` (< 0: all devices). */
 void coli_cuda_stats(int device, size_t *tensor_count, size_t *tensor_bytes);
+/* backend_cuda.h:51: live scratch of the host-pointer calls on `device` (< 0: all devices), not
+ * counting the resident weights. */
+size_t coli_cuda_scratch_bytes(int device);
+/* backend_cuda.h:52-53: totals over the grouped expert calls since load (calls, experts, rows) and
+ * their device-timed upload / kernel / download milliseconds. */
+void coli_cuda_group_stats(uint64_t *calls, uint64_t *experts, uint64_t *rows, double *h2d_ms, double *kernel_ms,
+                           double *d2h_ms);
+/* backend_cuda.h:86: 1 if the device reads pageable host memory in place.  Always 0 here: weights
+ * live in HBM and a "wrap" copies (the engine then skips its zero-copy branches, gpu.rs:207). */
+int coli_cuda_pageable_access(int device);
+/* backend_cuda.h:66 and 69: residency switches of the reference's unified-memory box; accepted
+ * and without effect (weights and expert staging are always device copies here). */
+void coli_cuda_set_weight_zerocopy(int on);
+void coli_cuda_set_ffn_devcopy(int on);
+/* backend_cuda.h:87-91: page-lock / release host memory the caller owns.  register returns 0 on
+ * failure with the error cleared; the caller carries on with pageable memory. */
+int coli_cuda_host_register(void *p, size_t bytes);
+void coli_cuda_host_unregister(void *p);
 /* Added: text of the most recent failure on the calling thread ("" if none).  The reference
  * logs "[CUDA] what: msg" to stderr (backend_cuda.cu:102-106); this library does both. */
 const char *coli_cuda_last_error(void);
@@ -77,6 +96,20 @@ int coli_cuda_tensor_wrap(ColiCudaTensor **tensor, const void *weights, const fl
  * [O, ceil(I/16)], `gscale` = per-tensor f32.  Host pointers; copied into HBM. */
 int coli_cuda_tensor_wrap_nvfp4(ColiCudaTensor **tensor, const void *weights, const void *bscale, float gscale,
                                 int I, int O, int device);
+/* backend_cuda.h:71-72 (Rust declaration cuda.rs:83-91).  MXFP4: the same packed e2m1 nibbles,
+ * `bscale` = one OCP E8M0 byte (2^(b-127)) per 32 inputs, [O, ceil(I/32)]; `gscale` is 1.0 in real
+ * containers (linear.rs:134-175).  Host pointers; copied into HBM, where the matrix is held in the
+ * NVFP4 form: every block scale becomes the ue4m3 code of the same power of two relative to the
+ * tensor's largest block scale (one shift per tensor, folded into gscale), so the decoded weights
+ * are bit-identical as long as a block lies within 17 binades of the largest one; a block further
+ * below decodes as zero (its weights are under 2^-17 of the largest block's), and a scale byte
+ * of 0xFF (NaN) stays NaN.  Blocks whose nibbles are all zero are ignored when the shift is chosen. */
+int coli_cuda_tensor_wrap_mxfp4(ColiCudaTensor **tensor, const void *weights, const void *bscale, float gscale,
+                                int I, int O, int device);
+/* Added: the host half of the call above, on HOST pointers and without touching a GPU: the ue4m3
+ * per-16 scale bytes [O, ceil(I/16)] and the tensor scale under which an MXFP4 matrix is held. */
+int coli_b200_mxfp4_resident_scales(const void *weights, const void *bscale, float gscale, int I, int O,
+                                    void *bscale16_out, float *gscale_out);
 /* backend_cuda.h:270-272. */
 void coli_cuda_tensor_free(ColiCudaTensor *tensor);
 size_t coli_cuda_tensor_bytes(const ColiCudaTensor *tensor);
@@ -97,7 +130,12 @@ int coli_b200_quantize_nvfp4(int device, const float *d_w, int O, int I, void *d
                              float *gscale);
 int coli_b200_quantize_fp8_b128(int device, const float *d_w, int O, int I, void *d_codes, float *d_scales);
 
-/* ---- expert FFN, reference signatures ------------------------------------------------------ */
+/* ---- expert FFN, reference signatures ------------------------------------------------------
+ * x is rounded from f32 to f16 on the device (nearest even, saturating at +-65504), as the
+ * reference's GPU path does before its fp16 MMA; y is f32.  A group that averages at least 8 rows
+ * per expert runs on the tcgen05 kernels, whose result passes through bf16 (2^-9 relative) before
+ * it is widened to f32; smaller groups write f32 directly.  The choice depends on the row counts
+ * alone. */
 /* backend_cuda.h:97-99 semantics for NVFP4 (backend_cuda.cu:3668-3806): y = down(silu(gate x) * up x),
  * x and y are HOST f32 [S, D] with D = gate->I; synchronous. */
 int coli_cuda_expert_mlp_nvfp4(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down, float *y,
@@ -105,6 +143,17 @@ int coli_cuda_expert_mlp_nvfp4(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCud
 /* backend_cuda.h:104-105 (fmt 4 per-row scaled e4m3; this library also accepts fmt 8). */
 int coli_cuda_expert_mlp_fp8(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down, float *y,
                              const float *x, int S);
+/* backend_cuda.h:75-76 and cuda.rs:212-220 (backend_cuda.cu:5707): the MXFP4 forms of the two
+ * calls above; fmt must be 6 on every tensor.  Same host-f32, synchronous contract. */
+int coli_cuda_expert_mlp_mxfp4(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down, float *y, const float *x,
+                               int S);
+int coli_cuda_expert_group_mxfp4(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups, ColiCudaTensor *const *downs,
+                                 const int *rows, int count, float *y, const float *x);
+/* backend_cuda.h:77-79: the same expert under Kimi-K3's "situ" activation.  That activation is not
+ * part of this library: the call always declines with 0 and an error text, as the reference's
+ * does when it cannot run (gpu.rs try_expert_ffn_mxfp4_situ falls back on a 0). */
+int coli_cuda_expert_mlp_mxfp4_situ(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down, float *y,
+                                    const float *x, int S, float beta, float linear_beta);
 /* backend_cuda.h:107-109 and 136-140: the format-agnostic forms of the calls above.  Accepted
  * formats are the ones this library keeps resident (4, 5, 8); the reference's f32 / int8 / int2
  * expert tensors are declined with 0. */
@@ -113,7 +162,7 @@ int coli_cuda_expert_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *
                            const int *rows, int count, float *y, const float *x);
 /* backend_cuda.h:127-129: y[S,O] = x[S,I] @ W[O,I]^T for an NVFP4 matrix (host f32 in and out,
  * synchronous).  The first call copies the container into HBM through *tensor, later calls reuse
- * the handle; x is rounded to bf16 on the device as in the expert calls. */
+ * the handle; x is rounded to f16 on the device as in the expert calls. */
 int coli_cuda_matmul_nvfp4(ColiCudaTensor **tensor, float *y, const float *x, const void *weights, const void *bscale,
                            float gscale, int S, int I, int O, int device);
 /* backend_cuda.h:131-132, 152-160: gateless ReLU^2 NVFP4 experts, y = down(relu(up x)^2)
@@ -149,7 +198,7 @@ typedef struct ColiMoeLayer {
   float routed_scale;      /* cfg.routed_scale */
   int32_t n_group;         /* 1 = ungrouped (the reference's only mode) */
   int32_t topk_group;
-  int32_t fmt;             /* COLI_FMT_NVFP4 or COLI_FMT_FP8_B128, all experts alike */
+  int32_t fmt;             /* COLI_FMT_NVFP4, _MXFP4, _FP8_B128 or _E4M3_ROW, all experts alike */
   int32_t device;
   const void *router_w;    /* HOST bf16 [E,H]; copied at create */
   const float *select_bias;/* HOST f32 [E] or NULL; sigmoid arm, selection only (moe.rs:1104) */
@@ -261,7 +310,8 @@ uint64_t coli_b200_launch_count(void);
  * device current) — make that first call before starting any stream capture.
  * All calls on one GPU share the one array: it keeps the previous call's logits (harmless, each
  * call overwrites its own [T,E] before reading) and two calls that overlap on the GPU — on
- * different streams, or from different threads — race on it; serialise them. */
+ * different streams, or from different threads — race on it; serialise them.
+ * x_dev and router_w_dev must be 16-byte aligned (128-bit loads); a misaligned pointer is refused. */
 #define COLI_ROUTE_NOALLOC_MAX_LOGITS 131072
 int coli_b200_route_noalloc(const void *x_dev, const void *router_w_dev, const float *select_bias_dev,
                             const float *logit_bias_dev, int T, int H, int E, int k, int score, int norm_topk,

@@ -58,7 +58,13 @@ extern "C" {
 // Weight formats: the reference's fmt codes (crates/colibri-core/src/quant.rs:707-746) plus
 // one code for the 128x128 block-scaled FP8 form that the reference only reads in its
 // converter (crates/colibri-engine/src/convert.rs:674-745).
-enum { ORC_FMT_F32 = 0, ORC_FMT_E4M3_ROW = 4, ORC_FMT_NVFP4 = 5, ORC_FMT_FP8_B128 = 8 };
+enum { ORC_FMT_F32 = 0, ORC_FMT_E4M3_ROW = 4, ORC_FMT_NVFP4 = 5, ORC_FMT_MXFP4 = 6, ORC_FMT_FP8_B128 = 8 };
+
+// OCP E8M0 block-scale byte: 2^(b - 127), 0xFF = NaN (crates/colibri-core/src/dtype.rs:136-141).
+static inline float e8m0_to_f32(uint8_t b) {
+  if (b == 0xFF) return std::numeric_limits<float>::quiet_NaN();
+  return ldexpf(1.0f, (int)b - 127);
+}
 
 typedef struct {
   int32_t H, E, k, I;
@@ -74,6 +80,7 @@ typedef struct {
   // Per-expert pointer tables with E (+1 when has_shared, the shared expert last) entries;
   // an expert that is never routed to may be NULL.
   // NVFP4: q = nibbles [O, K/2], s = ue4m3 bytes [O, K/16], g = f32 per matrix.
+  // MXFP4: q = nibbles [O, K/2], s = E8M0 bytes [O, K/32], g = f32 per matrix (1.0 in real containers).
   // FP8_B128: q = codes [O, K], s = f32 [ceil(O/128), ceil(K/128)], g unused.
   const uint8_t *const *gate_q, *const *up_q, *const *down_q;
   const void *const *gate_s, *const *up_s, *const *down_s;
@@ -87,6 +94,7 @@ uint8_t orc_e2m1_code(float t) { return coli_e2m1_code(t); }
 float orc_e2m1_to_f32(uint8_t n) { return coli_e2m1_to_f32(n); }
 uint16_t orc_f32_to_bf16(float v) { return coli_f32_to_bf16(v); }
 float orc_bf16_to_f32(uint16_t h) { return coli_bf16_to_f32(h); }
+float orc_e8m0_to_f32(uint8_t b) { return e8m0_to_f32(b); }
 float orc_expf(float x) { return coli_expf(x); }
 float orc_sigmoidf(float x) { return coli_sigmoidf(x); }
 float orc_siluf(float x) { return coli_siluf(x); }
@@ -142,6 +150,30 @@ void orc_quantize_fp8_b128(const float *w, int o, int i, uint8_t *codes, float *
 //                                                   applied once per output, after the sum)
 //   E4M3_ROW e4m3(w)                               (linear.rs:93-109; row scale after the sum)
 //   FP8_B128 e4m3(w) * scale[(o/128)*nbi + k/128]  (convert.rs:731-741, then an f32 matmul)
+// MXFP4 encoder of the reference's benchmark (crates/colibri-engine/src/gpubench.rs:84-119): per
+// block of 32 the smallest power of two 2^e with bmax / 2^e <= 6 (e = ceil(log2(bmax / 6)),
+// clamped to +-127, 0 for an all-zero block), scale byte 127 + e, nibble = nearest E2M1 level of
+// w / 2^e (first minimum wins, convert.rs:1078-1090).  No global scale (g = 1.0).
+void orc_quantize_mxfp4(const float *w, int o, int i, uint8_t *nib, uint8_t *bsc) {
+  const int nb = (i + 31) / 32, rb = (i + 1) / 2;
+  memset(nib, 0, (size_t)o * rb);
+  parallel_for(o, [&](int r) {
+    for (int b = 0; b < nb; ++b) {
+      const int c0 = b * 32, c1 = std::min((b + 1) * 32, i);
+      float bmax = 0.0f;
+      for (int c = c0; c < c1; ++c) bmax = std::max(bmax, std::fabs(w[(int64_t)r * i + c]));
+      int e = bmax > 0.0f ? (int)ceilf(log2f(bmax / 6.0f)) : 0;
+      e = std::max(-127, std::min(127, e));
+      bsc[(int64_t)r * nb + b] = (uint8_t)(127 + e);
+      const float sc = exp2f((float)e);
+      for (int c = c0; c < c1; ++c) {
+        const uint8_t code = coli_e2m1_code(w[(int64_t)r * i + c] / sc);
+        nib[(int64_t)r * rb + (c >> 1)] |= (c & 1) ? (uint8_t)(code << 4) : code;
+      }
+    }
+  });
+}
+
 static void decode_row(int fmt, const uint8_t *q, const void *s, int row, int K, float *wr) {
   if (fmt == ORC_FMT_NVFP4) {
     const int rb = (K + 1) / 2, nb = (K + 15) / 16;
@@ -151,6 +183,16 @@ static void decode_row(int fmt, const uint8_t *q, const void *s, int row, int K,
       const uint8_t byte = qr[k >> 1];
       const uint8_t n = (k & 1) ? (byte >> 4) : (byte & 0x0f);
       wr[k] = coli_e2m1_to_f32(n) * coli_e4m3_to_f32(br[k >> 4]);
+    }
+  } else if (fmt == ORC_FMT_MXFP4) {
+    // linear.rs:134-175: W[o,k] = E2M1[nib] * 2^(bs[o*nb + k/32] - 127), block scales decoded once per row
+    const int rb = (K + 1) / 2, nb = (K + 31) / 32;
+    const uint8_t *qr = q + (int64_t)row * rb;
+    const uint8_t *br = (const uint8_t *)s + (int64_t)row * nb;
+    for (int k = 0; k < K; ++k) {
+      const uint8_t byte = qr[k >> 1];
+      const uint8_t n = (k & 1) ? (byte >> 4) : (byte & 0x0f);
+      wr[k] = coli_e2m1_to_f32(n) * e8m0_to_f32(br[k >> 5]);
     }
   } else if (fmt == ORC_FMT_E4M3_ROW) {
     const uint8_t *qr = q + (int64_t)row * K;
@@ -166,15 +208,36 @@ static void decode_row(int fmt, const uint8_t *q, const void *s, int row, int K,
 }
 
 // y[S,O] = x[S,K] @ W[O,K]^T with a strictly k-ascending f32 sum per output
-// (linear.rs:18-133,199-220).  Eight tokens are accumulated side by side (independent
-// accumulators, so each output is still the reference's sequential sum); rows of W are
+// (linear.rs:18-175,199-220).  Tokens are accumulated side by side in blocks of 8, 4, 2 or 1
+// (independent accumulators, so each output is still the reference's sequential sum; a block is
+// never wider than the tokens left, so a one-row call does one row's arithmetic); rows of W are
 // spread over threads (disjoint outputs).
+extern "C++" {
+template <int W>
+static inline void dot_block(const float *wr, const float *xp, int K, float *acc) {
+  for (int j = 0; j < W; ++j) acc[j] = 0.0f;
+  for (int k = 0; k < K; ++k) {
+    const float wv = wr[k];
+    for (int j = 0; j < W; ++j) acc[j] += wv * xp[(size_t)k * W + j];
+  }
+}
+}
 void orc_matmul_qt(int fmt, const uint8_t *q, const void *s, float g, const float *x, float *y, int S,
                    int K, int O) {
-  const int nblk = (S + 7) / 8;
-  std::vector<float> xb((size_t)nblk * K * 8, 0.0f);  // [blk][k][8]
-  for (int si = 0; si < S; ++si)
-    for (int k = 0; k < K; ++k) xb[((size_t)(si >> 3) * K + k) * 8 + (si & 7)] = x[(size_t)si * K + k];
+  // token blocks: as many of 8 as fit, then one each of 4, 2, 1 for the remainder
+  struct Blk { int s0, w; size_t off; };
+  std::vector<Blk> blks;
+  size_t total = 0;
+  for (int s0 = 0; s0 < S;) {
+    const int left = S - s0, w = left >= 8 ? 8 : left >= 4 ? 4 : left >= 2 ? 2 : 1;
+    blks.push_back({s0, w, total});
+    total += (size_t)K * w;
+    s0 += w;
+  }
+  std::vector<float> xb(total);  // per block [k][w]
+  for (const Blk &b : blks)
+    for (int j = 0; j < b.w; ++j)
+      for (int k = 0; k < K; ++k) xb[b.off + (size_t)k * b.w + j] = x[(size_t)(b.s0 + j) * K + k];
   // rows in chunks of 16 so each task amortises its scratch row
   const int nchunk = (O + 15) / 16;
   parallel_for(nchunk, [&](int ch) {
@@ -182,20 +245,19 @@ void orc_matmul_qt(int fmt, const uint8_t *q, const void *s, float g, const floa
     for (int row = ch * 16; row < std::min(O, ch * 16 + 16); ++row) {
       decode_row(fmt, q, s, row, K, wr.data());
       float rs = 1.0f;
-      if (fmt == ORC_FMT_NVFP4) rs = g;
+      const bool scaled = fmt == ORC_FMT_NVFP4 || fmt == ORC_FMT_MXFP4 || fmt == ORC_FMT_E4M3_ROW;
+      if (fmt == ORC_FMT_NVFP4 || fmt == ORC_FMT_MXFP4) rs = g;
       if (fmt == ORC_FMT_E4M3_ROW) rs = ((const float *)s)[row];
-      for (int b = 0; b < nblk; ++b) {
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        const float *xp = &xb[(size_t)b * K * 8];
-        for (int k = 0; k < K; ++k) {
-          const float wv = wr[k];
-          for (int j = 0; j < 8; ++j) acc[j] += wv * xp[(size_t)k * 8 + j];
+      for (const Blk &b : blks) {
+        float acc[8];
+        const float *xp = &xb[b.off];
+        switch (b.w) {
+          case 8: dot_block<8>(wr.data(), xp, K, acc); break;
+          case 4: dot_block<4>(wr.data(), xp, K, acc); break;
+          case 2: dot_block<2>(wr.data(), xp, K, acc); break;
+          default: dot_block<1>(wr.data(), xp, K, acc); break;
         }
-        for (int j = 0; j < 8 && b * 8 + j < S; ++j) {
-          float a = acc[j];
-          if (fmt == ORC_FMT_NVFP4 || fmt == ORC_FMT_E4M3_ROW) a = a * rs;
-          y[(size_t)(b * 8 + j) * O + row] = a;
-        }
+        for (int j = 0; j < b.w; ++j) y[(size_t)(b.s0 + j) * O + row] = scaled ? acc[j] * rs : acc[j];
       }
     }
   });

@@ -12,7 +12,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liboracle.so")
 
-FMT_E4M3_ROW, FMT_NVFP4, FMT_FP8_B128 = 4, 5, 8
+FMT_E4M3_ROW, FMT_NVFP4, FMT_MXFP4, FMT_FP8_B128 = 4, 5, 6, 8
 
 
 def build(force: bool = False) -> str:
@@ -62,6 +62,8 @@ def lib() -> C.CDLL:
         L.orc_expf_array.restype, L.orc_expf_array.argtypes = None, [P, P, C.c_int64]
         L.orc_quantize_nvfp4.restype, L.orc_quantize_nvfp4.argtypes = None, [P, i, i, P, P, C.POINTER(f)]
         L.orc_quantize_fp8_b128.restype, L.orc_quantize_fp8_b128.argtypes = None, [P, i, i, P, P]
+        L.orc_quantize_mxfp4.restype, L.orc_quantize_mxfp4.argtypes = None, [P, i, i, P, P]
+        L.orc_e8m0_to_f32.restype, L.orc_e8m0_to_f32.argtypes = f, [C.c_uint8]
         L.orc_matmul_qt.restype, L.orc_matmul_qt.argtypes = None, [i, P, P, f, P, P, i, i, i]
         L.orc_expert_ffn.restype, L.orc_expert_ffn.argtypes = None, [C.POINTER(OrcLayer), i, P, i, P]
         L.orc_route.restype, L.orc_route.argtypes = None, [C.POINTER(OrcLayer), P, P, P]
@@ -128,6 +130,16 @@ def quantize_fp8_b128(w: np.ndarray):
     return codes, sc
 
 
+def quantize_mxfp4(w: np.ndarray):
+    """(nibbles [O, I/2], E8M0 block scales [O, ceil(I/32)], 1.0) — gpubench.rs:84-119."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    O, I = w.shape
+    nib = np.zeros((O, (I + 1) // 2), np.uint8)
+    bs = np.zeros((O, (I + 31) // 32), np.uint8)
+    lib().orc_quantize_mxfp4(_p(w), O, I, _p(nib), _p(bs))
+    return nib, bs, 1.0
+
+
 def matmul_qt(fmt: int, q: np.ndarray, s: np.ndarray, g: float, x: np.ndarray, O: int) -> np.ndarray:
     x = np.ascontiguousarray(x, dtype=np.float32)
     S, K = x.shape
@@ -162,7 +174,7 @@ class Layer:
             L.logit_bias = self.logit_bias.ctypes.data
         allx = list(experts) + ([shared] if shared is not None else [])
         n = len(allx)
-        sdt = np.uint8 if fmt == FMT_NVFP4 else np.float32
+        sdt = np.uint8 if fmt in (FMT_NVFP4, FMT_MXFP4) else np.float32
         tabs = {}
         for mi, name in enumerate(("gate", "up", "down")):
             qs, ss = (C.c_void_p * n)(), (C.c_void_p * n)()

@@ -25,17 +25,31 @@ def _stale() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile the library for sm_100a with nvcc (cross-compiles without a GPU)."""
+    """Compile the library for sm_100a with nvcc (cross-compiles without a GPU): one object per
+    source, compiled side by side, then one link."""
     if not force and not _stale():
         return LIB_PATH
-    cmd = ["nvcc", *NVCC_FLAGS, "-o", LIB_PATH, *SOURCES]
-    if verbose:
-        cmd.insert(1, "-Xptxas=-v")
-    r = subprocess.run(cmd, cwd=_CSRC, capture_output=True, text=True)
+    from concurrent.futures import ThreadPoolExecutor
+
+    objdir = os.path.join(_HERE, "build")
+    os.makedirs(objdir, exist_ok=True)
+    flags = [f for f in NVCC_FLAGS if f != "-shared"]
+
+    def compile_one(src):
+        obj = os.path.join(objdir, src.replace(".cu", ".o"))
+        cmd = ["nvcc", *flags, *(["-Xptxas=-v"] if verbose else []), "-c", "-o", obj, src]
+        r = subprocess.run(cmd, cwd=_CSRC, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {src}:\n" + r.stdout + r.stderr)
+        if verbose:
+            print(r.stderr)
+        return obj
+
+    with ThreadPoolExecutor(max_workers=min(8, len(SOURCES))) as pool:
+        objs = list(pool.map(compile_one, SOURCES))
+    r = subprocess.run(["nvcc", "-shared", "-o", LIB_PATH, *objs], cwd=_CSRC, capture_output=True, text=True)
     if r.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + r.stdout + r.stderr)
-    if verbose:
-        print(r.stderr)
+        raise RuntimeError("link failed:\n" + r.stdout + r.stderr)
     return LIB_PATH
 
 
@@ -70,6 +84,18 @@ SIGNATURES = {
     "coli_cuda_set_activation": (None, [_i, _f, _f]),
     "coli_cuda_stats": (None, [_i, C.POINTER(_sz), C.POINTER(_sz)]),
     "coli_cuda_last_error": (C.c_char_p, []),
+    "coli_cuda_scratch_bytes": (_sz, [_i]),
+    "coli_cuda_group_stats": (None, [_P, _P, _P, _P, _P, _P]),
+    "coli_cuda_pageable_access": (_i, [_i]),
+    "coli_cuda_set_weight_zerocopy": (None, [_i]),
+    "coli_cuda_set_ffn_devcopy": (None, [_i]),
+    "coli_cuda_host_register": (_i, [_P, _sz]),
+    "coli_cuda_host_unregister": (None, [_P]),
+    "coli_cuda_tensor_wrap_mxfp4": (_i, [_PP, _P, _P, _f, _i, _i, _i]),
+    "coli_b200_mxfp4_resident_scales": (_i, [_P, _P, _f, _i, _i, _P, C.POINTER(_f)]),
+    "coli_cuda_expert_mlp_mxfp4": (_i, [_P, _P, _P, _P, _P, _i]),
+    "coli_cuda_expert_group_mxfp4": (_i, [_PP, _PP, _PP, C.POINTER(_i), _i, _P, _P]),
+    "coli_cuda_expert_mlp_mxfp4_situ": (_i, [_P, _P, _P, _P, _P, _i, _f, _f]),
     "coli_cuda_tensor_upload": (_i, [_PP, _P, _P, _i, _i, _i, _i]),
     "coli_cuda_tensor_wrap": (_i, [_PP, _P, _P, _i, _i, _i, _i]),
     "coli_cuda_tensor_wrap_nvfp4": (_i, [_PP, _P, _P, _f, _i, _i, _i]),

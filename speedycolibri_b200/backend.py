@@ -9,7 +9,7 @@ import ctypes as C
 import numpy as np
 
 from . import _lib
-from .configs import FMT_E4M3_ROW, FMT_FP8_B128, FMT_NVFP4
+from .configs import FMT_E4M3_ROW, FMT_FP8_B128, FMT_MXFP4, FMT_NVFP4
 
 
 class CudaError(RuntimeError):
@@ -92,6 +92,17 @@ class CudaTensor:
         return cls(h.value, FMT_NVFP4, I, O, device)
 
     @classmethod
+    def wrap_mxfp4(cls, nibbles: np.ndarray, bscale: np.ndarray, gscale: float, I: int, O: int, device: int = 0):
+        """coli_cuda_tensor_wrap_mxfp4: nibbles [O, ceil(I/2)] u8, bscale [O, ceil(I/32)] E8M0 bytes."""
+        nibbles = np.ascontiguousarray(nibbles, dtype=np.uint8)
+        bscale = np.ascontiguousarray(bscale, dtype=np.uint8)
+        assert nibbles.size == O * ((I + 1) // 2) and bscale.size == O * ((I + 31) // 32)
+        h = C.c_void_p()
+        _check(_lib_().coli_cuda_tensor_wrap_mxfp4(C.byref(h), _np_ptr(nibbles), _np_ptr(bscale), float(gscale), I, O, device),
+               "coli_cuda_tensor_wrap_mxfp4")
+        return cls(h.value, FMT_MXFP4, I, O, device)
+
+    @classmethod
     def upload(cls, codes: np.ndarray, scales: np.ndarray, fmt: int, I: int, O: int, device: int = 0):
         """coli_cuda_tensor_upload for the FP8 forms (fmt 4: row scales [O]; fmt 8: [ceil(O/128), ceil(I/128)])."""
         codes = np.ascontiguousarray(codes, dtype=np.uint8)
@@ -119,6 +130,9 @@ class CudaTensor:
         if self.fmt == FMT_NVFP4:
             q = np.empty((O, (I + 1) // 2), np.uint8)
             s = np.empty((O, (I + 15) // 16), np.uint8)
+        elif self.fmt == FMT_MXFP4:
+            q = np.empty((O, (I + 1) // 2), np.uint8)
+            s = np.empty((O, (I + 31) // 32), np.uint8)
         elif self.fmt == FMT_FP8_B128:
             q = np.empty((O, I), np.uint8)
             s = np.empty(((O + 127) // 128, (I + 127) // 128), np.float32)
@@ -199,6 +213,40 @@ def expert_group_nvfp4(gates, ups, downs, rows, x: np.ndarray) -> np.ndarray:
     _check(_lib_().coli_cuda_expert_group_nvfp4(mk(gates), mk(ups), mk(downs), r, n, _np_ptr(y), _np_ptr(x)),
            "coli_cuda_expert_group_nvfp4")
     return y
+
+
+def expert_mlp_mxfp4(gate: CudaTensor, up: CudaTensor, down: CudaTensor, x: np.ndarray) -> np.ndarray:
+    """coli_cuda_expert_mlp_mxfp4 (cuda.rs:92-99): fmt 6 on all three; x, y host f32 [S, D]."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    y = np.empty_like(x)
+    _check(_lib_().coli_cuda_expert_mlp_mxfp4(gate.handle, up.handle, down.handle, _np_ptr(y), _np_ptr(x), x.shape[0]),
+           "coli_cuda_expert_mlp_mxfp4")
+    return y
+
+
+def expert_group_mxfp4(gates, ups, downs, rows, x: np.ndarray) -> np.ndarray:
+    """coli_cuda_expert_group_mxfp4 (cuda.rs:212-220): x holds sum(rows) rows in expert order."""
+    n = len(rows)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    y = np.empty_like(x)
+    mk = lambda ts: (C.c_void_p * n)(*[t.handle for t in ts])
+    r = (C.c_int * n)(*[int(v) for v in rows])
+    _check(_lib_().coli_cuda_expert_group_mxfp4(mk(gates), mk(ups), mk(downs), r, n, _np_ptr(y), _np_ptr(x)),
+           "coli_cuda_expert_group_mxfp4")
+    return y
+
+
+def scratch_bytes(device: int = -1) -> int:
+    """coli_cuda_scratch_bytes (backend_cuda.h:48-51)."""
+    return int(_lib_().coli_cuda_scratch_bytes(device))
+
+
+def group_stats() -> dict:
+    """coli_cuda_group_stats (backend_cuda.h:52-53): totals over the grouped expert calls since load."""
+    c, e, r = C.c_uint64(), C.c_uint64(), C.c_uint64()
+    a, b, d = C.c_double(), C.c_double(), C.c_double()
+    _lib_().coli_cuda_group_stats(C.byref(c), C.byref(e), C.byref(r), C.byref(a), C.byref(b), C.byref(d))
+    return dict(calls=c.value, experts=e.value, rows=r.value, h2d_ms=a.value, kernel_ms=b.value, d2h_ms=d.value)
 
 
 class F32Matmul:

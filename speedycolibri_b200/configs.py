@@ -5,6 +5,7 @@ from dataclasses import dataclass, replace
 
 FMT_E4M3_ROW = 4
 FMT_NVFP4 = 5
+FMT_MXFP4 = 6
 FMT_FP8_B128 = 8
 SCORE_SOFTMAX = 0
 SCORE_SIGMOID = 1
@@ -38,6 +39,8 @@ class MoeShape:
         """Packed bytes of one [O,K] weight matrix (crates/colibri-core/src/quant.rs:762-766)."""
         if self.fmt == FMT_NVFP4:
             return O * ((K + 1) // 2) + O * ((K + 15) // 16) + 4
+        if self.fmt == FMT_MXFP4:
+            return O * ((K + 1) // 2) + O * ((K + 31) // 32) + 4
         if self.fmt == FMT_FP8_B128:
             return O * K + 4 * ((O + 127) // 128) * ((K + 127) // 128)
         return O * K + 4 * O
@@ -87,5 +90,8 @@ CONFIGS = {
     "mid_fp8_ragged": MoeShape("mid_fp8_ragged", H=320, E=6, k=2, I=192, T=333, shared=False, fmt=FMT_FP8_B128,
                                block_spread=1.5),
     "mid_fp8row": MoeShape("mid_fp8row", H=256, E=4, k=2, I=128, T=100, fmt=FMT_E4M3_ROW, block_spread=1.0),
+    # MXFP4 (E8M0 scale per 32): register-level and tcgen05 kernel families
+    "tiny_mx": MoeShape("tiny_mx", H=128, E=8, k=2, I=64, T=21, fmt=FMT_MXFP4, norm_topk=True),
+    "mid_mx": MoeShape("mid_mx", H=512, E=8, k=2, I=256, T=512, fmt=FMT_MXFP4, norm_topk=True, block_spread=1.0),
     "tiny_zipf": MoeShape("tiny_zipf", H=64, E=16, k=4, I=32, T=70, shared=False, zipf_s=1.2),
 }

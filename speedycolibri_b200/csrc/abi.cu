@@ -41,6 +41,8 @@ struct DeviceContext {
   // scratch of the host-pointer expert calls, grown on demand
   void *buf[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   size_t cap[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};  // phase marks of the host-pointer group calls
+  int sm_count = 0;
 };
 std::mutex g_init_mu;
 DeviceContext *g_ctx[COLI_CUDA_MAX_DEVICES];
@@ -69,6 +71,12 @@ bool reserve(DeviceContext *c, int slot, size_t bytes) {
 
 extern "C" int coli_cuda_init(const int *devices, int count) {
   std::lock_guard<std::mutex> lk(g_init_mu);
+  for (int i = 0; devices && i < count && i < COLI_CUDA_MAX_DEVICES; ++i)  // a repeated ordinal is refused, backend_cuda.cu:2636-2640
+    for (int j = 0; j < i; ++j)
+      if (devices[i] == devices[j]) {
+        coli_set_error("coli_cuda_init: device %d is listed twice", devices[i]);
+        return 0;
+      }
   int n = 0;
   if (cudaGetDeviceCount(&n) != cudaSuccess || n < 1) {
     coli_set_error("no CUDA device is visible");
@@ -101,6 +109,7 @@ extern "C" int coli_cuda_init(const int *devices, int count) {
   for (int i = 0; i < count; ++i) {
     DeviceContext *c = new DeviceContext();
     c->device = devices[i];
+    cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, devices[i]);
     if (!coli_cuda_check(cudaSetDevice(c->device), "cudaSetDevice") ||
         !coli_cuda_check(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking), "stream creation")) {
       delete c;
@@ -120,6 +129,8 @@ extern "C" void coli_cuda_shutdown(void) {
     cudaStreamSynchronize(c->stream);
     for (int s = 0; s < 8; ++s)
       if (c->buf[s]) cudaFree(c->buf[s]);
+    for (int s = 0; s < 4; ++s)
+      if (c->ev[s]) cudaEventDestroy(c->ev[s]);
     cudaStreamDestroy(c->stream);
     delete c;
     g_ctx[i] = nullptr;
@@ -154,14 +165,52 @@ extern "C" void coli_cuda_stats(int device, size_t *tensor_count, size_t *tensor
   if (tensor_count) *tensor_count = n;
   if (tensor_bytes) *tensor_bytes = b;
 }
+// Live scratch of the host-pointer calls on `device` (< 0: all), excluding the weights that
+// coli_cuda_stats reports (backend_cuda.h:48-51).
+extern "C" size_t coli_cuda_scratch_bytes(int device) {
+  size_t b = 0;
+  for (int i = 0; i < g_ndev; ++i)
+    if (g_ctx[i] && (device < 0 || g_ctx[i]->device == device))
+      for (int s = 0; s < 8; ++s) b += g_ctx[i]->cap[s];
+  return b;
+}
+// backend_cuda.h:86: whether the device reads pageable host memory in place.  A B200 behind PCIe
+// does not (at any useful speed): every "wrap" of this library copies into HBM, so the answer is 0
+// and the engine never takes its zero-copy branches (gpu.rs:207).
+extern "C" int coli_cuda_pageable_access(int device) {
+  (void)device;
+  return 0;
+}
+// backend_cuda.h:66-69: residency switches of the reference's unified-memory box.  Weights are
+// always copied into HBM here and expert weights are always device copies, so both are accepted
+// and change nothing.
+extern "C" void coli_cuda_set_weight_zerocopy(int on) { (void)on; }
+extern "C" void coli_cuda_set_ffn_devcopy(int on) { (void)on; }
+// backend_cuda.h:87-91: page-lock host memory the engine owns, so that the copies of the
+// host-pointer calls run as DMA out of it.  0 on failure with the sticky error cleared: the caller
+// carries on with pageable memory.
+extern "C" int coli_cuda_host_register(void *p, size_t bytes) {
+  if (!p || bytes == 0) return 0;
+  if (cudaHostRegister(p, bytes, cudaHostRegisterDefault) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return 1;
+}
+extern "C" void coli_cuda_host_unregister(void *p) {
+  if (p && cudaHostUnregister(p) != cudaSuccess) cudaGetLastError();
+}
 // ---- resident weights ----------------------------------------------------------------------------
-static bool fmt_supported(int fmt) { return fmt == COLI_FMT_NVFP4 || fmt == COLI_FMT_FP8_B128 || fmt == COLI_FMT_E4M3_ROW; }
+static bool fmt_supported(int fmt) {
+  return fmt == COLI_FMT_NVFP4 || fmt == COLI_FMT_MXFP4 || fmt == COLI_FMT_FP8_B128 || fmt == COLI_FMT_E4M3_ROW;
+}
 
 static size_t src_q_bytes(int fmt, int I, int O) {
-  return fmt == COLI_FMT_NVFP4 ? (size_t)O * ((I + 1) / 2) : (size_t)O * I;
+  return (fmt == COLI_FMT_NVFP4 || fmt == COLI_FMT_MXFP4) ? (size_t)O * ((I + 1) / 2) : (size_t)O * I;
 }
 static size_t src_s_bytes(int fmt, int I, int O) {
   if (fmt == COLI_FMT_NVFP4) return (size_t)O * ((I + 15) / 16);
+  if (fmt == COLI_FMT_MXFP4) return (size_t)O * ((I + 31) / 32);
   if (fmt == COLI_FMT_FP8_B128) return sizeof(float) * (size_t)((O + 127) / 128) * ((I + 127) / 128);
   return sizeof(float) * (size_t)O;
 }
@@ -218,6 +267,10 @@ static int upload_from_host(ColiCudaTensor **tensor, const void *q, const void *
     coli_set_error("tensor upload: format %d is not part of the MoE expert path (supported: 4, 5, 8)", fmt);
     return 0;
   }
+  if (fmt == COLI_FMT_MXFP4) {
+    coli_set_error("tensor upload: MXFP4 carries E8M0 block scales; use coli_cuda_tensor_wrap_mxfp4");
+    return 0;
+  }
   if (*tensor) return existing_matches(*tensor, fmt, I, O, device);
   DeviceContext *ctx = find_ctx(device);
   if (!select_ctx(ctx)) return 0;
@@ -250,8 +303,92 @@ extern "C" int coli_cuda_tensor_wrap_nvfp4(ColiCudaTensor **tensor, const void *
                                            float gscale, int I, int O, int device) {
   return upload_from_host(tensor, weights, bscale, gscale, COLI_FMT_NVFP4, I, O, device);
 }
+// MXFP4 -> the resident NVFP4 form.  A block scale 2^e (E8M0 byte e + 127) becomes the ue4m3 code
+// of 2^(e + shift) in both 16-wide halves of its 32-wide block; shift = 8 - (largest e among blocks
+// that hold a non-zero weight), so the largest block scale lands on 2^8, the top of ue4m3's powers
+// of two, and blocks down to 2^-9 (17 binades lower) stay exact.  The tensor scale absorbs 2^-shift.
+static bool mxfp4_to_resident_scales(const uint8_t *nib, const uint8_t *e8, int O, int I, float gscale,
+                                     std::vector<uint8_t> &bs16, float *gscale_out) {
+  const int nb32 = (I + 31) / 32, nb16 = (I + 15) / 16, rb = (I + 1) / 2;
+  int max_e = -1000;
+  for (int o = 0; o < O; ++o)
+    for (int b = 0; b < nb32; ++b) {
+      const uint8_t code = e8[(size_t)o * nb32 + b];
+      if (code == 0xFF || (int)code - 127 <= max_e) continue;
+      const uint8_t *p = nib + (size_t)o * rb + 16 * b;
+      const int nbytes = (rb - 16 * b) < 16 ? (rb - 16 * b) : 16;
+      bool nonzero = false;
+      for (int j = 0; j < nbytes && !nonzero; ++j) nonzero = (p[j] & 0x77) != 0;  // magnitude bits of both nibbles
+      if (nonzero) max_e = (int)code - 127;
+    }
+  const int shift = max_e == -1000 ? 0 : 8 - max_e;
+  const double g2 = ldexp((double)gscale, -shift);
+  const float gf = (float)g2;
+  if (gscale != 0.0f && (!(fabs(g2) <= 3.0e38) || fabs(g2) < 1.2e-38)) {
+    coli_set_error("tensor_wrap_mxfp4: tensor scale %g with block exponents up to %d leaves the f32 range", (double)gscale, max_e);
+    return false;
+  }
+  bs16.assign((size_t)O * nb16, 0);
+  for (int o = 0; o < O; ++o)
+    for (int b = 0; b < nb16; ++b) {
+      const uint8_t code = e8[(size_t)o * nb32 + (b >> 1)];
+      uint8_t out;
+      if (code == 0xFF) {
+        out = 0x7F;  // NaN stays NaN (dtype.rs:137-139)
+      } else {
+        const int ec = (int)code - 127 + shift;
+        out = ec > 8 ? 0x78 /* only all-zero blocks get here */ : ec >= -6 ? (uint8_t)((ec + 7) << 3) : ec >= -9 ? (uint8_t)(1u << (ec + 9)) : 0;
+      }
+      bs16[(size_t)o * nb16 + b] = out;
+    }
+  *gscale_out = gf;
+  return true;
+}
+
+extern "C" int coli_b200_mxfp4_resident_scales(const void *weights, const void *bscale, float gscale, int I, int O,
+                                               void *bscale16_out, float *gscale_out) {
+  if (!weights || !bscale || !bscale16_out || !gscale_out || I < 1 || O < 1) {
+    coli_set_error("mxfp4_resident_scales: null pointer or empty shape");
+    return 0;
+  }
+  std::vector<uint8_t> bs16;
+  if (!mxfp4_to_resident_scales((const uint8_t *)weights, (const uint8_t *)bscale, O, I, gscale, bs16, gscale_out)) return 0;
+  memcpy(bscale16_out, bs16.data(), bs16.size());
+  return 1;
+}
+
+extern "C" int coli_cuda_tensor_wrap_mxfp4(ColiCudaTensor **tensor, const void *weights, const void *bscale,
+                                           float gscale, int I, int O, int device) {
+  if (!tensor || !weights || !bscale || I < 1 || O < 1) {
+    coli_set_error("tensor_wrap_mxfp4: null pointer or empty shape");
+    return 0;
+  }
+  if (*tensor) return existing_matches(*tensor, COLI_FMT_MXFP4, I, O, device);
+  std::vector<uint8_t> bs16;
+  float g2 = 0.0f;
+  if (!mxfp4_to_resident_scales((const uint8_t *)weights, (const uint8_t *)bscale, O, I, gscale, bs16, &g2)) return 0;
+  ColiCudaTensor *t = nullptr;
+  if (!upload_from_host(&t, weights, bs16.data(), g2, COLI_FMT_NVFP4, I, O, device)) return 0;
+  DeviceContext *ctx = find_ctx(device);
+  t->s_src_bytes = src_s_bytes(COLI_FMT_MXFP4, I, O);
+  if (!select_ctx(ctx) || !coli_cuda_check(cudaMalloc((void **)&t->s_src, t->s_src_bytes), "scale allocation") ||
+      !coli_cuda_check(cudaMemcpy(t->s_src, bscale, t->s_src_bytes, cudaMemcpyHostToDevice), "scale upload")) {
+    coli_cuda_tensor_free(t);
+    return 0;
+  }
+  t->fmt = COLI_FMT_MXFP4;
+  t->gscale_src = gscale;
+  ctx->tensor_bytes += t->s_src_bytes;
+  *tensor = t;
+  return 1;
+}
+
 extern "C" int coli_b200_tensor_from_device(ColiCudaTensor **tensor, int fmt, const void *d_q, const void *d_s,
                                             float gscale, int I, int O, int device) {
+  if (fmt == COLI_FMT_MXFP4) {
+    coli_set_error("tensor_from_device: MXFP4 is transcoded on the host; use coli_cuda_tensor_wrap_mxfp4");
+    return 0;
+  }
   if (!tensor || !d_q || !d_s || I < 1 || O < 1 || !fmt_supported(fmt)) {
     coli_set_error("tensor_from_device: bad argument");
     return 0;
@@ -276,7 +413,15 @@ extern "C" int coli_b200_tensor_export(const ColiCudaTensor *t, void *q_host, vo
   void *dq = nullptr, *ds = nullptr;
   int ok = coli_cuda_check(cudaMalloc(&dq, qb), "staging allocation") && coli_cuda_check(cudaMalloc(&ds, sb), "staging allocation");
   if (ok) {
-    if (t->fmt == COLI_FMT_NVFP4)
+    if (t->fmt == COLI_FMT_MXFP4) {
+      // nibbles from the resident form, block scales as they were uploaded
+      void *d16 = nullptr;
+      ok = coli_cuda_check(cudaMalloc(&d16, src_s_bytes(COLI_FMT_NVFP4, t->I, t->O)), "staging allocation") &&
+           colib::unpack_nvfp4(t, (uint8_t *)dq, (uint8_t *)d16, ctx->stream) &&
+           coli_cuda_check(cudaMemcpyAsync(ds, t->s_src, sb, cudaMemcpyDeviceToDevice, ctx->stream), "scale copy") &&
+           coli_cuda_check(cudaStreamSynchronize(ctx->stream), "tensor export sync");
+      if (d16) cudaFree(d16);
+    } else if (t->fmt == COLI_FMT_NVFP4)
       ok = colib::unpack_nvfp4(t, (uint8_t *)dq, (uint8_t *)ds, ctx->stream);
     else
       ok = colib::unpack_fp8(t, (uint8_t *)dq, ctx->stream) &&
@@ -287,7 +432,7 @@ extern "C" int coli_b200_tensor_export(const ColiCudaTensor *t, void *q_host, vo
        coli_cuda_check(cudaStreamSynchronize(ctx->stream), "tensor export sync");
   if (dq) cudaFree(dq);
   if (ds) cudaFree(ds);
-  if (ok && gscale) *gscale = t->gscale;
+  if (ok && gscale) *gscale = t->fmt == COLI_FMT_MXFP4 ? t->gscale_src : t->gscale;
   return ok;
 }
 extern "C" void coli_cuda_tensor_free(ColiCudaTensor *t) {
@@ -296,13 +441,14 @@ extern "C" void coli_cuda_tensor_free(ColiCudaTensor *t) {
     if (g_ctx[i] && g_ctx[i]->device == t->device) {
       cudaSetDevice(t->device);
       g_ctx[i]->tensor_count--;
-      g_ctx[i]->tensor_bytes -= t->q_bytes + t->s_bytes;
+      g_ctx[i]->tensor_bytes -= t->q_bytes + t->s_bytes + t->s_src_bytes;
     }
   if (t->q) cudaFree(t->q);
   if (t->s) cudaFree(t->s);
+  if (t->s_src) cudaFree(t->s_src);
   free(t);
 }
-extern "C" size_t coli_cuda_tensor_bytes(const ColiCudaTensor *t) { return t ? t->q_bytes + t->s_bytes : 0; }
+extern "C" size_t coli_cuda_tensor_bytes(const ColiCudaTensor *t) { return t ? t->q_bytes + t->s_bytes + t->s_src_bytes : 0; }
 extern "C" int coli_cuda_tensor_device(const ColiCudaTensor *t) { return t ? t->device : -1; }
 
 extern "C" int coli_b200_quantize_nvfp4(int device, const float *d_w, int O, int I, void *d_nibbles, void *d_bscale,
@@ -440,6 +586,12 @@ extern "C" int coli_b200_moe_create(ColiMoe **out, const ColiMoeLayer *L, int ma
     coli_set_error("moe_create: n_group=%d must divide E=%d and be <= 32", L->n_group, L->E);
     return 0;
   }
+  if (L->n_group > 1 && L->k > (L->topk_group < L->n_group ? L->topk_group : L->n_group) * (L->E / L->n_group)) {
+    // the kept groups hold fewer than k experts: the scan would run out of candidates and repeat expert 0
+    coli_set_error("moe_create: k=%d exceeds the %d experts of the %d groups a token may use", L->k,
+                   (L->topk_group < L->n_group ? L->topk_group : L->n_group) * (L->E / L->n_group), L->topk_group);
+    return 0;
+  }
   if (!fmt_supported(L->fmt) || !L->router_w || !L->gate || !L->up || !L->down) {
     coli_set_error("moe_create: missing router/expert tables or unsupported format %d", L->fmt);
     return 0;
@@ -548,7 +700,7 @@ extern "C" int coli_b200_moe_create(ColiMoe **out, const ColiMoeLayer *L, int ma
   ok = ok && ws_alloc(m, &m->status, 1) && coli_cuda_check(cudaMemset(m->status, 0, sizeof(int)), "status clear");
   m->ticket = nullptr;
   ok = ok && ws_alloc(m, &m->ticket, 1) && coli_cuda_check(cudaMemset(m->ticket, 0, sizeof(unsigned int)), "ticket clear");
-  if (ok && use_tc_path(L->fmt, (int)rows, m->nseg)) ok = ws_alloc(m, &m->xg, rows * H);
+  if (ok && use_tc_path(coli_kernel_fmt(L->fmt), (int)rows, m->nseg)) ok = ws_alloc(m, &m->xg, rows * H);
   m->select_bias = nullptr;
   m->logit_bias = nullptr;
   if (ok && L->select_bias) ok = ws_alloc(m, &m->select_bias, E);
@@ -569,6 +721,8 @@ extern "C" int coli_b200_moe_create(ColiMoe **out, const ColiMoeLayer *L, int ma
   if (ok && L->logit_bias)
     ok = coli_cuda_check(cudaMemcpyAsync(m->logit_bias, L->logit_bias, sizeof(float) * E, cudaMemcpyHostToDevice, st), "bias upload");
   ok = ok && coli_cuda_check(cudaStreamSynchronize(st), "moe_create sync");
+  // from here on the handle's format is the one its kernels decode (MXFP4 is resident in the NVFP4 form)
+  m->L.fmt = coli_kernel_fmt(L->fmt);
   // the handle keeps no host pointers
   m->L.router_w = nullptr;
   m->L.select_bias = nullptr;
@@ -1045,9 +1199,28 @@ extern "C" uint64_t coli_b200_sharding_fingerprint(uint32_t num_nodes, uint32_t 
 
 // ---- the reference's host-pointer expert calls -------------------------------------------------------
 // Same contract as backend_cuda.cu:3668-3806 / 4410-4792 (host f32 in, host f32 out, synchronous,
-// one mutex per device held across the call).  Activations are rounded to bf16 on the device
-// (the kernels are W4A16 / W8A16 with bf16 activation values, held in f16 for the MMA); outputs
-// are written as f32.
+// one mutex per device held across the call).  Activations are rounded from f32 to f16 on the device
+// (the kernels are W4A16 / W8A16, as the reference's GPU path is); outputs are written as f32.
+// Kernel selection follows the row counts alone, as the reference's does (backend_cuda.cu:4738-4783
+// switches kernels at 32 rows): from 8 rows per expert on average the group runs on the tcgen05
+// kernels, whose y is rounded to bf16 before it is widened to f32; below that on the
+// register-level kernel, which writes f32 directly.
+namespace {
+std::mutex g_group_stats_mu;  // backend_cuda.cu:98-100
+uint64_t g_group_calls = 0, g_group_experts = 0, g_group_rows = 0;
+double g_group_h2d_ms = 0.0, g_group_kernel_ms = 0.0, g_group_d2h_ms = 0.0;
+}  // namespace
+extern "C" void coli_cuda_group_stats(uint64_t *calls, uint64_t *experts, uint64_t *rows, double *h2d_ms, double *kernel_ms,
+                                      double *d2h_ms) {
+  std::lock_guard<std::mutex> lk(g_group_stats_mu);
+  if (calls) *calls = g_group_calls;
+  if (experts) *experts = g_group_experts;
+  if (rows) *rows = g_group_rows;
+  if (h2d_ms) *h2d_ms = g_group_h2d_ms;
+  if (kernel_ms) *kernel_ms = g_group_kernel_ms;
+  if (d2h_ms) *d2h_ms = g_group_d2h_ms;
+}
+
 static int run_host_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups, ColiCudaTensor *const *downs,
                           const int *rows, int count, float *y, const float *x, int want_fmt_a, int want_fmt_b,
                           const char *who) {
@@ -1071,19 +1244,29 @@ static int run_host_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *u
     coli_set_error("%s: D=%d and I=%d must be multiples of 8", who, D, I);
     return 0;
   }
+  if (total > (1L << 24)) {
+    coli_set_error("%s: %ld rows in one call", who, total);
+    return 0;
+  }
   DeviceContext *ctx = find_ctx(device);
   if (!select_ctx(ctx)) return 0;
   std::lock_guard<std::mutex> lk(ctx->mu);
   cudaStream_t st = ctx->stream;
+  const int kfmt = coli_kernel_fmt(fmt);
+  const bool tc = use_tc_path(kfmt, (int)total, count);
+  const bool tct = tc && use_tct(kfmt, (int)total, count);
   const int avg = (int)((total + count - 1) / count);
-  const int rpi = avg <= 8 ? 8 : avg <= 16 ? 16 : 32;
+  const int rpi = tc ? (tct ? tct_tile_tokens((int)total, count) : colib::TC_MAX_TOKENS) : (avg <= 8 ? 8 : avg <= 16 ? 16 : 32);
   const int max_items = max_work_items((int)total, count, rpi);
   const size_t xb = (size_t)total * D;
-  // slots: 0 x f32 / y f32, 1 x f16, 2 h f16, 3 tables + counts + work list
-  const size_t tbl_bytes = sizeof(WeightRef) * 3 * count + sizeof(int32_t) * (2 * count + 2 + 3 * (size_t)max_items + 1);
+  // slots: 0 x f32 / y f32, 1 x f16, 2 h f16, 3 tables + counts + work list + status word, 4 y bf16 (tcgen05 path)
+  const size_t tbl_bytes = sizeof(WeightRef) * 3 * count + sizeof(int32_t) * (2 * count + 2 + 3 * (size_t)max_items + 2);
   if (!reserve(ctx, 0, xb * sizeof(float)) || !reserve(ctx, 1, xb * sizeof(__half)) ||
-      !reserve(ctx, 2, (size_t)total * I * sizeof(__half)) || !reserve(ctx, 3, tbl_bytes))
+      !reserve(ctx, 2, (size_t)total * I * sizeof(__half)) || !reserve(ctx, 3, tbl_bytes) ||
+      (tc && !reserve(ctx, 4, xb * sizeof(__nv_bfloat16))))
     return 0;
+  if (!ctx->ev[0])
+    for (int i = 0; i < 4; ++i) CK(cudaEventCreate(&ctx->ev[i]), "event creation");
   std::vector<WeightRef> tbl(3 * (size_t)count);
   for (int c = 0; c < count; ++c) {
     tbl[c] = WeightRef{gates[c]->q, gates[c]->s, gates[c]->gscale, 0};
@@ -1097,37 +1280,85 @@ static int run_host_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *u
   int32_t *d_irow = d_iseg + max_items;
   int32_t *d_inr = d_irow + max_items;
   int32_t *d_nit = d_inr + max_items;
+  int32_t *d_status = d_nit + 1;
+  CK(cudaEventRecord(ctx->ev[0], st), "phase event");
   CK(cudaMemcpyAsync(ctx->buf[0], x, xb * sizeof(float), cudaMemcpyHostToDevice, st), "expert input upload");
   CK(cudaMemcpyAsync(d_tbl, tbl.data(), sizeof(WeightRef) * tbl.size(), cudaMemcpyHostToDevice, st), "expert table upload");
   CK(cudaMemcpyAsync(d_cnt, rows, sizeof(int32_t) * count, cudaMemcpyHostToDevice, st), "row count upload");
+  CK(cudaMemsetAsync(d_status, 0, sizeof(int32_t), st), "status clear");
+  CK(cudaEventRecord(ctx->ev[1], st), "phase event");
   CK(cudaStreamSynchronize(st), "expert upload sync");  // tbl is a local; rows/x belong to the caller
-  if (!colib::launch_f32_to_f16_via_bf16((const float *)ctx->buf[0], (__half *)ctx->buf[1], xb, st)) return 0;
+  if (!colib::launch_f32_to_f16((const float *)ctx->buf[0], (__half *)ctx->buf[1], xb, st)) return 0;
   if (!colib::launch_items_from_counts(d_cnt, count, rpi, d_off, d_iseg, d_irow, d_inr, d_nit, st)) return 0;
-  colib::FfnParams fp;
-  fp.fmt = fmt;
-  fp.H = D;
-  fp.I = I;
-  fp.gate = d_tbl;
-  fp.up = d_tbl + count;
-  fp.down = d_tbl + 2 * count;
-  fp.seg_expert = nullptr;
-  fp.item_seg = d_iseg;
-  fp.item_row0 = d_irow;
-  fp.item_nrows = d_inr;
-  fp.n_items = d_nit;
-  fp.max_items = max_items;
-  fp.rows_per_item = rpi;
-  fp.items_expected = max_items;
-  fp.x = (const __half *)ctx->buf[1];
-  fp.row_token = nullptr;
-  fp.h = (__half *)ctx->buf[2];
-  fp.y = nullptr;
-  fp.y32 = (float *)ctx->buf[0];  // x f32 is dead once converted
-  fp.relu2_out = nullptr;
-  fp.act = current_activation();
-  if (!colib::launch_ffn_small(fp, st)) return 0;
+  if (tc) {
+    colib::TcParams tp;
+    tp.fmt = kfmt;
+    tp.H = D;
+    tp.I = I;
+    tp.gate = d_tbl;
+    tp.up = d_tbl + count;
+    tp.down = d_tbl + 2 * count;
+    tp.seg_expert = nullptr;
+    tp.item_seg = d_iseg;
+    tp.item_row0 = d_irow;
+    tp.item_nrows = d_inr;
+    tp.n_items = d_nit;
+    tp.max_items = max_items;
+    tp.tile_tokens = rpi;
+    tp.h = (__half *)ctx->buf[2];
+    tp.y = (__nv_bfloat16 *)ctx->buf[4];
+    tp.status = d_status;
+    tp.act = current_activation();
+    const int sms = ctx->sm_count;
+    const int ok = tct ? colib::launch_gate_up_tct(tp, ctx->buf[1], (int)total, sms, st) && colib::launch_down_tct(tp, (int)total, sms, st)
+                       : colib::launch_gate_up_tc(tp, ctx->buf[1], (int)total, sms, st) && colib::launch_down_tc(tp, (int)total, sms, st);
+    if (!ok || !colib::launch_bf16_to_f32((const __nv_bfloat16 *)ctx->buf[4], (float *)ctx->buf[0], xb, st)) return 0;
+  } else {
+    colib::FfnParams fp;
+    fp.fmt = kfmt;
+    fp.H = D;
+    fp.I = I;
+    fp.gate = d_tbl;
+    fp.up = d_tbl + count;
+    fp.down = d_tbl + 2 * count;
+    fp.seg_expert = nullptr;
+    fp.item_seg = d_iseg;
+    fp.item_row0 = d_irow;
+    fp.item_nrows = d_inr;
+    fp.n_items = d_nit;
+    fp.max_items = max_items;
+    fp.rows_per_item = rpi;
+    fp.items_expected = max_items;
+    fp.x = (const __half *)ctx->buf[1];
+    fp.row_token = nullptr;
+    fp.h = (__half *)ctx->buf[2];
+    fp.y = nullptr;
+    fp.y32 = (float *)ctx->buf[0];  // x f32 is dead once converted
+    fp.relu2_out = nullptr;
+    fp.act = current_activation();
+    if (!colib::launch_ffn_small(fp, st)) return 0;
+  }
+  CK(cudaEventRecord(ctx->ev[2], st), "phase event");
+  int32_t kst = 0;
   CK(cudaMemcpyAsync(y, ctx->buf[0], xb * sizeof(float), cudaMemcpyDeviceToHost, st), "expert output download");
+  if (tc) CK(cudaMemcpyAsync(&kst, d_status, sizeof(int32_t), cudaMemcpyDeviceToHost, st), "status read");
+  CK(cudaEventRecord(ctx->ev[3], st), "phase event");
   CK(cudaStreamSynchronize(st), "expert call sync");
+  if (kst != 0) {
+    coli_set_error("%s: a tcgen05 expert kernel abandoned a bounded wait (code %d); the output is invalid", who, (int)kst);
+    return 0;
+  }
+  float ms[3] = {0.0f, 0.0f, 0.0f};
+  for (int i = 0; i < 3; ++i) cudaEventElapsedTime(&ms[i], ctx->ev[i], ctx->ev[i + 1]);
+  {
+    std::lock_guard<std::mutex> sl(g_group_stats_mu);
+    g_group_calls++;
+    g_group_experts += (uint64_t)count;
+    g_group_rows += (uint64_t)total;
+    g_group_h2d_ms += ms[0];
+    g_group_kernel_ms += ms[1];
+    g_group_d2h_ms += ms[2];
+  }
   return 1;
 }
 
@@ -1143,6 +1374,24 @@ extern "C" int coli_cuda_expert_mlp_nvfp4(ColiCudaTensor *gate, ColiCudaTensor *
 extern "C" int coli_cuda_expert_mlp_fp8(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down, float *y,
                                         const float *x, int S) {
   return run_host_group(&gate, &up, &down, &S, 1, y, x, COLI_FMT_E4M3_ROW, COLI_FMT_FP8_B128, "expert_mlp_fp8");
+}
+
+// MXFP4 experts (backend_cuda.h:71-79, backend_cuda.cu:5707): the same two launches; the handles
+// hold the weights in the NVFP4 resident form (see coli_cuda_tensor_wrap_mxfp4).
+extern "C" int coli_cuda_expert_mlp_mxfp4(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down, float *y,
+                                          const float *x, int S) {
+  return run_host_group(&gate, &up, &down, &S, 1, y, x, COLI_FMT_MXFP4, COLI_FMT_MXFP4, "expert_mlp_mxfp4");
+}
+extern "C" int coli_cuda_expert_group_mxfp4(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                                            ColiCudaTensor *const *downs, const int *rows, int count, float *y,
+                                            const float *x) {
+  return run_host_group(gates, ups, downs, rows, count, y, x, COLI_FMT_MXFP4, COLI_FMT_MXFP4, "expert_group_mxfp4");
+}
+extern "C" int coli_cuda_expert_mlp_mxfp4_situ(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down, float *y,
+                                               const float *x, int S, float beta, float linear_beta) {
+  (void)gate, (void)up, (void)down, (void)y, (void)x, (void)S, (void)beta, (void)linear_beta;
+  coli_set_error("expert_mlp_mxfp4_situ: the situ activation is not part of this library (declined)");
+  return 0;
 }
 
 // Gateless ReLU^2 experts (Nemotron-H): y = down(relu(up x)^2), moe.rs:1189-1199;
@@ -1199,7 +1448,7 @@ static int run_host_group_relu2(ColiCudaTensor *const *ups, ColiCudaTensor *cons
   CK(cudaMemcpyAsync(d_tbl, tbl.data(), sizeof(WeightRef) * tbl.size(), cudaMemcpyHostToDevice, st), "expert table upload");
   CK(cudaMemcpyAsync(d_cnt, rows, sizeof(int32_t) * count, cudaMemcpyHostToDevice, st), "row count upload");
   CK(cudaStreamSynchronize(st), "expert upload sync");  // tbl is a local; rows/x belong to the caller
-  if (!colib::launch_f32_to_f16_via_bf16((const float *)ctx->buf[0], (__half *)ctx->buf[1], xb, st)) return 0;
+  if (!colib::launch_f32_to_f16((const float *)ctx->buf[0], (__half *)ctx->buf[1], xb, st)) return 0;
   if (!colib::launch_items_from_counts(d_cnt, count, rpi, d_off, d_iseg, d_irow, d_inr, d_nit, st)) return 0;
   colib::FfnParams fp;
   fp.fmt = COLI_FMT_NVFP4;
@@ -1310,10 +1559,10 @@ static int run_host_matmul(ColiCudaTensor *w, float *y, const float *x, int S, c
   CK(cudaMemcpyAsync(d_tbl, &ref, sizeof(WeightRef), cudaMemcpyHostToDevice, st), "matmul table upload");
   CK(cudaMemcpyAsync(d_cnt, &S, sizeof(int32_t), cudaMemcpyHostToDevice, st), "matmul row count upload");
   CK(cudaStreamSynchronize(st), "matmul upload sync");  // ref and S are locals
-  if (!colib::launch_f32_to_f16_via_bf16((const float *)ctx->buf[0], (__half *)ctx->buf[1], xb, st)) return 0;
+  if (!colib::launch_f32_to_f16((const float *)ctx->buf[0], (__half *)ctx->buf[1], xb, st)) return 0;
   if (!colib::launch_items_from_counts(d_cnt, 1, rpi, d_off, d_iseg, d_irow, d_inr, d_nit, st)) return 0;
   colib::FfnParams fp;
-  fp.fmt = w->fmt;
+  fp.fmt = coli_kernel_fmt(w->fmt);
   fp.H = O;  // the kernel's "down" form contracts over its I and writes H features per row
   fp.I = I;
   fp.gate = fp.up = fp.down = d_tbl;

@@ -1,22 +1,24 @@
 // Weighted combine: out[t] = sum_kk w[t,kk] * y[slot[t,kk]] (kk ascending, f32) + shared[t],
 // rounded once to bf16 — crates/colibri-engine/src/moe.rs:1549-1553 (routed accumulate),
 // 1875-1885 (shared expert added after the routed sum).  A gather per output row instead of the
-// reference's scatter-add, so the f32 order is fixed and no atomics are needed.
+// reference's scatter-add, so the f32 order is fixed and no atomics are needed.  The order is a
+// token's own kk order; the reference adds expert by expert in the batch's first-appearance order
+// (moe.rs:1243-1267), so the two f32 sums agree to rounding (tolerance-level), not bit for bit.
 #include "internal.cuh"
 
 namespace colib {
 
 __global__ void __launch_bounds__(256) k_combine(CombineParams p, const __nv_bfloat16 *shared_y) {
   coli_grid_dependency_sync();
-  const int t = blockIdx.y;
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;  // 8-element column group
+  const int t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;  // 8-element column group
   if (c * 8 >= p.H) return;
   float acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
   // batches of 8 experts: all slots and weights, then all rows, are requested before the first
   // is used (a load-use loop would pay two memory round trips per expert); the sum itself runs
-  // in ascending kk as the reference's does
+  // in ascending kk
   for (int k0 = 0; k0 < p.k; k0 += 8) {
     float w[8];
     int row[8];
@@ -87,7 +89,7 @@ int launch_combine(const CombineParams &p, cudaStream_t st) {
     return 0;
   }
   const __nv_bfloat16 *shared_y = p.has_shared ? p.shared_y : nullptr;
-  dim3 grid((p.H / 8 + 255) / 256, p.T);
+  dim3 grid(p.T, (p.H / 8 + 255) / 256);
   coli_count_launch(1);
   return coli_cuda_check(launch_dependent(k_combine, grid, dim3(256), 0, st, p, shared_y), "combine launch") ? 1 : 0;
 }
@@ -175,16 +177,27 @@ int launch_f32_to_bf16(const float *src, __nv_bfloat16 *dst, size_t n, cudaStrea
   return coli_cuda_check(cudaGetLastError(), "f32->bf16 launch") ? 1 : 0;
 }
 
-__global__ void k_f32_to_f16_via_bf16(const float *src, __half *dst, size_t n) {
+__global__ void k_f32_to_f16(const float *src, __half *dst, size_t n) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
-    dst[i] = coli_f32_to_f16_via_bf16(src[i]);
+    dst[i] = __float2half_rn(fminf(fmaxf(src[i], -65504.0f), 65504.0f));
 }
-int launch_f32_to_f16_via_bf16(const float *src, __half *dst, size_t n, cudaStream_t st) {
+int launch_f32_to_f16(const float *src, __half *dst, size_t n, cudaStream_t st) {
   if (n == 0) return 1;
   const size_t blocks = (n + 255) / 256;
-  k_f32_to_f16_via_bf16<<<(unsigned)(blocks > 4736 ? 4736 : blocks), 256, 0, st>>>(src, dst, n);
+  k_f32_to_f16<<<(unsigned)(blocks > 4736 ? 4736 : blocks), 256, 0, st>>>(src, dst, n);
   coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "f32->f16 launch") ? 1 : 0;
+}
+__global__ void k_bf16_to_f32(const __nv_bfloat16 *src, float *dst, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    dst[i] = __bfloat162float(src[i]);
+}
+int launch_bf16_to_f32(const __nv_bfloat16 *src, float *dst, size_t n, cudaStream_t st) {
+  if (n == 0) return 1;
+  const size_t blocks = (n + 255) / 256;
+  k_bf16_to_f32<<<(unsigned)(blocks > 4736 ? 4736 : blocks), 256, 0, st>>>(src, dst, n);
+  coli_count_launch(1);
+  return coli_cuda_check(cudaGetLastError(), "bf16->f32 launch") ? 1 : 0;
 }
 // n must be a multiple of 8 (rows of H elements, H % 8 == 0)
 __global__ void k_bf16_to_f16(const uint4 *src, uint4 *dst, size_t n8) {

@@ -388,19 +388,23 @@ static int launch_one(const FfnParams &p, bool gated, cudaStream_t st) {
   } else {
     // two warps per CTA keep the per-SM share of tasks even; the grid covers what fits at once
     constexpr int W = 2;
-    static int resident[2] = {0, 0};  // CTAs per device, per kernel variant
-    if (resident[gated ? 1 : 0] == 0) {
-      int dev = 0, sms = 0, per_sm = 0;
-      if (!coli_cuda_check(cudaGetDevice(&dev), "device query") ||
-          !coli_cuda_check(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "device query"))
-        return 0;
+    // resident CTAs per kernel variant and device ordinal (an occupancy figure belongs to one device)
+    static int resident_tab[2][32];
+    int dev = 0;
+    if (!coli_cuda_check(cudaGetDevice(&dev), "device query")) return 0;
+    int uncached = 0;
+    int &resident_slot = (dev >= 0 && dev < 32) ? resident_tab[gated ? 1 : 0][dev] : uncached;
+    if (resident_slot == 0) {
+      int sms = 0, per_sm = 0;
+      if (!coli_cuda_check(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "device query")) return 0;
       const cudaError_t e = gated ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_ffn_mm<FMT, NB, true, false>, W * 32, 0)
                                   : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_ffn_mm<FMT, NB, false, false>, W * 32, 0);
       if (!coli_cuda_check(e, "occupancy query")) return 0;
-      resident[gated ? 1 : 0] = sms * (per_sm > 0 ? per_sm : 1);
+      resident_slot = sms * (per_sm > 0 ? per_sm : 1);
     }
+    const int resident_ctas = resident_slot;
     const long max_ctas = ((long)row_tiles * p.max_items + W - 1) / W;
-    const int grid = (int)(max_ctas < resident[gated ? 1 : 0] ? max_ctas : resident[gated ? 1 : 0]);
+    const int grid = (int)(max_ctas < resident_ctas ? max_ctas : resident_ctas);
     const cudaError_t e = gated ? launch_dependent(k_ffn_mm<FMT, NB, true, false>, dim3(grid), dim3(W * 32), 0, st, p)
                                 : launch_dependent(k_ffn_mm<FMT, NB, false, false>, dim3(grid), dim3(W * 32), 0, st, p);
     coli_count_launch(1);

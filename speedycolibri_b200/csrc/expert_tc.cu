@@ -327,13 +327,8 @@ static int launch_tc(const TcParams &p, const void *rows_base, int rows_cap, int
   constexpr int MATS = 2;
   constexpr int STAGES = 3;
   const size_t smem = (size_t)STAGES * (MATS * TC_A_BYTES + TC_B_BYTES) + 1024 /*align*/ + 8 * (3 * STAGES + 4) + 16 + 64;
-  static bool attr_done = false;
-  if (!attr_done) {
-    if (!coli_cuda_check(cudaFuncSetAttribute(k_ffn_tc<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                         "tcgen05 kernel shared-memory attribute"))
-      return 0;
-    attr_done = true;
-  }
+  static ColiPerDeviceOnce attr_once;
+  if (!coli_set_smem_limit(attr_once, k_ffn_tc<GATED>, smem, "tcgen05 kernel shared-memory attribute")) return 0;
   CUtensorMap map;
   if (!make_rows_map(&map, rows_base, rows_cap, GATED ? p.H : p.I)) return 0;
   const int FT = GATED ? TC_BM : 2 * TC_BM;

@@ -445,7 +445,10 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
         if (FMT == COLI_FMT_FP8_B128 && grow < Op) {
           const int KT = KB >> 1;
           srow = reinterpret_cast<const float *>(wr.s) + (size_t)(grow >> 7) * KT;
-          norm = TT_FP8_HEADROOM / tt_block_scale_max(srow, KT);
+          // a row block whose scales are all zero (an all-zero or padded weight block: the encoder
+          // writes scale = amax / 448 = 0) decodes to zeros, as code x 0 does in convert.rs:731-741
+          const float mx = tt_block_scale_max(srow, KT);
+          norm = mx > 0.0f ? TT_FP8_HEADROOM / mx : 0.0f;
         }
         TtPacked8 pa = tt_zero_packed8(), pb = pa;
         if (kb0 < KB) pa = tt_load_packed8<FMT>(wr, Op, grow, kb0, srow, norm);
@@ -471,13 +474,8 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
 template <bool GATED, int FMT, int ACC>
 static int launch_tct(const TcParams &p, const void *rows_base, int rows_cap, int sm_count, cudaStream_t st) {
   const size_t smem = (size_t)TtBudget<ACC>::B_STAGES * TtBudget<ACC>::B_BYTES + 1024 /*align*/ + 8 * TtBudget<ACC>::NBARS + 16 + 64;
-  static bool attr_done = false;
-  if (!attr_done) {
-    if (!coli_cuda_check(cudaFuncSetAttribute(k_ffn_tct<GATED, FMT, ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                         "tcgen05 kernel shared-memory attribute"))
-      return 0;
-    attr_done = true;
-  }
+  static ColiPerDeviceOnce attr_once;
+  if (!coli_set_smem_limit(attr_once, k_ffn_tct<GATED, FMT, ACC>, smem, "tcgen05 kernel shared-memory attribute")) return 0;
   CUtensorMap map;
   if (!make_rows_map(&map, rows_base, rows_cap, GATED ? p.H : p.I)) return 0;
   const int FT = GATED ? TC_BM : 2 * TC_BM;

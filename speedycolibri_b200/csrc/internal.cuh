@@ -20,6 +20,11 @@
 //   FP8_B128  q: [KT][Op][128 B]  e4m3 codes, k ascending
 //             s: f32 [ceil(O/128)][KT]   (the reference's own grid, convert.rs:731-741)
 //   E4M3_ROW  q as FP8_B128; s: f32 [O] row scales (linear.rs:93-109)
+//   MXFP4     held in the NVFP4 form above: at upload each E8M0 scale 2^e of a 32-wide block is
+//             re-expressed as the ue4m3 code of 2^(e + shift) for both of its 16-wide halves, with
+//             one shift per tensor folded into the tensor scale (gscale x 2^-shift), so every
+//             expert kernel reads it unchanged; `s_src` keeps the container's own scale bytes for
+//             the export call.  The handle's fmt stays 6; kernels are given coli_kernel_fmt(fmt).
 // Op = O rounded up to 16, Kp = I rounded up to 128; padding bytes are zero (decode to 0.0).
 //
 // Arithmetic type of the expert GEMMs: f16 x f16 -> f32.  FP4/FP8 codes convert to f16 with one
@@ -34,7 +39,12 @@ struct ColiCudaTensor {
   uint8_t *s;
   float gscale;
   size_t q_bytes, s_bytes;
+  uint8_t *s_src;       // MXFP4 only: the E8M0 block scales as uploaded, [O, ceil(I/32)]
+  size_t s_src_bytes;
+  float gscale_src;     // MXFP4 only: the tensor scale as uploaded (gscale above carries the shift)
 };
+// the format the expert kernels decode for a handle of format `fmt`
+static inline int coli_kernel_fmt(int fmt) { return fmt == COLI_FMT_MXFP4 ? COLI_FMT_NVFP4 : fmt; }
 
 // What a kernel needs to read one matrix.
 struct WeightRef {
@@ -60,6 +70,35 @@ bool coli_cuda_check(cudaError_t e, const char *what);
 
 // every kernel launch of the library bumps this (read through coli_b200_launch_count)
 void coli_count_launch(int n);
+
+// A "done once" flag per CUDA device.  Function attributes (cudaFuncSetAttribute) and occupancy
+// figures belong to one device's copy of a kernel, and one process may drive several devices
+// (coli_cuda_init takes a list), so a launcher that has to raise a kernel's shared-memory limit
+// keeps one of these per kernel instead of a process-wide bool.  The guarded action must be
+// idempotent: two host threads may both see "not done" for the same device.
+struct ColiPerDeviceOnce {
+  unsigned done_mask = 0;  // bit d = done on device ordinal d (ordinals >= 32 are never cached)
+  // the current device's ordinal, or -1; `done` tells whether the action already ran there
+  int current(bool *done) const {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) dev = -1;
+    *done = dev >= 0 && dev < 32 && ((__atomic_load_n(&done_mask, __ATOMIC_ACQUIRE) >> dev) & 1u);
+    return dev;
+  }
+  void mark(int dev) {
+    if (dev >= 0 && dev < 32) __atomic_fetch_or(&done_mask, 1u << dev, __ATOMIC_RELEASE);
+  }
+};
+// Raise a kernel's dynamic shared-memory limit on the current device, once per device.
+template <class K>
+static inline bool coli_set_smem_limit(ColiPerDeviceOnce &once, K kernel, size_t bytes, const char *what) {
+  bool done = false;
+  const int dev = once.current(&done);
+  if (done) return true;
+  if (!coli_cuda_check(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes), what)) return false;
+  once.mark(dev);
+  return true;
+}
 
 // ---- launchers (defined in the kernel translation units) ------------------------------------
 namespace colib {
@@ -196,9 +235,11 @@ int launch_f32_to_bf16(const float *src, __nv_bfloat16 *dst, size_t n, cudaStrea
 // out[t] = bf16(x[t] * r_t * w), r_t = 1 / sqrt(mean(x[t]^2) + eps) with the mean square accumulated
 // in f64 (math.rs:8-20); H must be a multiple of 4
 int launch_rmsnorm_bf16(const float *x, const float *w, float eps, __nv_bfloat16 *out, int T, int H, cudaStream_t st);
-// activations for the expert GEMMs: the bf16 value (rounding f32 to bf16 first), held in f16
+// activations for the expert GEMMs: the block's bf16 values held in f16; the host-f32 calls of the
+// reference's API round f32 to f16 directly (nearest even, saturating), as the reference's GPU path does
 int launch_bf16_to_f16(const __nv_bfloat16 *src, __half *dst, size_t n, cudaStream_t st);
-int launch_f32_to_f16_via_bf16(const float *src, __half *dst, size_t n, cudaStream_t st);
+int launch_f32_to_f16(const float *src, __half *dst, size_t n, cudaStream_t st);
+int launch_bf16_to_f32(const __nv_bfloat16 *src, float *dst, size_t n, cudaStream_t st);
 // y[S,O] = x[S,I] @ W[O,I]^T, all f32, one thread per output, multiply then add per k in order
 // (crates/colibri-engine/src/linear.rs:199-220).
 int launch_matmul_f32_seq(const float *x, const float *w, float *y, int S, int I, int O, cudaStream_t st);

@@ -408,13 +408,8 @@ __global__ void __launch_bounds__(128) k_route_topk(RouteParams p) {
 template <int BM, int NT>
 static bool launch_router_big(const RouteParams &p, dim3 grid, cudaStream_t st) {
   constexpr size_t smem = (size_t)2 * 32 * ((BM + 4) + (64 + 4)) * sizeof(float);
-  static bool attr_set = false;
-  if (!attr_set && smem > 48 * 1024) {
-    if (!coli_cuda_check(cudaFuncSetAttribute(k_router_gemm_big<BM, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                         "router shared-memory attribute"))
-      return false;
-    attr_set = true;
-  }
+  static ColiPerDeviceOnce attr_once;
+  if (smem > 48 * 1024 && !coli_set_smem_limit(attr_once, k_router_gemm_big<BM, NT>, smem, "router shared-memory attribute")) return false;
   k_router_gemm_big<BM, NT><<<grid, NT, smem, st>>>(p);
   return true;
 }
@@ -429,13 +424,14 @@ int launch_router(const RouteParams &p, cudaStream_t st) {
     coli_set_error("router: unsupported k=%d / n_group=%d for E=%d", p.k, p.n_group, p.E);
     return 0;
   }
+  if (p.n_group > 1 && p.k > min(p.topk_group, p.n_group) * (p.E / p.n_group)) {
+    coli_set_error("router: k=%d exceeds the experts of the %d groups a token may use", p.k, p.topk_group);
+    return 0;
+  }
   const size_t dec_smem = (size_t)(p.T + 8) * (p.H + 8) * sizeof(__nv_bfloat16);
   if (p.T <= 8 && p.H % 8 == 0 && dec_smem <= 200 * 1024) {
-    static bool attr_set = false;
-    if (!attr_set) {
-      cudaFuncSetAttribute(k_router_decode, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-      attr_set = true;
-    }
+    static ColiPerDeviceOnce attr_once;
+    if (!coli_set_smem_limit(attr_once, k_router_decode, 200 * 1024, "decode router shared-memory attribute")) return 0;
     k_router_decode<<<(p.E + 7) / 8, 256, dec_smem, st>>>(p);  // 256 threads stage the rows, T*8 of them walk the chains
     coli_count_launch(1);
   } else {
@@ -473,8 +469,11 @@ int launch_router(const RouteParams &p, cudaStream_t st) {
 // Permutation into expert-contiguous segments.  Stable: rows of one expert keep ascending
 // token order (moe.rs:1373-1387), positions are a pure function of the routing.
 //   1. k_seg_count : one warp per chunk of 32 tokens walks its tokens in order; lane kk bumps
-//                    a shared-memory counter of expert idx[t][kk] (a token's experts are
-//                    distinct, so no two lanes touch one counter) and records the rank.
+//                    a shared-memory counter of expert idx[t][kk] and records the rank.  A
+//                    token's experts are distinct except in the degenerate case the reference's
+//                    scan also has (a row of NaN logits selects expert 0 k times); lanes that
+//                    hold the same expert are ranked among themselves so that every pair still
+//                    gets a row of its own.  An id outside [0, E) gets no row (slot -1).
 //   2. k_seg_scan  : per expert an exclusive running sum over chunks; exclusive scan over the
 //                    segment order; builds the work list (segments cut into row_per_item runs).
 //   3. k_permute   : row position = segment offset + chunk prefix + rank; copies the token row.
@@ -489,10 +488,16 @@ __global__ void __launch_bounds__(128) k_seg_count(PermuteParams p, int nchunk) 
   if (chunk >= nchunk) return;
   const int t0 = chunk * 32, t1 = min(p.T, t0 + 32);
   for (int t = t0; t < t1; ++t) {
-    if (lane < p.k) {
-      const int e = p.topk_idx[(size_t)t * p.k + lane];
-      p.local_rank[(size_t)t * p.k + lane] = cnt[e];
-      cnt[e] += 1;
+    int e = -1;
+    if (lane < p.k) e = p.topk_idx[(size_t)t * p.k + lane];
+    const bool valid = e >= 0 && e < p.E;
+    const unsigned same = __match_any_sync(0xffffffffu, valid ? e : -1 - lane);  // invalid lanes match nobody
+    int base = 0;
+    if (valid) base = cnt[e];
+    __syncwarp();
+    if (valid) {
+      p.local_rank[(size_t)t * p.k + lane] = base + __popc(same & ((1u << lane) - 1u));
+      if ((same & ((1u << lane) - 1u)) == 0) cnt[e] = base + __popc(same);  // lowest lane of the group
     }
     __syncwarp();
   }
@@ -602,8 +607,8 @@ __global__ void __launch_bounds__(256) k_permute(PermuteParams p) {
   if (warp < nrouted) {
     t = warp / p.k;
     const int e = p.topk_idx[warp];
-    const int s = p.expert_slot ? p.expert_slot[e] : e;
-    if (s < 0) {  // not resident here: no row, the combine skips negative slots
+    const int s = (e < 0 || e >= p.E) ? -1 : (p.expert_slot ? p.expert_slot[e] : e);
+    if (s < 0) {  // not resident here (or not an expert id): no row, the combine skips negative slots
       if (lane == 0) p.slot[warp] = -1;
       return;
     }
@@ -640,17 +645,20 @@ __device__ __forceinline__ void permute_small_body(const PermuteParams &p, int m
   // segment of every pair, fetched with independent loads before the ordered walk below
   for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
     const int e = p.topk_idx[i];
-    idx_sm[i] = p.expert_slot ? p.expert_slot[e] : e;
+    idx_sm[i] = (e < 0 || e >= E) ? -1 : (p.expert_slot ? p.expert_slot[e] : e);
   }
   __syncthreads();
   if (threadIdx.x < 32) {  // one warp walks the tokens in order; lane kk owns pair (t, kk)
-    for (int t = 0; t < p.T; ++t) {
-      if ((int)threadIdx.x < p.k) {
-        const int s = idx_sm[t * p.k + threadIdx.x];
-        if (s >= 0) {
-          rank_sm[t * p.k + threadIdx.x] = cnt[s];
-          cnt[s] += 1;
-        }
+    const int ln = (int)threadIdx.x;
+    for (int t = 0; t < p.T; ++t) {  // lanes holding the same segment (a degenerate routing) rank among themselves
+      const int s = ln < p.k ? idx_sm[t * p.k + ln] : -1;
+      const unsigned same = __match_any_sync(0xffffffffu, s >= 0 ? s : -1 - ln);
+      int base = 0;
+      if (s >= 0) base = cnt[s];
+      __syncwarp();
+      if (s >= 0) {
+        rank_sm[t * p.k + ln] = base + __popc(same & ((1u << ln) - 1u));
+        if ((same & ((1u << ln) - 1u)) == 0) cnt[s] = base + __popc(same);
       }
       __syncwarp();
     }
@@ -753,13 +761,8 @@ int launch_decode_front(const RouteParams &rp, const PermuteParams &pp, unsigned
   if (!(rp.T >= 1 && rp.T <= 8 && rp.H % 8 == 0 && smem <= 180 * 1024 && rp.E <= 32 * kMaxSlots && rp.k <= 32 &&
         rp.n_group <= 32 && (rp.n_group <= 1 || rp.E % rp.n_group == 0) && permute_small_ok(pp) && ticket != nullptr))
     return -1;  // not applicable: the caller runs the separate stages
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (!coli_cuda_check(cudaFuncSetAttribute(k_decode_front, cudaFuncAttributeMaxDynamicSharedMemorySize, 180 * 1024),
-                         "decode front shared-memory attribute"))
-      return 0;
-    attr_set = true;
-  }
+  static ColiPerDeviceOnce attr_once;
+  if (!coli_set_smem_limit(attr_once, k_decode_front, 180 * 1024, "decode front shared-memory attribute")) return 0;
   coli_count_launch(1);
   return coli_cuda_check(launch_dependent(k_decode_front, dim3((rp.E + 7) / 8), dim3(256), smem, st, rp, pp, permute_max_items(pp), ticket),
                          "decode front launch")
@@ -844,8 +847,10 @@ int launch_items_from_counts(const int32_t *seg_count, int nseg, int rows_per_it
 // ---------------------------------------------------------------------------------------------
 static __device__ __align__(256) float g_route_scratch[COLI_ROUTE_NOALLOC_MAX_LOGITS];
 
-static float *g_route_scratch_addr[COLI_CUDA_MAX_DEVICES];  // per device, filled on first use
-static bool g_route_scratch_ready[COLI_CUDA_MAX_DEVICES];
+// Device address of the array per device ordinal, null until the first call on that device has
+// looked it up.  Several host threads may make that first call at once: the address is published
+// with release/acquire ordering, and two threads that both look it up store the same value.
+static float *g_route_scratch_addr[COLI_CUDA_MAX_DEVICES];
 
 extern "C" int coli_b200_route_noalloc(const void *x_dev, const void *router_w_dev, const float *select_bias_dev,
                                        const float *logit_bias_dev, int T, int H, int E, int k, int score,
@@ -870,7 +875,8 @@ extern "C" int coli_b200_route_noalloc(const void *x_dev, const void *router_w_d
     coli_set_error("route_noalloc: device ordinal %d out of range", dev);
     return 0;
   }
-  if (!g_route_scratch_ready[dev]) {
+  float *scratch = __atomic_load_n(&g_route_scratch_addr[dev], __ATOMIC_ACQUIRE);
+  if (!scratch) {
     // set-up, once per device, with that device current: resolve the symbol to its device address
     float *ptr = nullptr;
     if (!coli_cuda_check(cudaGetSymbolAddress((void **)&ptr, g_route_scratch), "route_noalloc: cudaGetSymbolAddress")) return 0;
@@ -878,10 +884,14 @@ extern "C" int coli_b200_route_noalloc(const void *x_dev, const void *router_w_d
       coli_set_error("route_noalloc: scratch symbol resolved to a null address");
       return 0;
     }
-    g_route_scratch_addr[dev] = ptr;
-    g_route_scratch_ready[dev] = true;
+    __atomic_store_n(&g_route_scratch_addr[dev], ptr, __ATOMIC_RELEASE);
+    scratch = ptr;
   }
   if (T == 0) return 1;
+  if (H % 8 == 0 && ((reinterpret_cast<uintptr_t>(x_dev) | reinterpret_cast<uintptr_t>(router_w_dev)) & 15)) {
+    coli_set_error("route_noalloc: x_dev and router_w_dev must be 16-byte aligned (the router reads them with 128-bit loads)");
+    return 0;
+  }
   colib::RouteParams p;
   p.T = T;
   p.H = H;
@@ -896,7 +906,7 @@ extern "C" int coli_b200_route_noalloc(const void *x_dev, const void *router_w_d
   p.router_w = (const __nv_bfloat16 *)router_w_dev;
   p.select_bias = select_bias_dev;
   p.logit_bias = logit_bias_dev;
-  p.logits = g_route_scratch_addr[dev];  // every logit of [T,E] is written before it is read: nothing to clear
+  p.logits = scratch;  // every logit of [T,E] is written before it is read: nothing to clear
   p.topk_idx = topk_idx_dev;
   p.topk_w = topk_w_dev;
   return colib::launch_router(p, (cudaStream_t)stream);

@@ -12,7 +12,7 @@ from typing import Optional, Sequence
 
 import numpy as np
 
-from .configs import FMT_NVFP4, MoeShape
+from .configs import FMT_MXFP4, FMT_NVFP4, MoeShape
 
 BASE_SEED = 20261125
 WEIGHT_STD = 0.02
@@ -132,3 +132,29 @@ def device_layer(shape: MoeShape, device: int = 0, local_experts: Optional[Seque
     shared = device_expert(shape, shape.E, device) if shape.shared else None
     return Layer(router=device_router_bits(shape, device), experts=experts, router_bias=select_bias(shape),
                  logit_bias=zipf_logit_bias(shape), shared=shared)
+
+
+def upload_packed_layer(shape: MoeShape, packed, device: int = 0, local=None):
+    """A ``Layer`` of resident handles from host arrays in the reference's container layout:
+    packed = dict(experts=[(gate, up, down) triples of (q, s, g)], shared=triple or None, router=bf16
+    bits, select_bias, logit_bias).  `local`: the expert ids this rank holds (default all)."""
+    from .backend import CudaTensor
+    from .moe import Expert, Layer
+
+    def up(ex):
+        out = []
+        for mi, which in enumerate(("gate", "up", "down")):
+            O, K = (shape.H, shape.I) if which == "down" else (shape.I, shape.H)
+            q, s, g = ex[mi]
+            if shape.fmt == FMT_NVFP4:
+                out.append(CudaTensor.wrap_nvfp4(q, s, g, K, O, device))
+            elif shape.fmt == FMT_MXFP4:
+                out.append(CudaTensor.wrap_mxfp4(q, s, g, K, O, device))
+            else:
+                out.append(CudaTensor.upload(q, s, shape.fmt, K, O, device))
+        return Expert(*out)
+
+    experts = [up(ex) if (local is None or e in local) else None for e, ex in enumerate(packed["experts"])]
+    shared = up(packed["shared"]) if packed["shared"] is not None else None
+    return Layer(router=packed["router"], experts=experts, router_bias=packed["select_bias"],
+                 logit_bias=packed["logit_bias"], shared=shared)

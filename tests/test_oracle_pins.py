@@ -358,3 +358,53 @@ def test_rmsnorm_gives_unit_rms_with_unit_weight(orc):
     rms = math.sqrt((out[0] * out[0] + out[1] * out[1]) / 2.0)
     assert abs(rms - 1.0) < 1e-5
     assert abs(out[1] / out[0] - 4.0 / 3.0) < 1e-5
+
+
+# ---- MXFP4 (fmt 6): E2M1 nibbles with one E8M0 power-of-two scale per 32 inputs ---------------
+# crates/colibri-core/src/dtype.rs:313-319  f8e8m0_known_values
+def test_e8m0_known_values(orc):
+    L = orc.lib()
+    assert L.orc_e8m0_to_f32(127) == 1.0
+    assert L.orc_e8m0_to_f32(128) == 2.0
+    assert L.orc_e8m0_to_f32(126) == 0.5
+    assert L.orc_e8m0_to_f32(0) == f32(2.0 ** -127)
+    assert L.orc_e8m0_to_f32(254) == f32(2.0 ** 127)
+    assert math.isnan(L.orc_e8m0_to_f32(255))  # dtype.rs:137-139
+
+
+# crates/colibri-engine/src/gpubench.rs:552-597  quantize_mxfp4_round_trips_through_the_production_decode
+def test_mxfp4_round_trips_through_the_decode(orc):
+    o, i = 32, 64  # two blocks of 32 per row
+    k = np.arange(o * i, dtype=np.float32)
+    w = np.sin(k * np.float32(0.017)).astype(np.float32)
+    w[1::2] *= np.float32(0.12)  # damped odd columns: a swapped nibble order becomes a large error
+    w = w.reshape(o, i)
+    nib, bs, g = orc.quantize_mxfp4(w)
+    assert nib.shape == (o, i // 2) and bs.shape == (o, i // 32) and g == 1.0
+    y = orc.matmul_qt(orc.FMT_MXFP4, nib, bs, g, np.eye(i, dtype=np.float32), o)  # y[k, r] = W[r, k]
+    rel = math.sqrt(float(((y.T.astype(np.float64) - w) ** 2).sum() / (w.astype(np.float64) ** 2).sum()))
+    assert rel < 0.25, rel  # the reference's bound: "quantized" lands near 0.1, "scrambled" near 1.0
+    # the encoder's rule (gpubench.rs:95-105): smallest power of two that brings the block max to <= 6
+    for r in (0, 7, 31):
+        for b in range(2):
+            bmax = float(np.abs(w[r, 32 * b:32 * b + 32]).max())
+            e = int(bs[r, b]) - 127
+            assert bmax / 2.0 ** e <= 6.0 < bmax / 2.0 ** (e - 1) + 1e-6
+
+
+def test_mxfp4_decode_is_code_times_power_of_two(orc):
+    """linear.rs:134-175 restated independently: W[o,k] = E2M1[nib] * 2^(bs[o, k/32] - 127) * g, low
+    nibble = even k; checked through the one-hot probe of linear.rs:449-485."""
+    rng = np.random.default_rng(5)
+    o, i = 5, 96
+    nib = rng.integers(0, 256, (o, i // 2), dtype=np.uint8)
+    bs = rng.integers(110, 140, (o, i // 32), dtype=np.uint8)
+    g = 0.75
+    W = orc.dequant(orc.FMT_MXFP4, nib, bs, g, o, i)
+    lut = np.array(E2M1 + [-v for v in E2M1], np.float32)
+    for r in range(o):
+        for k in range(i):
+            byte = int(nib[r, k >> 1])
+            code = (byte >> 4) if (k & 1) else (byte & 0x0F)
+            want = f32(f32(lut[code] * np.float32(2.0 ** (int(bs[r, k >> 5]) - 127))) * np.float32(g))
+            assert W[r, k] == want, (r, k, W[r, k], want)

@@ -32,7 +32,7 @@ def route_noalloc(lib, shape, x_dev, router_dev, sb_dev, lb_dev, T, stream=None)
 
 
 @pytest.mark.parametrize("name,T", [("tiny_sig", 37), ("tiny_zipf", 70), ("c1", 8)])
-def test_noalloc_routing_matches_handle_path_twice(gpu_backend, name, T):
+def test_noalloc_routing_matches_handle_path_twice(gpu_backend, orc, name, T):
     import torch
 
     from speedycolibri_b200 import _lib
@@ -42,8 +42,11 @@ def test_noalloc_routing_matches_handle_path_twice(gpu_backend, name, T):
     shape = CONFIGS[name].with_tokens(T)
     if name == "c1":  # device-generated weights; only the router matters here
         layer = synth.device_layer(shape.with_tokens(T))
+        L = orc.Layer(shape.H, shape.E, shape.k, shape.I, shape.score, shape.norm_topk, shape.routed_scale, shape.n_group,
+                      shape.topk_group, shape.fmt, layer.router, [None] * shape.E, None, layer.router_bias, layer.logit_bias)
     else:
-        layer = upload_layer(shape, host_layer(shape)[1])
+        L, packed = host_layer(shape)
+        layer = upload_layer(shape, packed)
     blk = MoeBlock(Config.from_shape(shape), layer, T)
     router_dev = torch.from_numpy(np.ascontiguousarray(layer.router).view(np.int16)).cuda()
     sb = torch.from_numpy(layer.router_bias).cuda() if layer.router_bias is not None else None
@@ -55,7 +58,37 @@ def test_noalloc_routing_matches_handle_path_twice(gpu_backend, name, T):
         idx, w = route_noalloc(lib, shape, xd, router_dev, sb, lb, T)
         assert np.array_equal(idx, want_idx), f"call {call}: indices differ"
         assert np.array_equal(w.view(np.uint32), want_w.view(np.uint32)), f"call {call}: weights differ"
+        # and against the CPU oracle, so that the check is not one CUDA path against another
+        o_idx, o_w = L.route_tokens(xh)
+        assert np.array_equal(idx, o_idx), f"call {call}: indices differ from the oracle"
+        assert np.array_equal(w.view(np.uint32), o_w.view(np.uint32)), f"call {call}: weights differ from the oracle"
     blk.close()
+
+
+def test_noalloc_at_the_exact_limit_on_a_side_stream(gpu_backend, orc):
+    """T*E == COLI_ROUTE_NOALLOC_MAX_LOGITS (E=512, T=256) fills the built-in scratch to its last
+    word; launched on a stream of its own and compared with the oracle's routing."""
+    import torch
+
+    from speedycolibri_b200 import _lib
+    from speedycolibri_b200.configs import MoeShape
+
+    lib = _lib.load()
+    shape = MoeShape("noalloc_limit", H=64, E=512, k=8, I=32, T=256, shared=False)
+    assert shape.T * shape.E == 131072
+    router = synth.host_router(shape)
+    xh = synth.host_tokens(shape)
+    L = orc.Layer(shape.H, shape.E, shape.k, shape.I, shape.score, shape.norm_topk, shape.routed_scale, shape.n_group,
+                  shape.topk_group, shape.fmt, router, [None] * shape.E, None, None, None)
+    want_idx, want_w = L.route_tokens(xh)
+    router_dev = torch.from_numpy(router.view(np.int16)).cuda()
+    xd = torch.from_numpy(xh.view(np.int16)).cuda()
+    side = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    for call in range(2):
+        idx, w = route_noalloc(lib, shape, xd, router_dev, None, None, shape.T, stream=side.cuda_stream)
+        assert np.array_equal(idx, want_idx), f"call {call}: indices differ from the oracle"
+        assert np.array_equal(w.view(np.uint32), want_w.view(np.uint32)), f"call {call}: weights differ from the oracle"
 
 
 def test_noalloc_rejects_oversize_and_bad_arguments(gpu_backend):
