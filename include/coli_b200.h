@@ -211,6 +211,8 @@ typedef struct ColiMoeLayer {
   ColiCudaTensor *sh_down;
   int32_t ep_rank, ep_world;   /* expert-parallel placement; 0/1 = single GPU */
   const int32_t *expert_owner; /* HOST [E] or NULL = contiguous e*world/E (sharding.rs:197-203) */
+  void *nccl_comm;             /* ncclComm_t over the ep_world ranks (this rank = ep_rank), or NULL; needed by
+                                  coli_b200_moe_block_ep_dev only.  Stays the caller's: the handle never destroys it. */
 } ColiMoeLayer;
 
 typedef struct ColiMoe ColiMoe; /* layer tables + workspace for up to max_tokens tokens */
@@ -275,6 +277,51 @@ int coli_b200_moe_combine_partial_dev(ColiMoe *moe, const void *y_rows_dev, cons
 /* out[t] = bf16(partial[t] + shared_y[t]) (shared_y_dev may be NULL) — moe.rs:1875-1885. */
 int coli_b200_moe_finish_dev(ColiMoe *moe, const float *partial_dev, const void *shared_y_dev, void *out_dev, int T,
                              void *stream);
+
+/* ---- expert-parallel block: one call per rank (replaces crates/colibri-engine/src/moe.rs:1737-1794
+ * `moe_sharded` and :1620-1734 `sharded_experts_partial`; the TCP request/response of
+ * crates/colibri-cluster/src/transport.rs:33-58 becomes an all-to-all over NCCL send/recv) -----------
+ * The handle is created with ep_rank / ep_world / expert_owner, the experts this rank owns, the
+ * shared expert (replicated) and nccl_comm; max_tokens bounds the tokens of ALL ranks in one call.
+ * Every rank calls with its own x_dev[T_local,H] (bf16; T_local may differ between ranks and may be
+ * 0) and receives out_dev[T_local,H].  Sequence: router + top-k of the own tokens; each token row is
+ * sent ONCE to every rank that owns at least one of its k experts (with the k expert ids); the
+ * owners run the grouped expert FFN over the rows they received and send the result row of every
+ * (token, kk) pair back unweighted; the home rank applies the routing weights in the token's own kk
+ * order and adds its shared expert, so the arithmetic is that of the single-GPU block.  The shared
+ * expert runs on a second stream beside the exchange.  The call blocks the host once, for the
+ * per-rank counts every send/recv needs (2 x world integers), and returns with the rest queued on
+ * `stream`; it must be made by every rank of the communicator, in the same order.  Limits: at most
+ * 8 ranks, k <= 16.  A rank that would receive more than max_tokens tokens fails the call on every
+ * rank alike. */
+int coli_b200_moe_block_ep_dev(ColiMoe *moe, const void *x_dev, void *out_dev, int T_local, void *stream);
+/* The same sequence for `world` handles of ONE process on ONE device (ranks[r] has ep_rank = r, no
+ * communicator): phases run rank after rank on `stream`, the exchanges are device-to-device copies.
+ * For checking the expert-parallel path on a single GPU; x_dev / out_dev / T_local have one entry
+ * per rank. */
+int coli_b200_moe_block_ep_emulate(ColiMoe *const *ranks, int world, const void *const *x_dev, void *const *out_dev,
+                                   const int *T_local, void *stream);
+/* For callers without a communicator of their own: rank 0 obtains a 128-byte id, passes it to the
+ * other ranks by any means, and every rank creates its end (ncclGetUniqueId / ncclCommInitRank of
+ * the NCCL library already in the process, else libnccl.so.2).  `device` must be initialised. */
+int coli_b200_nccl_unique_id(void *id128);
+int coli_b200_nccl_comm_create(void **comm, const void *id128, int rank, int world, int device);
+void coli_b200_nccl_comm_destroy(void *comm);
+/* Host-only (no GPU is touched): the layout rank `rank` derives from a count table [world][2*world]
+ * as returned by coli_b200_ep_last_counts.  out is int32 [8][world]: tokens sent to d, pairs owned by
+ * d, tokens received from s, pairs received from s, then the first row of each peer's segment in the
+ * send buffer, the receive buffer, the return-send buffer and the return-receive buffer.  Segments
+ * are laid out own first, then the peers in ascending rank, on both sides of both exchanges. */
+int coli_b200_ep_layout(const int32_t *table, int world, int rank, int32_t *out);
+/* Stage timing of the expert-parallel call (measurement mode: synchronises at the end of every
+ * call while on).  ms[COLI_EP_STAGES]: router+top-k, plan+pack, count exchange (includes the host
+ * wait), dispatch, permute, expert FFN, return pack, return exchange, combine. */
+#define COLI_EP_STAGES 9
+int coli_b200_ep_profile(ColiMoe *moe, int enable);
+int coli_b200_ep_stage_ms(ColiMoe *moe, float *ms /* [COLI_EP_STAGES] */, int *calls);
+/* The count table of the last expert-parallel call, HOST int32 [world][2*world]: row s = rank s's
+ * tokens sent to each rank, then its (token, kk) pairs owned by each rank. */
+int coli_b200_ep_last_counts(ColiMoe *moe, int32_t *table);
 
 /* ---- tracing (the role of the reference's COLI_PROFILE phase counters ROUTER_US, MOE_PREP_US,
  * GPUFFN_US, SCATTER_US, crates/colibri-engine/src/forward.rs:86-160) ------------------------ */

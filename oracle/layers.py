@@ -47,16 +47,24 @@ def host_layer(shape: MoeShape):
                                                                     select_bias=sb, logit_bias=lb)
 
 
-def host_sample_layer(shape: MoeShape, x_bits):
-    """Oracle layer holding only the experts the sample tokens route to (generated on the host).
-    Returns (layer, number of routed experts touched)."""
+def host_sample_layer(shape: MoeShape, x_bits, cache: dict | None = None):
+    """Oracle layer holding only the experts the sample tokens route to (generated on the host, several
+    experts at a time on host threads).  `cache` (expert id -> packed triple) carries experts over
+    from an earlier, smaller sample.  Returns (layer, number of routed experts touched)."""
+    from concurrent.futures import ThreadPoolExecutor
+
     router = synth.host_router(shape)
     sb, lb = synth.select_bias(shape), synth.zipf_logit_bias(shape)
     probe = make_layer(shape, router, [None] * shape.E, None, sb, lb)
     idx, _ = probe.route_tokens(x_bits)
     needed = sorted(set(idx.reshape(-1).tolist()))
-    experts = [host_packed_expert(shape, e) if e in needed else None for e in range(shape.E)]
-    shared = host_packed_expert(shape, shape.E) if shape.shared else None
+    cache = {} if cache is None else cache
+    todo = [e for e in needed + ([shape.E] if shape.shared else []) if e not in cache]
+    with ThreadPoolExecutor(max_workers=max(1, min(8, oracle.hardware_threads()))) as pool:
+        for e, packed in zip(todo, pool.map(lambda e: host_packed_expert(shape, e), todo)):
+            cache[e] = packed
+    experts = [cache[e] if e in needed else None for e in range(shape.E)]
+    shared = cache[shape.E] if shape.shared else None
     return make_layer(shape, router, experts, shared, sb, lb), len(needed)
 
 

@@ -9,8 +9,8 @@ import threading
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_HERE, "csrc")
 LIB_PATH = os.path.join(_HERE, "libcoli_b200.so")
-SOURCES = ["abi.cu", "routing.cu", "layout.cu", "expert_small.cu", "expert_tc.cu", "expert_tc_tmem.cu", "combine.cu"]
-HEADERS = ["internal.cuh", "tc_common.cuh", "coli_math.h", os.path.join("..", "..", "include", "coli_b200.h")]
+SOURCES = ["abi.cu", "ep.cu", "routing.cu", "layout.cu", "expert_small.cu", "expert_tc.cu", "expert_tc_tmem.cu", "combine.cu"]
+HEADERS = ["internal.cuh", "host_state.cuh", "tc_common.cuh", "coli_math.h", os.path.join("..", "..", "include", "coli_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-ffp-contract=off", "-shared",
@@ -64,6 +64,7 @@ class ColiMoeLayer(C.Structure):
         ("gate", C.POINTER(C.c_void_p)), ("up", C.POINTER(C.c_void_p)), ("down", C.POINTER(C.c_void_p)),
         ("sh_gate", C.c_void_p), ("sh_up", C.c_void_p), ("sh_down", C.c_void_p),
         ("ep_rank", C.c_int32), ("ep_world", C.c_int32), ("expert_owner", C.c_void_p),
+        ("nccl_comm", C.c_void_p),
     ]
 
 
@@ -131,6 +132,15 @@ SIGNATURES = {
     "coli_b200_moe_shared_dev": (_i, [_P, _P, _i, _P, _P]),
     "coli_b200_moe_combine_partial_dev": (_i, [_P, _P, _P, _P, _P, _i, _P]),
     "coli_b200_moe_finish_dev": (_i, [_P, _P, _P, _P, _i, _P]),
+    "coli_b200_moe_block_ep_dev": (_i, [_P, _P, _P, _i, _P]),
+    "coli_b200_moe_block_ep_emulate": (_i, [_PP, _i, _PP, _PP, C.POINTER(_i), _P]),
+    "coli_b200_nccl_unique_id": (_i, [_P]),
+    "coli_b200_nccl_comm_create": (_i, [_PP, _P, _i, _i, _i]),
+    "coli_b200_nccl_comm_destroy": (None, [_P]),
+    "coli_b200_ep_layout": (_i, [_P, _i, _i, _P]),
+    "coli_b200_ep_profile": (_i, [_P, _i]),
+    "coli_b200_ep_stage_ms": (_i, [_P, C.POINTER(_f), C.POINTER(_i)]),
+    "coli_b200_ep_last_counts": (_i, [_P, _P]),
     "coli_b200_moe_profile": (_i, [_P, _i]),
     "coli_b200_moe_phase_ms": (_i, [_P, C.POINTER(_f), C.POINTER(_i)]),
     "coli_b200_moe_stream": (_P, [_P]),

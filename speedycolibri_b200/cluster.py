@@ -1,14 +1,15 @@
 """Expert parallelism: the ownership map of crates/colibri-cluster/src/sharding.rs and the
 sharded block of crates/colibri-engine/src/moe.rs:1620-1794, with the reference's TCP
-request/response (crates/colibri-cluster/src/net.rs) replaced by NCCL all-to-all over NVLink.
+request/response (crates/colibri-cluster/src/net.rs) replaced by an all-to-all of token rows over
+NCCL send/recv inside one library call.
 
 What is kept from the reference: the expert -> rank map (contiguous ``e*N/E`` or an explicit
 LPT table), the FNV-1a fingerprint every rank compares before exchanging anything, "move
 activations to experts, never weights", and that a peer failure aborts the layer with an
 exception rather than returning zeros.  What changes: tokens are sharded across ranks (each
-rank routes its own T/world tokens), activations reach the peers through one NCCL all-gather
-and the partial sums return through one reduce-scatter, instead of rank 0 driving every peer
-with a request/response per layer."""
+rank routes its own tokens), a token row visits each rank that owns one of its experts once,
+and the unweighted expert outputs come back to the token's home rank, which combines them —
+instead of rank 0 driving every peer with all of x and folding [T,H] partial sums."""
 from __future__ import annotations
 
 from typing import List, Optional, Sequence
@@ -140,126 +141,95 @@ def verify_peers(sharding: ExpertSharding, group=None) -> None:
             raise RuntimeError(f"sharding fingerprint mismatch: rank {r} disagrees with rank {dist.get_rank(group)} ({fp:#018x})")
 
 
+def ep_layout(table: np.ndarray, rank: int) -> dict:
+    """The segment layout rank `rank` derives from the count table [world, 2, world] of an
+    expert-parallel call (``coli_b200_ep_layout``, host-only)."""
+    from . import _lib
+    from .backend import _check
+
+    table = np.ascontiguousarray(table, dtype=np.int32)
+    world = table.shape[0]
+    out = np.zeros((8, world), np.int32)
+    _check(_lib.load().coli_b200_ep_layout(table.ctypes.data, world, rank, out.ctypes.data), "coli_b200_ep_layout")
+    names = ("send_tok", "send_pair", "recv_tok", "recv_pair", "send_off", "recv_off", "ret_send_off", "ret_recv_off")
+    return {n: out[i].copy() for i, n in enumerate(names)}
+
+
+def rows_per_rank(table: np.ndarray) -> np.ndarray:
+    """Expert rows (token, kk pairs) each rank computes in a call with this count table."""
+    return np.asarray(table)[:, 1, :].sum(axis=0)
+
+
+def ep_communicator(device: int, group=None) -> int:
+    """An ncclComm_t (as an integer) over the ranks of `group`, made by the library itself: rank 0
+    draws the 128-byte id, torch.distributed carries it to the others (any backend), every rank
+    joins.  The caller destroys it with ``destroy_communicator`` after the handles that use it."""
+    import ctypes as C
+
+    import torch.distributed as dist
+
+    from . import _lib
+    from .backend import _check
+
+    lib = _lib.load()
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    box = [None]
+    if rank == 0:
+        buf = (C.c_char * 128)()
+        _check(lib.coli_b200_nccl_unique_id(buf), "coli_b200_nccl_unique_id")
+        box[0] = bytes(buf)
+    dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+    comm = C.c_void_p()
+    _check(lib.coli_b200_nccl_comm_create(C.byref(comm), box[0], rank, world, device), "coli_b200_nccl_comm_create")
+    return comm.value
+
+
+def destroy_communicator(comm: int) -> None:
+    from . import _lib
+
+    if comm:
+        _lib.load().coli_b200_nccl_comm_destroy(comm)
+
+
 class ShardedMoe:
     """Expert-parallel block over the ranks of `group` (one process per GPU) — the role of
-    crates/colibri-engine/src/moe.rs:1737 `moe_sharded`.
+    crates/colibri-engine/src/moe.rs:1737 `moe_sharded`.  A thin owner of the pieces: the sharding
+    (verified against the peers), the communicator and the ``MoeBlock`` handle created with both;
+    a call is ONE library call per rank (``coli_b200_moe_block_ep_dev``).
 
-    Each rank holds T_local tokens and the experts `sharding` gives it.  Per call, on the current
-    stream, with no host synchronisation (every exchanged size follows from T, H, k):
+    `layer` holds the experts ``sharding`` gives this rank (others None) and the shared expert;
+    `max_tokens` bounds the tokens of ALL ranks in one call."""
 
-      1. router + top-k of the own tokens                          (block.topk_dev)
-      2. all-gather of tokens (overlapped with 1 and 7a), indices, weights   (NCCL)
-      3. rows of the (token, kk) pairs routed to resident experts  (block.gather_local_dev)
-      4. grouped expert FFN over those rows                        (block.experts_dev)
-      5. f32 partial sum per token over the resident experts       (block.combine_partial_dev)
-      6. reduce-scatter of the partials: every rank receives the sum for its own tokens (NCCL) —
-         the fold of peer partials of moe.rs:1725-1733
-      7. + shared expert of the own tokens, one rounding to bf16   (block.shared_dev, finish_dev)
-
-    Like the reference (moe.rs:1671-1678) every rank sees all activation rows and only weights
-    never move; unlike it, no rank drives the others.  `block` must be created with
-    max_tokens >= world * T_local.  Buffers are allocated once and reused by every call."""
-
-    def __init__(self, block, sharding: ExpertSharding, t_local: int, group=None):
-        import torch
+    def __init__(self, cfg, layer, sharding: ExpertSharding, max_tokens: int, device: int, group=None):
         import torch.distributed as dist
 
-        self.block, self.sharding, self.group, self.Tl = block, sharding, group, int(t_local)
+        from .moe import MoeBlock
+
+        self.sharding, self.group = sharding, group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        assert self.world == sharding.num_nodes and self.rank == block.ep_rank
-        cfg = block.cfg
-        self.k, self.H = cfg.topk, cfg.hidden
-        T = self.T = self.world * self.Tl
-        assert block.max_tokens >= T, "create the block with max_tokens = tokens of all ranks"
-        assert block.local_experts() == sharding.count_for(self.rank)
-        self.gloo = dist.get_backend(group) == "gloo"
-        dev = "cpu" if self.gloo else torch.device("cuda", block.device)
-        bf, i32, f32 = torch.bfloat16, torch.int32, torch.float32
-        self.x_all = torch.empty((T, self.H), dtype=bf, device=dev)
-        self.idx = torch.empty((self.Tl, self.k), dtype=i32, device=dev)
-        self.w = torch.empty((self.Tl, self.k), dtype=f32, device=dev)
-        self.idx_all = torch.empty((T, self.k), dtype=i32, device=dev)
-        self.w_all = torch.empty((T, self.k), dtype=f32, device=dev)
-        self.rows = torch.empty((T * self.k, self.H), dtype=bf, device=dev)
-        self.y_rows = torch.empty((T * self.k, self.H), dtype=bf, device=dev)
-        self.seg_count = torch.zeros(max(1, block.local_experts()), dtype=i32, device=dev)
-        self.slot = torch.empty(T * self.k, dtype=i32, device=dev)
-        self.partial = torch.empty((T, self.H), dtype=f32, device=dev)
-        self.mine = torch.empty((self.Tl, self.H), dtype=f32, device=dev)
-        self.shared_y = torch.empty((self.Tl, self.H), dtype=bf, device=dev) if block.has_shared else None
-        self.rows_expected = max(1, T * self.k // self.world)
+        assert self.world == sharding.num_nodes
+        verify_peers(sharding, group)
+        self.comm = ep_communicator(device, group)
+        self.block = MoeBlock(cfg, layer, max_tokens, device=device, ep_rank=self.rank, ep_world=self.world,
+                              expert_owner=sharding.owner_table() if sharding.is_hot_aware() else None, nccl_comm=self.comm)
+        assert self.block.local_experts() == sharding.count_for(self.rank)
 
-    def _stream(self):
+    def __call__(self, x, out=None):
+        return self.block.forward_ep(x, out)
+
+    def stage_ms(self, x, steps: int):
+        """Per-stage milliseconds averaged over `steps` extra calls (every rank must take part)."""
+        self.block.ep_profile(True)
+        for _ in range(steps):
+            self.block.forward_ep(x)
+        ms, calls = self.block.ep_stage_ms()
+        self.block.ep_profile(False)
+        return {k: v / max(calls, 1) for k, v in ms.items()}
+
+    def close(self):
         import torch
 
-        return 0 if self.gloo else torch.cuda.current_stream().cuda_stream
-
-    STAGES = ("topk", "all_gather", "gather_local", "experts", "combine_partial", "reduce_scatter+shared", "finish")
-
-    def __call__(self, x, out=None, timing=None):
-        """`timing`: optional dict that receives per-stage milliseconds (CUDA events on the current
-        stream; synchronises at the end, so only for measurement)."""
-        import torch
-        import torch.distributed as dist
-
-        assert x.shape == (self.Tl, self.H)
-        b, st = self.block, self._stream()
-        if out is None:
-            out = torch.empty_like(x)
-        marks = []
-
-        def mark():
-            if timing is not None and not self.gloo:
-                e = torch.cuda.Event(enable_timing=True)
-                e.record()
-                marks.append(e)
-
-        mark()
-        # the token all-gather does not depend on the routing: let it run under the router and the
-        # shared expert (NCCL's own stream), and join before the first kernel that reads x_all
-        gather_x = None
-        if self.gloo:
-            dist.all_gather_into_tensor(self.x_all, x, group=self.group)
-        else:
-            gather_x = dist.all_gather_into_tensor(self.x_all, x, group=self.group, async_op=True)
-        b.topk_dev(x, self.idx, self.w, st)
-        mark()
-        dist.all_gather_into_tensor(self.idx_all, self.idx, group=self.group)
-        dist.all_gather_into_tensor(self.w_all, self.w, group=self.group)
-        if gather_x is not None:
-            gather_x.wait()
-        mark()
-        b.gather_local_dev(self.x_all, self.idx_all, self.rows, self.seg_count, self.slot, st)
-        mark()
-        b.experts_dev(self.rows, self.seg_count, self.rows_expected, self.y_rows, st)
-        mark()
-        b.combine_partial_dev(self.y_rows, self.slot, self.w_all, self.partial, st)
-        mark()
-        # The shared expert (replicated weights, own tokens) is independent of the exchange: it
-        # runs on the compute stream while NCCL reduces the partial sums on its own stream.
-        if self.gloo:  # gloo has no reduce-scatter: all-reduce and keep the own slice
-            dist.all_reduce(self.partial, group=self.group)
-            self.mine.copy_(self.partial[self.rank * self.Tl:(self.rank + 1) * self.Tl])
-            if b.has_shared:
-                b.shared_dev(x, self.shared_y, st)
-        else:
-            rs = dist.reduce_scatter_tensor(self.mine, self.partial, group=self.group, async_op=True)
-            if b.has_shared:
-                b.shared_dev(x, self.shared_y, st)
-            rs.wait()
-        mark()
-        b.finish_dev(self.mine, self.shared_y, out, st)
-        mark()
-        if marks:
-            torch.cuda.synchronize()
-            for name, e0, e1 in zip(self.STAGES, marks[:-1], marks[1:]):
-                timing[name] = timing.get(name, 0.0) + e0.elapsed_time(e1)
-        return out
-
-
-def moe_sharded(block, sharding: ExpertSharding, x, group=None):
-    """One expert-parallel block call; keeps a ShardedMoe (and its buffers) on the block."""
-    sm = getattr(block, "_sharded", None)
-    if sm is None or sm.Tl != x.shape[0] or sm.sharding is not sharding:
-        sm = block._sharded = ShardedMoe(block, sharding, x.shape[0], group)
-    return sm(x)
+        torch.cuda.synchronize()
+        self.block.close()
+        destroy_communicator(self.comm)
+        self.comm = None

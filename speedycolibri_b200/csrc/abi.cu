@@ -8,7 +8,7 @@
 #include <mutex>
 #include <vector>
 
-#include "internal.cuh"
+#include "host_state.cuh"
 
 // ---- errors ---------------------------------------------------------------------------------
 static thread_local char g_err[512] = "";
@@ -33,17 +33,6 @@ extern "C" uint64_t coli_b200_launch_count(void) { return g_launches.load(std::m
 
 // ---- device contexts (backend_cuda.cu:87-129, 2594-2655) --------------------------------------
 namespace {
-struct DeviceContext {
-  int device = -1;
-  cudaStream_t stream = nullptr;
-  std::mutex mu;  // held across a whole host-pointer call, as the reference does
-  size_t tensor_count = 0, tensor_bytes = 0;
-  // scratch of the host-pointer expert calls, grown on demand
-  void *buf[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
-  size_t cap[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};  // phase marks of the host-pointer group calls
-  int sm_count = 0;
-};
 std::mutex g_init_mu;
 DeviceContext *g_ctx[COLI_CUDA_MAX_DEVICES];
 int g_ndev = 0;
@@ -51,13 +40,6 @@ int g_act_oai = 0;  // process-wide gate/up combine, backend_cuda.cu:339-350
 float g_act_alpha = 1.702f;
 float g_act_limit = 0.0f;
 
-DeviceContext *find_ctx(int device) {
-  for (int i = 0; i < g_ndev; ++i)
-    if (g_ctx[i] && g_ctx[i]->device == device) return g_ctx[i];
-  coli_set_error("device %d is not initialised (call coli_cuda_init)", device);
-  return nullptr;
-}
-bool select_ctx(DeviceContext *c) { return c && coli_cuda_check(cudaSetDevice(c->device), "cudaSetDevice"); }
 bool reserve(DeviceContext *c, int slot, size_t bytes) {
   if (c->cap[slot] >= bytes) return true;
   if (c->buf[slot]) cudaFree(c->buf[slot]);
@@ -68,6 +50,16 @@ bool reserve(DeviceContext *c, int slot, size_t bytes) {
   return true;
 }
 }  // namespace
+
+DeviceContext *coli_find_ctx(int device) {
+  for (int i = 0; i < g_ndev; ++i)
+    if (g_ctx[i] && g_ctx[i]->device == device) return g_ctx[i];
+  coli_set_error("device %d is not initialised (call coli_cuda_init)", device);
+  return nullptr;
+}
+bool coli_select_ctx(DeviceContext *c) { return c && coli_cuda_check(cudaSetDevice(c->device), "cudaSetDevice"); }
+static DeviceContext *find_ctx(int device) { return coli_find_ctx(device); }
+static bool select_ctx(DeviceContext *c) { return coli_select_ctx(c); }
 
 extern "C" int coli_cuda_init(const int *devices, int count) {
   std::lock_guard<std::mutex> lk(g_init_mu);
@@ -470,60 +462,13 @@ extern "C" int coli_b200_quantize_fp8_b128(int device, const float *d_w, int O, 
 }
 
 // ---- the block ------------------------------------------------------------------------------------
-struct ColiMoe {
-  ColiMoeLayer L;
-  DeviceContext *ctx;
-  int max_tokens;
-  int nseg;            // E (+1 with a shared expert)
-  bool has_shared;
-  bool all_resident;
-  std::vector<int32_t> h_expert_slot;  // expert -> segment position in (owner, id) order
-  std::vector<int32_t> h_seg_expert;   // segment position -> weight-table index
-  int first_local_seg, n_local_seg;
-  // device tables
-  __nv_bfloat16 *router_w;
-  float *select_bias, *logit_bias;
-  WeightRef *gate, *up, *down;  // [E+1], entry E = shared expert
-  int32_t *expert_slot, *seg_expert;
-  int32_t *local_slot;  // expert -> position among this rank's experts, or -1
-  // workspace
-  float *logits, *topk_w;
-  int32_t *topk_idx, *local_rank, *chunk_cnt, *seg_count, *seg_off, *slot, *row_token;
-  int32_t *item_seg, *item_row0, *item_nrows, *n_items;
-  int item_cap;
-  __nv_bfloat16 *y, *x_stage, *out_stage;
-  __half *h;    // intermediate rows of the expert FFN
-  __half *x16;  // token-order f16 copy of the activations (small-batch path, shared expert stage)
-  __half *xg;   // gathered f16 rows for the tcgen05 path (null when max_tokens never reaches it)
-  int *status;        // device status word of the tcgen05 kernels
-  unsigned int *ticket;  // device word of the fused decode front end (zero between launches)
-  colib::ActParams act;  // the process-wide activation setting when the handle was created
-  int sm_count;
-  size_t h_rows_cap;  // rows the h scratch holds
-  size_t ws_bytes;
-  std::vector<void *> allocs;
-  // tracing
-  bool profiling;
-  cudaEvent_t ev[COLI_PHASES + 1];
-  float phase_ms[COLI_PHASES];
-  int phase_calls;
-};
-
-template <class T>
-static bool ws_alloc(ColiMoe *m, T **p, size_t count) {
-  const size_t bytes = (count ? count : 1) * sizeof(T);
-  if (!coli_cuda_check(cudaMalloc((void **)p, bytes), "workspace allocation")) return false;
-  m->allocs.push_back(*p);
-  m->ws_bytes += bytes;
-  return true;
-}
-
 extern "C" void coli_b200_moe_destroy(ColiMoe *m) {
   if (!m) return;
   if (m->ctx) {
     cudaSetDevice(m->ctx->device);
-    cudaStreamSynchronize(m->ctx->stream);
+    cudaDeviceSynchronize();
   }
+  coli_ep_destroy(m);
   for (void *p : m->allocs) cudaFree(p);
   for (int i = 0; i <= COLI_PHASES; ++i)
     if (m->ev[i]) cudaEventDestroy(m->ev[i]);
@@ -556,22 +501,26 @@ extern "C" void *coli_b200_moe_stream(ColiMoe *m) { return m ? (void *)m->ctx->s
 // 160 tokens and wins while segments are about that long; longer NVFP4 segments amortise the
 // shared-memory weight tiles of the other kernel over 256 tokens.  The FP8 formats exist in the
 // tensor-memory kernel only (longer segments are cut into several of its tiles).
-static bool use_tct(int fmt, int rows, int nseg) {
+bool coli_use_tct(int fmt, int rows, int nseg) {
   return fmt != COLI_FMT_NVFP4 || rows <= 160 * (nseg > 0 ? nseg : 1);
 }
 // Tile width of the tensor-memory kernel: short tiles (and a weight ring twice as deep) while the
 // average segment fits one of them with room to spare, the full width otherwise.
-static int tct_tile_tokens(int rows, int nseg) {
+int coli_tct_tile_tokens(int rows, int nseg) {
   return rows <= 48 * (nseg > 0 ? nseg : 1) ? colib::TCT_SHORT_TOKENS : colib::TCT_MAX_TOKENS;
 }
-static bool use_tc_path(int fmt, int rows, int nseg) {
+bool coli_use_tc_path(int fmt, int rows, int nseg) {
   return (fmt == COLI_FMT_NVFP4 || fmt == COLI_FMT_FP8_B128 || fmt == COLI_FMT_E4M3_ROW) && nseg > 0 && rows / nseg >= 8;
 }
 
-static int rows_per_item_for(const ColiMoeLayer &L, int rows, int nseg) {
+int coli_rows_per_item_for(int rows, int nseg) {
   const int avg = (rows + nseg - 1) / (nseg > 0 ? nseg : 1);
   return avg <= 8 ? 8 : avg <= 16 ? 16 : 32;
 }
+static bool use_tct(int fmt, int rows, int nseg) { return coli_use_tct(fmt, rows, nseg); }
+static int tct_tile_tokens(int rows, int nseg) { return coli_tct_tile_tokens(rows, nseg); }
+static bool use_tc_path(int fmt, int rows, int nseg) { return coli_use_tc_path(fmt, rows, nseg); }
+static int rows_per_item_for(const ColiMoeLayer &, int rows, int nseg) { return coli_rows_per_item_for(rows, nseg); }
 
 extern "C" int coli_b200_moe_create(ColiMoe **out, const ColiMoeLayer *L, int max_tokens) {
   if (!out || !L || max_tokens < 1) {
@@ -624,6 +573,7 @@ extern "C" int coli_b200_moe_create(ColiMoe **out, const ColiMoeLayer *L, int ma
       return 0;
     }
   }
+  m->h_owner.assign(owner.begin(), owner.end());
   m->h_expert_slot.assign(E, 0);
   m->h_seg_expert.assign(E + 1, E);
   m->first_local_seg = 0;
@@ -690,6 +640,16 @@ extern "C" int coli_b200_moe_create(ColiMoe **out, const ColiMoeLayer *L, int ma
        ws_alloc(m, &m->h, rows * I) && ws_alloc(m, &m->y, rows * H) && ws_alloc(m, &m->x_stage, T * H) &&
        ws_alloc(m, &m->out_stage, T * H) && ws_alloc(m, &m->x16, T * H);
   m->h_rows_cap = rows;
+  m->seg_main.h = m->h;
+  m->seg_main.h_rows = rows;
+  m->seg_main.item_seg = m->item_seg;
+  m->seg_main.item_row0 = m->item_row0;
+  m->seg_main.item_nrows = m->item_nrows;
+  m->seg_main.n_items = m->n_items;
+  m->seg_main.seg_off = m->seg_off;
+  m->seg_main.item_cap = m->item_cap;
+  m->seg_main.seg_cap = E + 1;
+  m->ep = nullptr;
   m->xg = nullptr;
   m->status = nullptr;
   {
@@ -721,6 +681,7 @@ extern "C" int coli_b200_moe_create(ColiMoe **out, const ColiMoeLayer *L, int ma
   if (ok && L->logit_bias)
     ok = coli_cuda_check(cudaMemcpyAsync(m->logit_bias, L->logit_bias, sizeof(float) * E, cudaMemcpyHostToDevice, st), "bias upload");
   ok = ok && coli_cuda_check(cudaStreamSynchronize(st), "moe_create sync");
+  if (ok && world > 1 && L->nccl_comm) ok = coli_ep_ensure(m, L->nccl_comm) != 0;
   // from here on the handle's format is the one its kernels decode (MXFP4 is resident in the NVFP4 form)
   m->L.fmt = coli_kernel_fmt(L->fmt);
   // the handle keeps no host pointers
@@ -729,7 +690,9 @@ extern "C" int coli_b200_moe_create(ColiMoe **out, const ColiMoeLayer *L, int ma
   m->L.logit_bias = nullptr;
   m->L.expert_owner = nullptr;
   m->L.gate = m->L.up = m->L.down = nullptr;
+  m->L.nccl_comm = nullptr;
   if (!ok) {
+    coli_ep_destroy(m);
     for (void *p : m->allocs) cudaFree(p);
     delete m;
     return 0;
@@ -746,7 +709,8 @@ static cudaStream_t pick_stream(ColiMoe *m, void *stream) {
   return (cudaStream_t)stream;
 }
 
-static bool check_T(ColiMoe *m, int T, const char *who) {
+static bool check_T(ColiMoe *m, int T, const char *who) { return coli_check_T(m, T, who); }
+bool coli_check_T(ColiMoe *m, int T, const char *who) {
   if (!m) {
     coli_set_error("%s: null handle", who);
     return false;
@@ -758,7 +722,8 @@ static bool check_T(ColiMoe *m, int T, const char *who) {
   return select_ctx(m->ctx);
 }
 
-static colib::RouteParams route_params(ColiMoe *m, const void *x_dev, int T) {
+static colib::RouteParams route_params(ColiMoe *m, const void *x_dev, int T) { return coli_route_params(m, x_dev, T); }
+colib::RouteParams coli_route_params(ColiMoe *m, const void *x_dev, int T) {
   colib::RouteParams rp;
   rp.T = T;
   rp.H = m->L.H;
@@ -781,6 +746,10 @@ static colib::RouteParams route_params(ColiMoe *m, const void *x_dev, int T) {
 
 static colib::PermuteParams permute_params(ColiMoe *m, const void *x_dev, int T, bool with_shared, int rpi, void *rows_dev,
                                            int32_t *seg_count, int32_t *slot) {
+  return coli_permute_params(m, x_dev, T, with_shared, rpi, rows_dev, seg_count, slot);
+}
+colib::PermuteParams coli_permute_params(ColiMoe *m, const void *x_dev, int T, bool with_shared, int rpi, void *rows_dev,
+                                         int32_t *seg_count, int32_t *slot) {
   colib::PermuteParams pp;
   pp.T = T;
   pp.H = m->L.H;
@@ -1041,38 +1010,44 @@ extern "C" int coli_b200_moe_gather_local_dev(ColiMoe *m, const void *x_dev, con
   return colib::launch_permute(pp, st);
 }
 
-// h scratch for the stage calls grows on demand (synchronises the device when it does).
-static bool ensure_h(ColiMoe *m, size_t rows) {
-  if (rows <= m->h_rows_cap) return true;
+// scratch of a grouped-FFN run grows on demand (synchronises the device when it does)
+static bool ensure_h(ColiMoe *m, SegScratch &sc, size_t rows) {
+  if (rows <= sc.h_rows) return true;
   if (!coli_cuda_check(cudaDeviceSynchronize(), "scratch regrow sync")) return false;
   __half *nh = nullptr;
   if (!coli_cuda_check(cudaMalloc((void **)&nh, rows * m->L.I * sizeof(__half)), "scratch regrow")) return false;
   m->allocs.push_back(nh);  // the old block is released with the handle
   m->ws_bytes += rows * m->L.I * sizeof(__half);
-  m->h = nh;
-  m->h_rows_cap = rows;
+  sc.h = nh;
+  sc.h_rows = rows;
   return true;
 }
-static bool ensure_items(ColiMoe *m, int need) {
-  if (need <= m->item_cap) return true;
+static bool ensure_items(ColiMoe *m, SegScratch &sc, int need, int n_seg) {
+  if (n_seg > sc.seg_cap) {
+    if (!coli_cuda_check(cudaDeviceSynchronize(), "work list regrow sync")) return false;
+    if (!ws_alloc(m, &sc.seg_off, (size_t)n_seg + 2)) return false;
+    sc.seg_cap = n_seg;
+  }
+  if (!sc.n_items && !ws_alloc(m, &sc.n_items, 1)) return false;
+  if (need <= sc.item_cap) return true;
   if (!coli_cuda_check(cudaDeviceSynchronize(), "work list regrow sync")) return false;
-  m->item_cap = need;
-  return ws_alloc(m, &m->item_seg, need) && ws_alloc(m, &m->item_row0, need) && ws_alloc(m, &m->item_nrows, need);
+  sc.item_cap = need;
+  return ws_alloc(m, &sc.item_seg, need) && ws_alloc(m, &sc.item_row0, need) && ws_alloc(m, &sc.item_nrows, need);
 }
 
 // rows_cap bounds the rows the buffers hold (the work list is sized from it); rows_expected only
 // selects the kernel family, so that the choice is a function of shapes, never of data.
-static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, const WeightRef *d, const int32_t *seg_expert_dev,
-                        const void *rows_dev, const int32_t *seg_count_dev, int n_seg, int rows_cap, int rows_expected,
-                        void *y_dev, cudaStream_t st) {
+int coli_run_segments(ColiMoe *m, SegScratch &sc, const WeightRef *g, const WeightRef *u, const WeightRef *d,
+                      const int32_t *seg_expert_dev, const void *rows_dev, const int32_t *seg_count_dev, int n_seg,
+                      int rows_cap, int rows_expected, void *y_dev, cudaStream_t st) {
   if (rows_cap == 0 || n_seg == 0) return 1;
   const bool tc = use_tc_path(m->L.fmt, rows_expected, n_seg);
   const bool tct = tc && use_tct(m->L.fmt, rows_expected, n_seg);
   const int rpi = tc ? (tct ? tct_tile_tokens(rows_expected, n_seg) : colib::TC_MAX_TOKENS) : rows_per_item_for(m->L, rows_expected, n_seg);
   const int max_items = max_work_items(rows_cap, n_seg, rpi);
-  if (!ensure_h(m, (size_t)rows_cap) || !ensure_items(m, max_items)) return 0;
-  if (!colib::launch_items_from_counts(seg_count_dev, n_seg, rpi, m->seg_off, m->item_seg, m->item_row0, m->item_nrows,
-                                       m->n_items, st))
+  if (!ensure_h(m, sc, (size_t)rows_cap) || !ensure_items(m, sc, max_items, n_seg)) return 0;
+  if (!colib::launch_items_from_counts(seg_count_dev, n_seg, rpi, sc.seg_off, sc.item_seg, sc.item_row0, sc.item_nrows,
+                                       sc.n_items, st))
     return 0;
   if (tc) {
     colib::TcParams tp;
@@ -1083,13 +1058,13 @@ static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, cons
     tp.up = u;
     tp.down = d;
     tp.seg_expert = seg_expert_dev;
-    tp.item_seg = m->item_seg;
-    tp.item_row0 = m->item_row0;
-    tp.item_nrows = m->item_nrows;
-    tp.n_items = m->n_items;
+    tp.item_seg = sc.item_seg;
+    tp.item_row0 = sc.item_row0;
+    tp.item_nrows = sc.item_nrows;
+    tp.n_items = sc.n_items;
     tp.max_items = max_items;
     tp.tile_tokens = rpi;
-    tp.h = m->h;
+    tp.h = sc.h;
     tp.y = (__nv_bfloat16 *)y_dev;
     tp.status = m->status;
     tp.act = m->act;
@@ -1104,21 +1079,26 @@ static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, cons
   fp.up = u;
   fp.down = d;
   fp.seg_expert = seg_expert_dev;
-  fp.item_seg = m->item_seg;
-  fp.item_row0 = m->item_row0;
-  fp.item_nrows = m->item_nrows;
-  fp.n_items = m->n_items;
+  fp.item_seg = sc.item_seg;
+  fp.item_row0 = sc.item_row0;
+  fp.item_nrows = sc.item_nrows;
+  fp.n_items = sc.n_items;
   fp.max_items = max_items;
   fp.rows_per_item = rpi;
   fp.items_expected = (rows_expected < n_seg ? rows_expected : n_seg) + rows_expected / rpi;
   fp.x = (const __half *)rows_dev;
   fp.row_token = nullptr;
-  fp.h = m->h;
+  fp.h = sc.h;
   fp.y = (__nv_bfloat16 *)y_dev;
   fp.y32 = nullptr;
   fp.relu2_out = nullptr;
   fp.act = m->act;
   return colib::launch_ffn_small(fp, st);
+}
+static int run_segments(ColiMoe *m, const WeightRef *g, const WeightRef *u, const WeightRef *d, const int32_t *seg_expert_dev,
+                        const void *rows_dev, const int32_t *seg_count_dev, int n_seg, int rows_cap, int rows_expected,
+                        void *y_dev, cudaStream_t st) {
+  return coli_run_segments(m, m->seg_main, g, u, d, seg_expert_dev, rows_dev, seg_count_dev, n_seg, rows_cap, rows_expected, y_dev, st);
 }
 
 extern "C" int coli_b200_moe_experts_dev(ColiMoe *m, const void *rows_dev, const int32_t *seg_count_dev, int rows_cap,

@@ -60,7 +60,7 @@ class MoeBlock:
     """One layer's device-resident tables and workspace (``ColiMoe``)."""
 
     def __init__(self, cfg: Config, layer: Layer, max_tokens: int, device: int = 0, ep_rank: int = 0,
-                 ep_world: int = 1, expert_owner: Optional[Sequence[int]] = None):
+                 ep_world: int = 1, expert_owner: Optional[Sequence[int]] = None, nccl_comm: Optional[int] = None):
         self.cfg, self.device, self.max_tokens = cfg, device, max_tokens
         self.ep_rank, self.ep_world = ep_rank, ep_world
         E = cfg.n_experts
@@ -93,6 +93,8 @@ class MoeBlock:
             own = np.ascontiguousarray(expert_owner, dtype=np.int32)
             keep.append(own)
             L.expert_owner = own.ctypes.data
+        if nccl_comm:
+            L.nccl_comm = nccl_comm
         h = C.c_void_p()
         _check(_lib_().coli_b200_moe_create(C.byref(h), C.byref(L), max_tokens), "coli_b200_moe_create")
         self.handle = h.value
@@ -171,7 +173,38 @@ class MoeBlock:
     def workspace_bytes(self) -> int:
         return _lib_().coli_b200_moe_workspace_bytes(self.handle)
 
-    # -- stages (used by cluster.moe_sharded) ---------------------------------------------------
+    # -- expert-parallel call (one per rank; the role of moe.rs:1737 `moe_sharded`) ---------------
+    def forward_ep(self, x, out=None, stream=None):
+        """torch bf16 CUDA [T_local,H] -> [T_local,H]; every rank of the communicator calls it."""
+        import torch
+
+        assert x.dtype == torch.bfloat16 and x.is_cuda and x.is_contiguous()
+        if out is None:
+            out = torch.empty_like(x)
+        st = torch.cuda.current_stream(x.device).cuda_stream if stream is None else stream
+        _check(_lib_().coli_b200_moe_block_ep_dev(self.handle, x.data_ptr(), out.data_ptr(), x.shape[0], st),
+               "coli_b200_moe_block_ep_dev")
+        return out
+
+    EP_STAGES = ("route", "plan_pack", "counts", "dispatch", "permute", "experts", "return_pack", "return", "combine")
+
+    def ep_profile(self, enable: bool) -> None:
+        _check(_lib_().coli_b200_ep_profile(self.handle, int(enable)), "coli_b200_ep_profile")
+
+    def ep_stage_ms(self):
+        """(dict stage -> accumulated ms, calls) since ep_profile(True)."""
+        ms = (C.c_float * len(self.EP_STAGES))()
+        n = C.c_int()
+        _check(_lib_().coli_b200_ep_stage_ms(self.handle, ms, C.byref(n)), "coli_b200_ep_stage_ms")
+        return dict(zip(self.EP_STAGES, [float(v) for v in ms])), n.value
+
+    def ep_last_counts(self) -> np.ndarray:
+        """int32 [world, 2, world]: [s, 0, d] tokens rank s sent to rank d, [s, 1, d] pairs of s owned by d."""
+        tab = np.zeros((self.ep_world, 2, self.ep_world), np.int32)
+        _check(_lib_().coli_b200_ep_last_counts(self.handle, _np_ptr(tab)), "coli_b200_ep_last_counts")
+        return tab
+
+    # -- stages (the pieces the block is made of, callable one by one) ----------------------------
     def local_experts(self) -> int:
         return _lib_().coli_b200_moe_local_experts(self.handle)
 

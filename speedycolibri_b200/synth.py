@@ -69,7 +69,7 @@ def host_dense_weight(shape: MoeShape, which: str, expert: int) -> np.ndarray:
     """f32 [O,K] ~N(0, 0.02): gate/up are [I,H], down is [H,I] (convert.rs expert_oi)."""
     O, K = (shape.H, shape.I) if which == "down" else (shape.I, shape.H)
     rng = np.random.Generator(np.random.Philox(tensor_seed(shape.name, which, expert)))
-    w = (rng.standard_normal((O, K)) * WEIGHT_STD).astype(np.float32)
+    w = rng.standard_normal((O, K), dtype=np.float32) * np.float32(WEIGHT_STD)
     if shape.block_spread > 0.0:
         # magnitudes that differ from one 128x128 block to the next (quantisation scales then do too)
         srng = np.random.Generator(np.random.Philox(tensor_seed(shape.name, which + "_spread", expert)))

@@ -29,10 +29,11 @@ def test_header_symbols_are_all_exported_and_bound():
 
 
 def test_struct_layout_matches_header():
-    """ColiMoeLayer: 11 ints/floats, padding to 8, 9 pointers, 2 ints, padding, 1 pointer."""
+    """ColiMoeLayer: 11 ints/floats, padding to 8, 9 pointers, 2 ints, 2 pointers."""
     from speedycolibri_b200 import _lib
 
-    assert C.sizeof(_lib.ColiMoeLayer) == 48 + 9 * 8 + 8 + 8
+    assert C.sizeof(_lib.ColiMoeLayer) == 48 + 9 * 8 + 8 + 8 + 8
+    assert _lib.ColiMoeLayer.nccl_comm.offset == 48 + 72 + 16
     assert _lib.ColiMoeLayer.router_w.offset == 48
     assert _lib.ColiMoeLayer.ep_rank.offset == 48 + 72
     assert _lib.ColiMoeLayer.expert_owner.offset == 48 + 72 + 8

@@ -1,5 +1,5 @@
 """Host logic of expert parallelism on CPU: the sharding maps (crates/colibri-cluster/src/sharding.rs
-tests :272-510), the exchange bookkeeping, and a 2-rank gloo run of the counts/rows exchange."""
+tests :272-510), the exchange layout, and 2- and 3-rank gloo runs of the counts/rows exchange."""
 import os
 import subprocess
 import sys
@@ -50,91 +50,80 @@ def test_capacity_weighted_largest_remainder():
 
 
 WORKER = r"""
+# Two gloo ranks on CPU carry out the expert-parallel exchange exactly as the library lays it out:
+# each rank plans its dispatch (stated here in numpy: a token goes once to every rank that owns one
+# of its experts, tokens ascending), the counts are all-gathered, BOTH sides derive their segment
+# offsets from the table with the library's own host function, rows travel with send/recv, a toy
+# expert (row * (e + 1)) runs on the owner, results return in (source, token, kk) order and the home
+# rank combines.  What is under test is that sender and receiver agree on every offset.
 import os, sys
 import numpy as np, torch, torch.distributed as dist
 sys.path.insert(0, sys.argv[1])
-from speedycolibri_b200.cluster import ExpertSharding, ShardedMoe, verify_peers
-dist.init_process_group("gloo", init_method="tcp://127.0.0.1:" + sys.argv[2], rank=int(sys.argv[3]), world_size=2)
-rank, world = dist.get_rank(), 2
-E, k, H, Tl = 8, 2, 16, 6
-
-
-class Cfg:
-    topk, hidden, n_experts = k, H, E
-
-
-class FakeBlock:
-    # Stage calls of MoeBlock restated with torch on the CPU; expert e maps a row x to (e + 1) * x,
-    # the shared expert to 0.5 * x.  Only the orchestration in ShardedMoe is under test.
-    cfg, device, has_shared = Cfg, 0, True
-
-    def __init__(self, sharding, rank, max_tokens):
-        self.ep_rank, self.max_tokens = rank, max_tokens
-        self.local = sharding.local_experts(rank)
-
-    def local_experts(self):
-        return len(self.local)
-
-    def topk_dev(self, x, idx, w, st):
-        v, i = torch.topk(x.float()[:, :E], k, dim=1)
-        idx.copy_(i.int())
-        w.copy_(torch.softmax(v, dim=1))
-
-    def shared_dev(self, x, y, st):
-        y.copy_((x.float() * 0.5).to(y.dtype))
-
-    def gather_local_dev(self, x_all, idx_all, rows, seg_count, slot, st):
-        slot.fill_(-1)
-        pos = 0
-        flat = idx_all.reshape(-1)
-        for j, e in enumerate(self.local):
-            hit = (flat == e).nonzero().reshape(-1)
-            seg_count[j] = len(hit)
-            for p in hit.tolist():
-                rows[pos] = x_all[p // k]
-                slot[p] = pos
-                pos += 1
-
-    def experts_dev(self, rows, seg_count, rows_expected, y, st):
-        pos = 0
-        for j, e in enumerate(self.local):
-            n = int(seg_count[j])
-            y[pos:pos + n] = (rows[pos:pos + n].float() * (e + 1)).to(y.dtype)
-            pos += n
-
-    def combine_partial_dev(self, y_rows, slot, w_all, partial, st):
-        partial.zero_()
-        for t in range(partial.shape[0]):
-            for kk in range(k):
-                s = int(slot[t * k + kk])
-                if s >= 0:
-                    partial[t] += float(w_all[t, kk]) * y_rows[s].float()
-
-    def finish_dev(self, partial, shared_y, out, st):
-        out.copy_((partial + shared_y.float()).to(out.dtype))
-
-
-sh = ExpertSharding.new(world, E)
+from speedycolibri_b200.cluster import ExpertSharding, ep_layout, verify_peers
+world = int(sys.argv[4])
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:" + sys.argv[2], rank=int(sys.argv[3]), world_size=world)
+rank = dist.get_rank()
+E, k, H = 12, 3, 8
+Tl = [7, 4, 5][rank]                       # ragged token counts
+sh = ExpertSharding.balanced(world, E, [5, 1, 1, 9, 1, 1, 2, 2, 7, 1, 1, 3])
 verify_peers(sh)
-blk = FakeBlock(sh, rank, world * Tl)
-sm = ShardedMoe(blk, sh, Tl)
-g = torch.Generator().manual_seed(5)
-x_all = torch.randn((world * Tl, H), generator=g).to(torch.bfloat16)   # same on both ranks
-x = x_all[rank * Tl:(rank + 1) * Tl].contiguous()
-for rep in range(2):                                                     # buffers are reused
-    out = sm(x)
-xf = x.float()
-v, i = torch.topk(xf[:, :E], k, dim=1)
-w = torch.softmax(v, dim=1)
-want = torch.zeros_like(xf)
+own = np.array(sh.owner_table())
+rng = np.random.default_rng(100 + rank)
+x = rng.standard_normal((Tl, H)).astype(np.float32)
+idx = np.stack([rng.choice(E, k, replace=False) for _ in range(Tl)]).astype(np.int32)
+w = rng.random((Tl, k)).astype(np.float32)
+peer_order = lambda r: [r] + [p for p in range(world) if p != r]
+# plan (device kernel k_ep_plan, restated)
+tok_list = {d: [t for t in range(Tl) if (own[idx[t]] == d).any()] for d in range(world)}
+pairs = {d: [(t, kk) for t in range(Tl) for kk in range(k) if own[idx[t, kk]] == d] for d in range(world)}
+cnt = torch.tensor([len(tok_list[d]) for d in range(world)] + [len(pairs[d]) for d in range(world)], dtype=torch.int32)
+allc = [torch.empty_like(cnt) for _ in range(world)]
+dist.all_gather(allc, cnt)
+table = torch.stack(allc).numpy().reshape(world, 2, world)
+lay = ep_layout(table, rank)
+assert list(lay["send_tok"]) == [len(tok_list[d]) for d in range(world)]
+R = int(lay["recv_tok"].sum())
+recv_x = torch.zeros((max(R, 1), H)); recv_idx = torch.zeros((max(R, 1), k), dtype=torch.int32)
+send_rows = int(sum(lay["send_tok"][p] for p in range(world) if p != rank))
+send_x = torch.zeros((max(send_rows, 1), H)); send_idx = torch.zeros((max(send_rows, 1), k), dtype=torch.int32)
+for d in range(world):                      # pack (k_ep_pack): own rows straight into the receive buffer
+    for j, t in enumerate(tok_list[d]):
+        if d == rank:
+            recv_x[j] = torch.from_numpy(x[t]); recv_idx[j] = torch.from_numpy(idx[t])
+        else:
+            send_x[lay["send_off"][d] + j] = torch.from_numpy(x[t]); send_idx[lay["send_off"][d] + j] = torch.from_numpy(idx[t])
+def exchange(bufs):                         # bufs: list of (send tensor slice or None, recv tensor slice or None, peer)
+    reqs = []
+    for snd, rcv, p in bufs:
+        if rcv is not None: reqs.append(dist.irecv(rcv, src=p))
+    for snd, rcv, p in bufs:
+        if snd is not None: reqs.append(dist.isend(snd.contiguous(), dst=p))
+    for r in reqs: r.wait()
+seg = lambda buf, off, n: buf[off:off + n] if n > 0 else None
+peers = [p for p in range(world) if p != rank]
+exchange([(seg(send_x, lay["send_off"][p], lay["send_tok"][p]), seg(recv_x, lay["recv_off"][p], lay["recv_tok"][p]), p) for p in peers])
+exchange([(seg(send_idx, lay["send_off"][p], lay["send_tok"][p]), seg(recv_idx, lay["recv_off"][p], lay["recv_tok"][p]), p) for p in peers])
+# owner side: every received pair that hits a resident expert, in (segment, token, kk) order
+stream = [recv_x[j] * float(int(recv_idx[j, kk]) + 1) for j in range(R) for kk in range(k) if own[int(recv_idx[j, kk])] == rank]
+assert len(stream) == int(lay["recv_pair"].sum())
+self_pairs = int(lay["recv_pair"][rank])
+ret_recv = torch.zeros((max(int(lay["send_pair"].sum()), 1), H))
+for j in range(self_pairs): ret_recv[j] = stream[j]
+ret_send = torch.stack(stream[self_pairs:]) if len(stream) > self_pairs else torch.zeros((1, H))
+exchange([(seg(ret_send, lay["ret_send_off"][p], lay["recv_pair"][p]), seg(ret_recv, lay["ret_recv_off"][p], lay["send_pair"][p]), p) for p in peers])
+# home side: pair (t, kk) owned by d sits at ret_recv_off[d] + its rank among d's pairs
+out = np.zeros((Tl, H), np.float32)
+for d in range(world):
+    for j, (t, kk) in enumerate(pairs[d]):
+        out[t] += w[t, kk] * ret_recv[lay["ret_recv_off"][d] + j].numpy()
+want = np.zeros((Tl, H), np.float32)
 for t in range(Tl):
     for kk in range(k):
-        want[t] += w[t, kk] * (xf[t] * (int(i[t, kk]) + 1)).to(torch.bfloat16).float()
-want = (want + (xf * 0.5).to(torch.bfloat16).float()).to(torch.bfloat16)
-assert torch.allclose(out.float(), want.float(), rtol=2e-2, atol=1e-2), (out.float() - want.float()).abs().max()
+        want[t] += w[t, kk] * x[t] * float(idx[t, kk] + 1)
+assert np.allclose(out, want, rtol=1e-5, atol=1e-6), np.abs(out - want).max()
 # a rank with a different map must be refused before any exchange
 try:
-    verify_peers(ExpertSharding.balanced(2, E, [rank + 1] + [1] * (E - 1)) if rank == 1 else sh)
+    verify_peers(ExpertSharding.balanced(world, E, [rank + 1] + [1] * (E - 1)) if rank == 1 else sh)
     ok = False
 except RuntimeError:
     ok = True
@@ -145,12 +134,13 @@ print("OK", rank)
 """
 
 
-def test_two_rank_sharded_block_gloo(tmp_path):
+@pytest.mark.parametrize("world", [2, 3])
+def test_exchange_layout_agrees_between_ranks_gloo(tmp_path, world):
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
-    port = str(29000 + os.getpid() % 2000)
-    procs = [subprocess.Popen([sys.executable, str(script), ROOT, port, str(r)], stdout=subprocess.PIPE,
-                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    port = str(29000 + (os.getpid() * 7 + world) % 2000)
+    procs = [subprocess.Popen([sys.executable, str(script), ROOT, port, str(r), str(world)], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(world)]
     outs = []
     for p in procs:
         try:

@@ -1,4 +1,5 @@
-"""Expert parallelism on real GPUs (needs >= 2): NCCL all-to-all dispatch/combine against the oracle."""
+"""Expert parallelism on real GPUs (needs >= 2): the one-call expert-parallel block (token rows
+exchanged with NCCL send/recv) against the oracle."""
 import os
 import subprocess
 import sys

@@ -388,6 +388,71 @@ def test_stage_calls_emulate_expert_parallel(gpu_backend, orc, world, name):
         b.close()
 
 
+@pytest.mark.parametrize("world,name,T,balanced", [(2, "tiny_sig", 37, False), (4, "tiny_sig", 150, False), (3, "tiny_zipf", 70, True),
+                                                    (2, "mid", 512, False), (8, "mid", 1000, True), (2, "tiny", 5, False)])
+def test_expert_parallel_call_emulated_on_one_gpu(gpu_backend, orc, world, name, T, balanced):
+    """The expert-parallel block call with `world` handles on ONE GPU (coli_b200_moe_block_ep_emulate:
+    same kernels, same offsets, the two exchanges done as device copies): ragged token shards (one
+    of them empty), contiguous and LPT expert maps, a rank that owns no expert of some tokens.
+    Routing must be exact and every rank's output within the bar against the oracle; and because
+    result rows return unweighted and the home rank combines, the output must equal the single-GPU
+    block's bit for bit when both take the same kernel family."""
+    import ctypes as C
+
+    import torch
+
+    from speedycolibri_b200 import _lib
+    from speedycolibri_b200.cluster import ExpertSharding, ep_layout, rows_per_rank
+
+    lib = _lib.load()
+    shape = CONFIGS[name].with_tokens(T)
+    L, packed = host_layer(shape)
+    x_all = synth.host_tokens(shape, T)
+    want = L.moe_block(x_all)
+    load = np.bincount(want["idx"].reshape(-1), minlength=shape.E).tolist()
+    sh = ExpertSharding.balanced(world, shape.E, load) if balanced else ExpertSharding.new(world, shape.E)
+    # ragged shards; rank 1 gets nothing when there are more than two ranks
+    cut = np.linspace(0, T, world + 1).astype(int)
+    if world > 2:
+        cut[2] = cut[1]
+    blocks, xs, outs = [], [], []
+    for r in range(world):
+        layer = upload_layer(shape, packed, local=set(sh.local_experts(r)))
+        blocks.append(make_block(shape, layer, max_tokens=T, ep_rank=r, ep_world=world,
+                                 expert_owner=sh.owner_table() if balanced else None))
+        xs.append(torch.from_numpy(x_all[cut[r]:cut[r + 1]].view(np.int16).copy()).cuda().view(torch.bfloat16).reshape(-1, shape.H))
+        outs.append(torch.zeros_like(xs[-1]))
+    hp = (C.c_void_p * world)(*[b.handle for b in blocks])
+    xp = (C.c_void_p * world)(*[t.data_ptr() if t.numel() else None for t in xs])
+    op = (C.c_void_p * world)(*[t.data_ptr() if t.numel() else None for t in outs])
+    tl = (C.c_int * world)(*[int(t.shape[0]) for t in xs])
+    for rep in range(2):  # buffers are reused
+        ok = lib.coli_b200_moe_block_ep_emulate(hp, world, xp, op, tl, None)
+        assert ok == 1, lib.coli_cuda_last_error().decode()
+    torch.cuda.synchronize()
+    for r, b in enumerate(blocks):
+        b.check()
+        n = int(tl[r])
+        if n == 0:
+            continue
+        idx, w = b.last_routing(n)
+        assert np.array_equal(idx, want["idx"][cut[r]:cut[r + 1]])
+        assert np.array_equal(w.view(np.uint32), want["w"][cut[r]:cut[r + 1]].view(np.uint32))
+        got = outs[r].view(torch.int16).cpu().numpy().view(np.uint16)
+        err = rel_l2(got, want["out"][cut[r]:cut[r + 1]])
+        assert err <= 5e-3, (r, err)
+    # the count table: every pair is computed exactly once, by the rank that owns its expert
+    tab = blocks[0].ep_last_counts()
+    assert tab[:, 1, :].sum() == T * shape.k
+    own = np.array(sh.owner_table())
+    assert rows_per_rank(tab).tolist() == [int((own[want["idx"]] == r).sum()) for r in range(world)]
+    for r in range(world):
+        lay = ep_layout(tab, r)
+        assert lay["send_tok"].sum() <= int(tl[r]) * min(shape.k, world) and lay["recv_off"][r] == 0
+    for b in blocks:
+        b.close()
+
+
 def test_tracing_phases_and_launch_count(gpu_backend):
     import torch
     from speedycolibri_b200 import _lib
