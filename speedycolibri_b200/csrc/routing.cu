@@ -14,6 +14,8 @@
 //     CF_* round-to-nearest intrinsics;
 //   * the arg-max of each round is the largest value with the lowest index, which is what the
 //     ascending strict-`>` scan returns; a round with no candidate above -inf returns 0.
+#include <cstdlib>
+
 #include "internal.cuh"
 
 namespace colib {
@@ -188,6 +190,129 @@ __global__ void __launch_bounds__(NT) k_router_gemm_big(RouteParams p) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int m = m0 + ty * TMR + i, n = n0 + tx * 4 + j;
+      if (m < p.T && n < p.E) {
+        float v = acc[i][j];
+        if (p.logit_bias) v = __fadd_rn(v, p.logit_bias[n]);
+        p.logits[(size_t)m * p.E + n] = v;
+      }
+    }
+}
+
+// Router GEMM, register-tiled: every thread owns TM tokens x TN experts (TM*TN independent
+// k-ascending fmaf chains), a CTA of NT threads covers (NT/16)*TM tokens x 16*TN experts.  The
+// kernel is bound by the shared-memory operand traffic per FMA, (TM + TN) / (TM * TN) words: an
+// 8 x 8 tile needs a quarter of what a 2 x 4 tile does, so large batches take the largest tile and
+// small ones the largest tile that still gives every SM a CTA.  Operands are staged as f32,
+// transposed (k-major), two buffers, 16-byte loads one chunk ahead; a thread's experts are
+// {tx*4 + j} in each 64-wide group, so the 16 lanes of a row read consecutive 16-byte words.
+// Same arithmetic as the other router kernels: the tile shape never changes an output's k order.
+// Needs H % 8 == 0.
+template <int TM, int TN, int NT>
+__global__ void __launch_bounds__(NT) k_router_rt(RouteParams p) {
+  static_assert(TN % 4 == 0 && (TM % 4 == 0 || TM == 2), "tile shape");
+  constexpr int BM = (NT / 16) * TM, BN = 16 * TN, BK = 32, LDX = BM + 4, LDW = BN + 4;
+  constexpr int SR = NT / 4;  // rows staged per pass (4 chunks of 8 k each)
+  constexpr int XP = (BM + SR - 1) / SR, WP = (BN + SR - 1) / SR;
+  extern __shared__ __align__(16) float rsm[];
+  float(*xs)[BK][LDX] = reinterpret_cast<float(*)[BK][LDX]>(rsm);
+  float(*ws)[BK][LDW] = reinterpret_cast<float(*)[BK][LDW]>(rsm + 2 * BK * LDX);
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  float acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+  const int sr = threadIdx.x % SR, sc = threadIdx.x / SR;
+  uint4 xv[XP], wv[WP];
+  auto fetch = [&](int k0) {
+    const int k = k0 + sc * 8;
+#pragma unroll
+    for (int h = 0; h < XP; ++h) {
+      const int r = sr + SR * h, m = m0 + r;
+      xv[h] = make_uint4(0, 0, 0, 0);
+      if (r < BM && m < p.T && k < p.H) xv[h] = *reinterpret_cast<const uint4 *>(p.x + (size_t)m * p.H + k);
+    }
+#pragma unroll
+    for (int h = 0; h < WP; ++h) {
+      const int r = sr + SR * h, n = n0 + r;
+      wv[h] = make_uint4(0, 0, 0, 0);
+      if (r < BN && n < p.E && k < p.H) wv[h] = *reinterpret_cast<const uint4 *>(p.router_w + (size_t)n * p.H + k);
+    }
+  };
+  auto stage = [&](int buf) {
+#pragma unroll
+    for (int h = 0; h < XP; ++h) {
+      const int r = sr + SR * h;
+      if (r < BM) {
+        const uint32_t u[4] = {xv[h].x, xv[h].y, xv[h].z, xv[h].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          xs[buf][sc * 8 + 2 * j][r] = __uint_as_float(u[j] << 16);
+          xs[buf][sc * 8 + 2 * j + 1][r] = __uint_as_float(u[j] & 0xffff0000u);
+        }
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < WP; ++h) {
+      const int r = sr + SR * h;
+      if (r < BN) {
+        const uint32_t u[4] = {wv[h].x, wv[h].y, wv[h].z, wv[h].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          ws[buf][sc * 8 + 2 * j][r] = __uint_as_float(u[j] << 16);
+          ws[buf][sc * 8 + 2 * j + 1][r] = __uint_as_float(u[j] & 0xffff0000u);
+        }
+      }
+    }
+  };
+  fetch(0);
+  stage(0);
+  __syncthreads();
+  if (BK < p.H) fetch(BK);
+  int buf = 0;
+  for (int k0 = 0; k0 < p.H; k0 += BK, buf ^= 1) {
+#pragma unroll 4
+    for (int kk = 0; kk < BK; ++kk) {
+      float a[TM], b[TN];
+      if (TM == 2) {
+        const float2 v = *reinterpret_cast<const float2 *>(&xs[buf][kk][ty * 2]);
+        a[0] = v.x;
+        a[TM - 1] = v.y;
+      } else {
+#pragma unroll
+        for (int q = 0; q < TM / 4; ++q) {
+          const float4 v = *reinterpret_cast<const float4 *>(&xs[buf][kk][ty * TM + 4 * q]);
+          a[4 * q] = v.x;
+          a[4 * q + 1] = v.y;
+          a[4 * q + 2] = v.z;
+          a[4 * q + 3] = v.w;
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < TN / 4; ++q) {
+        const float4 v = *reinterpret_cast<const float4 *>(&ws[buf][kk][q * 64 + tx * 4]);
+        b[4 * q] = v.x;
+        b[4 * q + 1] = v.y;
+        b[4 * q + 2] = v.z;
+        b[4 * q + 3] = v.w;
+      }
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+    }
+    if (k0 + BK < p.H) {
+      stage(buf ^ 1);
+      if (k0 + 2 * BK < p.H) fetch(k0 + 2 * BK);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      const int m = m0 + ty * TM + i, n = n0 + (j >> 2) * 64 + tx * 4 + (j & 3);
       if (m < p.T && n < p.E) {
         float v = acc[i][j];
         if (p.logit_bias) v = __fadd_rn(v, p.logit_bias[n]);
@@ -414,6 +539,45 @@ static bool launch_router_big(const RouteParams &p, dim3 grid, cudaStream_t st) 
   return true;
 }
 
+template <int TM, int TN, int NT>
+static bool launch_router_rt(const RouteParams &p, cudaStream_t st) {
+  constexpr int BM = (NT / 16) * TM, BN = 16 * TN;
+  constexpr size_t smem = (size_t)2 * 32 * ((BM + 4) + (BN + 4)) * sizeof(float);
+  static ColiPerDeviceOnce attr_once;
+  if (smem > 48 * 1024 && !coli_set_smem_limit(attr_once, k_router_rt<TM, TN, NT>, smem, "router shared-memory attribute")) return false;
+  dim3 grid((p.E + BN - 1) / BN, (p.T + BM - 1) / BM);
+  k_router_rt<TM, TN, NT><<<grid, NT, smem, st>>>(p);
+  return true;
+}
+// The register-tiled variants, largest tile first; `force` (1-based, from COLI_ROUTER_TILE, a
+// measurement aid) picks one regardless of the batch.  Returns -1 when none applies.
+static int launch_router_tiled(const RouteParams &p, cudaStream_t st) {
+  if (p.H % 8 != 0 || p.E < 64) return -1;
+  const char *fe = getenv("COLI_ROUTER_TILE");
+  const int force = fe ? atoi(fe) : 0;
+  auto ctas = [&](int bm, int bn) { return (long)((p.T + bm - 1) / bm) * ((p.E + bn - 1) / bn); };
+  int pick = force;
+  if (pick <= 0) {
+    // Measured on B200 (H = 7168 / 6144): the 8 x 8 tile pays once a batch gives every SM well over one
+    // 128 x 128 CTA (T = 16384, E = 384: 1.92 ms against 2.17); below that the narrower tiles of
+    // k_router_gemm_big, which keep two warps per scheduler, are as fast or faster.
+    if (p.E >= 128 && ctas(128, 128) >= 240) pick = 7;
+    else return -1;
+  }
+  bool ok = false;
+  switch (pick) {
+    case 1: ok = launch_router_rt<8, 8, 128>(p, st); break;   // 64 tokens x 128 experts
+    case 2: ok = launch_router_rt<4, 8, 128>(p, st); break;   // 32 x 128
+    case 3: ok = launch_router_rt<4, 4, 128>(p, st); break;   // 32 x 64
+    case 4: ok = launch_router_rt<4, 4, 64>(p, st); break;    // 16 x 64, two warps
+    case 5: ok = launch_router_rt<2, 4, 64>(p, st); break;    // 8 x 64
+    case 6: ok = launch_router_rt<8, 4, 128>(p, st); break;   // 64 x 64
+    case 7: ok = launch_router_rt<8, 8, 256>(p, st); break;   // 128 x 128
+    default: return -1;
+  }
+  return ok ? 1 : 0;
+}
+
 int launch_router(const RouteParams &p, cudaStream_t st) {
   if (p.T <= 0) return 1;
   if (p.E > 32 * kMaxSlots) {
@@ -433,6 +597,9 @@ int launch_router(const RouteParams &p, cudaStream_t st) {
     static ColiPerDeviceOnce attr_once;
     if (!coli_set_smem_limit(attr_once, k_router_decode, 200 * 1024, "decode router shared-memory attribute")) return 0;
     k_router_decode<<<(p.E + 7) / 8, 256, dec_smem, st>>>(p);  // 256 threads stage the rows, T*8 of them walk the chains
+    coli_count_launch(1);
+  } else if (const int tiled = launch_router_tiled(p, st); tiled >= 0) {
+    if (tiled == 0) return 0;
     coli_count_launch(1);
   } else {
     // the largest tile that still covers the SMs; every variant has identical arithmetic
@@ -778,7 +945,8 @@ int launch_permute(const PermuteParams &p, cudaStream_t st) {
   }
   const int nchunk = (p.T + 31) / 32;
   const int max_items = permute_max_items(p);
-  if (permute_small_ok(p)) {
+  // the one-CTA form also gathers the rows: fine for a decode batch, far too slow for hundreds of rows
+  if (permute_small_ok(p) && (!p.xg || p.T * (p.k + 1) <= 96)) {
     int conv = 0;
     if (p.x16) {
       const size_t n = (size_t)p.T * p.H / 8;

@@ -123,20 +123,32 @@ def test_expert_group_nvfp4_prefill_rows_take_the_tcgen05_path(gpu_backend, orc)
 
 
 def test_host_calls_take_genuine_f32_activations(gpu_backend, orc):
-    """x that is not bf16-representable: the call rounds it to f16 (11 significant bits), so the
-    result tracks the f32-activation oracle far closer than a bf16 rounding (8 bits) would."""
+    """The host-f32 calls round x to f16 (11 significant bits), not to bf16 (8): a one-hot x of
+    1 + 2^-9 — exact in f16, rounded to 1.0 by bf16 — must come back as that multiple of the weight
+    column; and an expert call on x that is not bf16-representable stays inside the bar."""
     shape = CONFIGS["tiny_sig"]
     L, packed = host_layer(shape)
+    q, s, g = packed["experts"][1][0]  # gate of expert 1: [I, H]
+    W = orc.dequant(orc.FMT_NVFP4, q, s, g, shape.I, shape.H)
+    mm = gpu_backend.Nvfp4Matmul(q, s, g, shape.I, shape.H)
+    scale = np.float32(1.0 + 2.0 ** -9)
+    x = np.zeros((4, shape.H), np.float32)
+    cols = [0, 17, 64, shape.H - 1]
+    for r, c in enumerate(cols):
+        x[r, c] = scale
+    y = mm(x)
+    for r, c in enumerate(cols):
+        assert np.allclose(y[r], W[:, c] * scale, rtol=1e-6, atol=0.0), (r, c)
+        nz = np.abs(W[:, c]) > 0
+        assert nz.any() and not np.allclose(y[r][nz], W[:, c][nz], rtol=1e-4, atol=0.0)  # a bf16 rounding would give exactly W
+    mm.free()
     layer = upload_layer(shape, packed)
     rng = np.random.default_rng(5)
     x = rng.standard_normal((16, shape.H)).astype(np.float32)
     e = layer.experts[1]
     y = gpu_backend.expert_mlp_nvfp4(e.gate, e.up, e.down, x)
     want = L.expert_ffn(1, x)
-    err = np.linalg.norm(y - want) / np.linalg.norm(want)
-    via_bf16 = L.expert_ffn(1, synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(x)))
-    err_bf16 = np.linalg.norm(via_bf16 - want) / np.linalg.norm(want)
-    assert err <= 3e-3 and err < err_bf16, (err, err_bf16)
+    assert np.linalg.norm(y - want) / np.linalg.norm(want) <= 3e-3
 
 
 # ---- degenerate inputs --------------------------------------------------------------------------------------
