@@ -289,11 +289,17 @@ int coli_b200_moe_finish_dev(ColiMoe *moe, const float *partial_dev, const void 
  * owners run the grouped expert FFN over the rows they received and send the result row of every
  * (token, kk) pair back unweighted; the home rank applies the routing weights in the token's own kk
  * order and adds its shared expert, so the arithmetic is that of the single-GPU block.  The shared
- * expert runs on a second stream beside the exchange.  The call blocks the host once, for the
- * per-rank counts every send/recv needs (2 x world integers), and returns with the rest queued on
- * `stream`; it must be made by every rank of the communicator, in the same order.  Limits: at most
- * 8 ranks, k <= 16.  A rank that would receive more than max_tokens tokens fails the call on every
- * rank alike. */
+ * expert runs on a second stream beside the exchange.
+ * Transport.  By default ("direct") every rank keeps its receive buffers in one slab that the other
+ * ranks map at create time (cudaIpc handles, all-gathered over nccl_comm); the pack kernels store
+ * rows, expert ids and the per-rank counts straight into the destination's slab over NVLink, and a
+ * one-word NCCL all-gather after the stores is the barrier that tells a rank its senders are done.
+ * Nothing needs the host: the call only queues work on `stream`.  With COLI_EP_TRANSPORT=nccl in
+ * the environment when the handle is created, rows are packed into send buffers and exchanged with
+ * grouped ncclSend / ncclRecv instead; the host then waits once per call for the counts those need.
+ * The call must be made by every rank of the communicator, in the same order.  Limits: at most 8
+ * ranks, k <= 16; all ranks together may bring at most max_tokens tokens to a call (a call that
+ * brings more computes nothing for the overflowing rank and coli_b200_moe_check reports it). */
 int coli_b200_moe_block_ep_dev(ColiMoe *moe, const void *x_dev, void *out_dev, int T_local, void *stream);
 /* The same sequence for `world` handles of ONE process on ONE device (ranks[r] has ep_rank = r, no
  * communicator): phases run rank after rank on `stream`, the exchanges are device-to-device copies.

@@ -774,6 +774,9 @@ colib::PermuteParams coli_permute_params(ColiMoe *m, const void *x_dev, int T, b
   pp.xg = (__half *)rows_dev;
   pp.gather_shared = 0;
   pp.x16 = nullptr;
+  pp.virt = nullptr;
+  pp.rows_cap = 0x7fffffff;
+  pp.overflow = nullptr;
   return pp;
 }
 
@@ -934,7 +937,7 @@ extern "C" int coli_b200_moe_check(ColiMoe *m) {
     cudaMemset(m->status, 0, sizeof(int));
     return 0;
   }
-  return 1;
+  return coli_ep_check(m);
 }
 
 extern "C" int coli_b200_moe_last_routing(ColiMoe *m, int T, int32_t *topk_idx, float *topk_w) {

@@ -30,6 +30,7 @@
 #include <dlfcn.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "host_state.cuh"
@@ -133,6 +134,16 @@ struct ColiEp {
   int32_t *seg_count = nullptr;    // [n_local]
   int32_t *shared_cnt = nullptr;   // [1]
   SegScratch seg_shared;
+  // direct transport: rows are stored straight into the peers' receive buffers over NVLink
+  bool direct = false;
+  uint8_t *slab = nullptr;         // table + recv_meta + recv_x + ret_recv of THIS rank; peers write into it
+  uint8_t *peer_slab[EP_MAX_WORLD] = {};  // the same slab of every rank as mapped into this process (own entry = slab)
+  bool peer_mapped[EP_MAX_WORLD] = {};    // opened with cudaIpcOpenMemHandle (to be closed)
+  size_t table_off = 0, meta_off = 0, x_off = 0, ret_off = 0, slab_bytes = 0;
+  int tl_cap = 0;                  // rows per source segment of recv_x / recv_meta
+  struct EpRecvInfo *info = nullptr;  // device: what this rank received, derived from the table
+  int32_t *bar_src = nullptr, *bar_dst = nullptr;  // operands of the tiny collective used as a barrier
+  int *overflow = nullptr;         // device word: a batch exceeded the row buffers
   bool timing = false;
   cudaEvent_t ev_t[EPS_N + 1] = {};
   float stage_ms[EPS_N] = {};
@@ -154,6 +165,11 @@ __device__ __forceinline__ int warp_incl_scan(int v, int lane) {
   return v;
 }
 
+// The receive slab of every rank (own entry included), by value into the kernels that store to peers.
+struct EpPeers {
+  uint8_t *slab[EP_MAX_WORLD];
+};
+
 struct EpPlanParams {
   int T, k, E, world, rank;
   const int32_t *topk_idx;  // [T,k]
@@ -162,6 +178,9 @@ struct EpPlanParams {
   int32_t *send_off;        // [world] out
   int32_t *send_pos;        // [T*world] out
   int32_t *home_slot;       // [T*k] out
+  int publish;              // direct transport: store the counts into row `rank` of every rank's table
+  EpPeers peers;
+  size_t table_off;
 };
 
 // One CTA.  Warp w owns a contiguous range of 32-token chunks, so that positions ascend with the
@@ -238,6 +257,14 @@ __global__ void __launch_bounds__(1024) k_ep_plan(EpPlanParams p) {
       p.cnt[d] = tot_tok[d];
       p.cnt[p.world + d] = tot_pair[d];
     }
+  }
+  if (p.publish && threadIdx.x < (unsigned)p.world) {
+    int32_t *row = reinterpret_cast<int32_t *>(p.peers.slab[threadIdx.x] + p.table_off) + (size_t)p.rank * 2 * p.world;
+    for (int d = 0; d < p.world; ++d) {
+      row[d] = tot_tok[d];
+      row[p.world + d] = tot_pair[d];
+    }
+    __threadfence_system();
   }
   __syncthreads();
 #pragma unroll
@@ -365,6 +392,148 @@ __global__ void __launch_bounds__(256) k_ep_ret_pack(const __nv_bfloat16 *y, con
 
 __global__ void k_set_i32(int32_t *p, int32_t v) { *p = v; }
 
+// ---- direct transport -----------------------------------------------------------------------------------
+// Receive buffers have one fixed segment of tl_cap rows per source rank, so a sender needs nobody
+// else's counts to know where its rows go: token number `pos` of rank s's list for rank d is row
+// s * tl_cap + pos of d's recv_x.
+struct EpPackDirectParams {
+  int T, H, k, world, rank, tl_cap;
+  const __nv_bfloat16 *x;
+  const int32_t *topk_idx, *send_pos;
+  EpPeers peers;
+  size_t x_off, meta_off;
+};
+__global__ void __launch_bounds__(256) k_ep_pack_direct(EpPackDirectParams p) {
+  const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (t >= p.T) return;
+  uint4 *row[EP_MAX_WORLD];
+  int32_t *meta[EP_MAX_WORLD];
+#pragma unroll
+  for (int d = 0; d < EP_MAX_WORLD; ++d) {
+    row[d] = nullptr;
+    meta[d] = nullptr;
+    if (d < p.world) {
+      const int pos = p.send_pos[(size_t)t * p.world + d];
+      if (pos >= 0 && pos < p.tl_cap) {
+        const size_t r = (size_t)p.rank * p.tl_cap + pos;
+        row[d] = reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(p.peers.slab[d] + p.x_off) + r * p.H);
+        meta[d] = reinterpret_cast<int32_t *>(p.peers.slab[d] + p.meta_off) + r * p.k;
+      }
+    }
+  }
+  const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (size_t)t * p.H);
+  const int vec = p.H / 8;
+  for (int c = lane; c < vec; c += 32) {
+    const uint4 v = src[c];
+#pragma unroll
+    for (int d = 0; d < EP_MAX_WORLD; ++d)
+      if (row[d]) row[d][c] = v;
+  }
+  if (lane < p.k) {
+    const int32_t e = p.topk_idx[(size_t)t * p.k + lane];
+#pragma unroll
+    for (int d = 0; d < EP_MAX_WORLD; ++d)
+      if (meta[d]) meta[d][lane] = e;
+  }
+  __threadfence_system();
+}
+
+}  // namespace colib
+// What a rank received, derived on the device from its (complete) copy of the count table.
+struct EpRecvInfo {
+  colib::VirtualBatch vb;   // the received tokens: segments in this rank's order (own first), slot = source rank
+  int32_t pair_base[9];     // pairs that hit this rank's experts in the segments before each one
+  int32_t ret_dst_off[8];   // per segment: first row of this rank's results in the source's ret_recv
+  int32_t src_rank[8];
+};
+namespace colib {
+__global__ void k_ep_recv_layout(const int32_t *table, int world, int rank, int tl_cap, EpRecvInfo *info) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const int w2 = 2 * world;
+  int tok = 0, pair = 0;
+  info->vb.nseg = world;
+  info->vb.stride = tl_cap;
+  for (int pos = 0; pos < world; ++pos) {
+    const int s = ep_rank_at(pos, rank);
+    int n = table[s * w2 + rank];
+    n = n < 0 ? 0 : (n > tl_cap ? tl_cap : n);
+    info->vb.off[pos] = tok;
+    info->vb.phys[pos] = s;
+    info->src_rank[pos] = s;
+    info->pair_base[pos] = pair;
+    tok += n;
+    pair += table[s * w2 + world + rank];
+    // where rank s expects the results of this rank: its own first, then the others ascending
+    int off = 0;
+    if (rank != s) {
+      off = table[s * w2 + world + s];
+      for (int d = 0; d < rank; ++d)
+        if (d != s) off += table[s * w2 + world + d];
+    }
+    info->ret_dst_off[pos] = off;
+  }
+  info->vb.off[world] = tok;
+  info->vb.total = tok;
+  info->pair_base[world] = pair;
+}
+
+// k_ep_ret_plan over a batch whose size is known on the device only
+__global__ void __launch_bounds__(1024) k_ep_ret_plan_virt(const int32_t *slot, const EpRecvInfo *info, int k, int32_t *ret_pos) {
+  __shared__ int w_cnt[32];
+  const int n = info->vb.total * k;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nchunk = (n + 31) / 32, cpw = (nchunk + 31) / 32;
+  const int c0 = min(nchunk, warp * cpw), c1 = min(nchunk, c0 + cpw);
+  int cnt = 0;
+  for (int c = c0; c < c1; ++c) {
+    const int i = c * 32 + lane;
+    cnt += __popc(__ballot_sync(0xffffffffu, i < n && slot[i] >= 0));
+  }
+  if (lane == 0) w_cnt[warp] = cnt;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int a = w_cnt[w];
+      w_cnt[w] = run;
+      run += a;
+    }
+  }
+  __syncthreads();
+  int base = w_cnt[warp];
+  const unsigned lt = (1u << lane) - 1u;
+  for (int c = c0; c < c1; ++c) {
+    const int i = c * 32 + lane;
+    const bool v = i < n && slot[i] >= 0;
+    const unsigned bal = __ballot_sync(0xffffffffu, v);
+    if (i < n) ret_pos[i] = v ? base + __popc(bal & lt) : -1;
+    base += __popc(bal);
+  }
+}
+
+// One warp per received pair: its result row is stored into the ret_recv of the token's home rank.
+__global__ void __launch_bounds__(256) k_ep_ret_pack_direct(const __nv_bfloat16 *y, const int32_t *slot, const int32_t *ret_pos,
+                                                            const EpRecvInfo *info, int k, int H, int ret_rows_cap, EpPeers peers,
+                                                            size_t ret_off, int *overflow) {
+  const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (i >= info->vb.total * k) return;
+  const int pos = ret_pos[i];
+  if (pos < 0) return;
+  const int j = i / k;
+  int s = 0;
+  while (s + 1 < info->vb.nseg && j >= info->vb.off[s + 1]) ++s;
+  const int row = info->ret_dst_off[s] + (pos - info->pair_base[s]);
+  if (row < 0 || row >= ret_rows_cap) {
+    if (lane == 0 && overflow) atomicExch(overflow, 1);
+    return;
+  }
+  const uint4 *src = reinterpret_cast<const uint4 *>(y + (size_t)slot[i] * H);
+  uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(peers.slab[info->src_rank[s]] + ret_off) + (size_t)row * H);
+  const int vec = H / 8;
+  for (int c = lane; c < vec; c += 32) dst[c] = src[c];
+  __threadfence_system();
+}
+
 }  // namespace colib
 
 // ---- host side ------------------------------------------------------------------------------------------
@@ -438,9 +607,28 @@ int ep_phase_a(ColiMoe *m, const void *x_dev, int T, cudaStream_t st) {
   pl.send_off = ep->send_off;
   pl.send_pos = ep->send_pos;
   pl.home_slot = ep->home_slot;
+  pl.publish = ep->direct ? 1 : 0;
+  for (int d = 0; d < EP_MAX_WORLD; ++d) pl.peers.slab[d] = ep->peer_slab[d];
+  pl.table_off = ep->table_off;
   colib::k_ep_plan<<<1, 1024, 0, st>>>(pl);
   coli_count_launch(1);
-  if (T > 0) {
+  if (T > 0 && ep->direct) {
+    colib::EpPackDirectParams pk;
+    pk.T = T;
+    pk.H = m->L.H;
+    pk.k = m->L.k;
+    pk.world = ep->world;
+    pk.rank = ep->rank;
+    pk.tl_cap = ep->tl_cap;
+    pk.x = (const __nv_bfloat16 *)x_dev;
+    pk.topk_idx = m->topk_idx;
+    pk.send_pos = ep->send_pos;
+    pk.peers = pl.peers;
+    pk.x_off = ep->x_off;
+    pk.meta_off = ep->meta_off;
+    colib::k_ep_pack_direct<<<(T + 7) / 8, 256, 0, st>>>(pk);
+    coli_count_launch(1);
+  } else if (T > 0) {
     colib::EpPackParams pk;
     pk.T = T;
     pk.H = m->L.H;
@@ -520,7 +708,7 @@ int ep_phase_c(ColiMoe *m, void *out_dev, int T, cudaStream_t st) {
     cp.H = m->L.H;
     cp.k = m->L.k;
     cp.has_shared = m->has_shared ? 1 : 0;
-    cp.y = ep->ret_recv;
+    cp.y = ep->direct ? reinterpret_cast<const __nv_bfloat16 *>(ep->slab + ep->ret_off) : ep->ret_recv;
     cp.shared_y = ep->shared_y;
     cp.slot = ep->home_slot;
     cp.topk_w = m->topk_w;
@@ -530,6 +718,44 @@ int ep_phase_c(ColiMoe *m, void *out_dev, int T, cudaStream_t st) {
     if (!colib::launch_combine(cp, st)) return 0;
   }
   EP_MARK(9);
+  return 1;
+}
+
+// Direct transport, after the barrier that follows the dispatch stores: every peer's rows and counts
+// are in this rank's slab.  Nothing here needs the host to know a count: grids are sized from the
+// handle's capacity and the kernels read the actual sizes from the device.
+int ep_direct_phase_b(ColiMoe *m, cudaStream_t st) {
+  ColiEp *ep = m->ep;
+  const int k = m->L.k, H = m->L.H, cap_tok = m->max_tokens;
+  const long rows_cap = (long)cap_tok * k;
+  colib::k_ep_recv_layout<<<1, 32, 0, st>>>(reinterpret_cast<const int32_t *>(ep->slab + ep->table_off), ep->world, ep->rank, ep->tl_cap, ep->info);
+  coli_count_launch(1);
+  EP_MARK(4);
+  colib::PermuteParams pp = coli_permute_params(m, ep->slab + ep->x_off, cap_tok, false, colib::TC_MAX_TOKENS, ep->rows, ep->seg_count, ep->recv_slot);
+  pp.topk_idx = reinterpret_cast<const int32_t *>(ep->slab + ep->meta_off);
+  pp.expert_slot = m->local_slot;
+  pp.nseg_routed = m->n_local_seg;
+  pp.virt = &ep->info->vb;
+  pp.rows_cap = (int)rows_cap;
+  pp.overflow = ep->overflow;
+  if (!colib::launch_permute(pp, st)) return 0;
+  EP_MARK(5);
+  if (m->n_local_seg > 0) {
+    const long expect = rows_cap / ep->world;
+    if (!coli_run_segments(m, m->seg_main, m->gate, m->up, m->down, m->seg_expert + m->first_local_seg, ep->rows, ep->seg_count,
+                           m->n_local_seg, (int)rows_cap, (int)(expect > 0 ? expect : 1), m->y, st))
+      return 0;
+  }
+  EP_MARK(6);
+  colib::k_ep_ret_plan_virt<<<1, 1024, 0, st>>>(ep->recv_slot, ep->info, k, ep->ret_pos);
+  coli_count_launch(1);
+  colib::EpPeers peers;
+  for (int d = 0; d < EP_MAX_WORLD; ++d) peers.slab[d] = ep->peer_slab[d];
+  colib::k_ep_ret_pack_direct<<<(unsigned)((rows_cap + 7) / 8), 256, 0, st>>>(m->y, ep->recv_slot, ep->ret_pos, ep->info, k, H,
+                                                                             ep->tl_cap * k, peers, ep->ret_off, ep->overflow);
+  coli_count_launch(1);
+  CK(cudaGetLastError(), "return store launch");
+  EP_MARK(7);
   return 1;
 }
 
@@ -562,10 +788,44 @@ int ep_finish_timing(ColiMoe *m) {
 
 }  // namespace
 
+// Direct transport: every rank publishes the IPC handle of its receive slab (all-gathered with the
+// communicator) and maps the slabs of the others.
+static bool ep_connect_direct(ColiMoe *m) {
+  ColiEp *ep = m->ep;
+  NcclApi *api = nccl_api();
+  if (!api) return false;
+  const int world = ep->world, rank = ep->rank;
+  cudaIpcMemHandle_t mine;
+  if (!coli_cuda_check(cudaIpcGetMemHandle(&mine, ep->slab), "cudaIpcGetMemHandle")) return false;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  uint8_t *dbuf = nullptr;
+  std::vector<cudaIpcMemHandle_t> all(world);
+  cudaStream_t st = m->ctx->stream;
+  bool ok = coli_cuda_check(cudaMalloc((void **)&dbuf, (size_t)64 * world), "handle buffer") &&
+            coli_cuda_check(cudaMemcpyAsync(dbuf + (size_t)64 * rank, &mine, 64, cudaMemcpyHostToDevice, st), "handle upload") &&
+            nccl_ok(api, api->AllGather(dbuf + (size_t)64 * rank, dbuf, 64, COLI_NCCL_INT8, ep->comm, st), "handle all-gather") &&
+            coli_cuda_check(cudaMemcpyAsync(all.data(), dbuf, (size_t)64 * world, cudaMemcpyDeviceToHost, st), "handle download") &&
+            coli_cuda_check(cudaStreamSynchronize(st), "handle exchange");
+  for (int p = 0; ok && p < world; ++p) {
+    if (p == rank) continue;
+    void *ptr = nullptr;
+    ok = coli_cuda_check(cudaIpcOpenMemHandle(&ptr, all[p], cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+    if (ok) {
+      ep->peer_slab[p] = (uint8_t *)ptr;
+      ep->peer_mapped[p] = true;
+    }
+  }
+  if (dbuf) cudaFree(dbuf);
+  return ok;
+}
+
 int coli_ep_ensure(ColiMoe *m, void *comm) {
   if (!m) return 0;
   if (m->ep) {
-    if (comm && !m->ep->comm) m->ep->comm = (ncclComm_t)comm;
+    if (comm && !m->ep->comm) {
+      m->ep->comm = (ncclComm_t)comm;
+      if (m->ep->direct && !ep_connect_direct(m)) return 0;
+    }
     return 1;
   }
   const int world = m->L.ep_world, rank = m->L.ep_rank, k = m->L.k, H = m->L.H, E = m->L.E;
@@ -593,11 +853,37 @@ int coli_ep_ensure(ColiMoe *m, void *comm) {
             coli_cuda_check(cudaEventCreateWithFlags(&ep->ev_counts, cudaEventDisableTiming), "event creation") &&
             coli_cuda_check(cudaMallocHost((void **)&ep->h_all_cnt, sizeof(int32_t) * 2 * world * world), "pinned allocation");
   ok = ok && ws_alloc(m, &ep->owner, (size_t)E) && ws_alloc(m, &ep->cnt, 2 * (size_t)world) && ws_alloc(m, &ep->send_off, (size_t)world) &&
-       ws_alloc(m, &ep->all_cnt, 2 * (size_t)world * world) && ws_alloc(m, &ep->send_pos, T * world) &&
-       ws_alloc(m, &ep->home_slot, T * k) && ws_alloc(m, &ep->send_x, send_rows * H) && ws_alloc(m, &ep->send_meta, send_rows * k) &&
-       ws_alloc(m, &ep->recv_x, T * H) && ws_alloc(m, &ep->recv_meta, T * k) && ws_alloc(m, &ep->recv_slot, T * k) &&
-       ws_alloc(m, &ep->ret_pos, T * k) && ws_alloc(m, &ep->ret_send, T * k * H) && ws_alloc(m, &ep->ret_recv, T * k * H) &&
-       ws_alloc(m, &ep->seg_count, (size_t)(m->n_local_seg > 0 ? m->n_local_seg : 1)) && ws_alloc(m, &ep->shared_cnt, 1);
+       ws_alloc(m, &ep->send_pos, T * world) && ws_alloc(m, &ep->home_slot, T * k) && ws_alloc(m, &ep->recv_slot, T * k) &&
+       ws_alloc(m, &ep->ret_pos, T * k) && ws_alloc(m, &ep->seg_count, (size_t)(m->n_local_seg > 0 ? m->n_local_seg : 1)) &&
+       ws_alloc(m, &ep->shared_cnt, 1) && ws_alloc(m, &ep->overflow, 1) &&
+       coli_cuda_check(cudaMemset(ep->overflow, 0, sizeof(int)), "flag clear");
+  // Transport.  "direct" (default): every rank's receive buffers sit in one slab that the peers map
+  // (cudaIpc) and store into over NVLink; "nccl" (COLI_EP_TRANSPORT=nccl, or when the slab cannot be
+  // shared): rows are packed into send buffers and exchanged with ncclSend / ncclRecv.
+  const char *tr = getenv("COLI_EP_TRANSPORT");
+  ep->direct = !(tr && strcmp(tr, "nccl") == 0);
+  if (ok && ep->direct) {
+    auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    ep->tl_cap = m->max_tokens;
+    ep->table_off = 0;
+    ep->meta_off = up(sizeof(int32_t) * 2 * world * world);
+    ep->x_off = ep->meta_off + up(sizeof(int32_t) * (size_t)world * ep->tl_cap * k);
+    ep->ret_off = ep->x_off + up(sizeof(__nv_bfloat16) * (size_t)world * ep->tl_cap * H);
+    ep->slab_bytes = ep->ret_off + up(sizeof(__nv_bfloat16) * (size_t)ep->tl_cap * k * H);
+    ok = coli_cuda_check(cudaMalloc((void **)&ep->slab, ep->slab_bytes), "receive slab allocation");
+    if (ok) {
+      m->allocs.push_back(ep->slab);
+      m->ws_bytes += ep->slab_bytes;
+      ep->peer_slab[rank] = ep->slab;
+      ok = coli_cuda_check(cudaMemset(ep->slab, 0, ep->meta_off), "table clear") && ws_alloc(m, &ep->info, 1) &&
+           ws_alloc(m, &ep->bar_src, 1) && ws_alloc(m, &ep->bar_dst, (size_t)world);
+    }
+    if (ok && comm && !ep_connect_direct(m)) ok = false;
+  } else if (ok) {
+    ok = ws_alloc(m, &ep->all_cnt, 2 * (size_t)world * world) && ws_alloc(m, &ep->send_x, send_rows * H) &&
+         ws_alloc(m, &ep->send_meta, send_rows * k) && ws_alloc(m, &ep->recv_x, T * H) && ws_alloc(m, &ep->recv_meta, T * k) &&
+         ws_alloc(m, &ep->ret_send, T * k * H) && ws_alloc(m, &ep->ret_recv, T * k * H);
+  }
   if (ok) {
     if (m->xg) {
       ep->rows = m->xg;  // the block's own gathered-row buffer: (T*k + T) rows
@@ -631,8 +917,23 @@ void coli_ep_destroy(ColiMoe *m) {
   for (int i = 0; i <= EPS_N; ++i)
     if (ep->ev_t[i]) cudaEventDestroy(ep->ev_t[i]);
   if (ep->h_all_cnt) cudaFreeHost(ep->h_all_cnt);
+  for (int p = 0; p < EP_MAX_WORLD; ++p)
+    if (ep->peer_mapped[p] && ep->peer_slab[p]) cudaIpcCloseMemHandle(ep->peer_slab[p]);
   delete ep;  // device buffers are in the handle's allocation list; the communicator belongs to the caller
   m->ep = nullptr;
+}
+
+// 1 if no expert-parallel call of this handle ran out of row capacity since the last check.
+int coli_ep_check(ColiMoe *m) {
+  if (!m || !m->ep || !m->ep->overflow) return 1;
+  int v = 0;
+  CK(cudaMemcpy(&v, m->ep->overflow, sizeof(int), cudaMemcpyDeviceToHost), "flag read");
+  if (v != 0) {
+    cudaMemset(m->ep->overflow, 0, sizeof(int));
+    coli_set_error("an expert-parallel call brought more tokens than the handle's max_tokens=%d holds; its results are invalid", m->max_tokens);
+    return 0;
+  }
+  return 1;
 }
 
 // ---- communicator helpers: for callers that have no ncclComm_t of their own -------------------------------
@@ -682,8 +983,14 @@ extern "C" int coli_b200_ep_stage_ms(ColiMoe *m, float *ms, int *calls) {
   return 1;
 }
 extern "C" int coli_b200_ep_last_counts(ColiMoe *m, int32_t *table) {
-  if (!m || !m->ep || !table) return 0;
-  memcpy(table, m->ep->h_all_cnt, sizeof(int32_t) * 2 * m->ep->world * m->ep->world);
+  if (!m || !m->ep || !table || !coli_select_ctx(m->ctx)) return 0;
+  const size_t bytes = sizeof(int32_t) * 2 * m->ep->world * m->ep->world;
+  if (m->ep->direct) {  // the table lives in the slab; nothing on the host has seen it yet
+    CK(cudaDeviceSynchronize(), "count read sync");
+    CK(cudaMemcpy(table, m->ep->slab + m->ep->table_off, bytes, cudaMemcpyDeviceToHost), "count read");
+    return 1;
+  }
+  memcpy(table, m->ep->h_all_cnt, bytes);
   return 1;
 }
 
@@ -718,6 +1025,16 @@ extern "C" int coli_b200_moe_block_ep_dev(ColiMoe *m, const void *x_dev, void *o
   cudaStream_t st = (cudaStream_t)stream;
   const int world = ep->world, rank = ep->rank, H = m->L.H, k = m->L.k;
   if (!ep_phase_a(m, x_dev, T_local, st)) return 0;
+  if (ep->direct) {
+    // the rows and counts were stored straight into the peers' slabs; a tiny collective after the stores
+    // is the barrier that tells every rank that all of its senders are done (and nothing needs the host)
+    if (!nccl_ok(api, api->AllGather(ep->bar_src, ep->bar_dst, 1, COLI_NCCL_INT32, ep->comm, st), "dispatch barrier")) return 0;
+    EP_MARK(3);
+    if (!ep_direct_phase_b(m, st)) return 0;
+    if (!nccl_ok(api, api->AllGather(ep->bar_src, ep->bar_dst, 1, COLI_NCCL_INT32, ep->comm, st), "return barrier")) return 0;
+    if (!ep_phase_c(m, out_dev, T_local, st)) return 0;
+    return ep_finish_timing(m);
+  }
   // counts: every rank's 2 x world figures to every rank, then to the host
   if (!nccl_ok(api, api->AllGather(ep->cnt, ep->all_cnt, (size_t)2 * world, COLI_NCCL_INT32, ep->comm, st), "count all-gather")) return 0;
   CK(cudaMemcpyAsync(ep->h_all_cnt, ep->all_cnt, sizeof(int32_t) * 2 * world * world, cudaMemcpyDeviceToHost, st), "count download");
@@ -777,6 +1094,27 @@ extern "C" int coli_b200_moe_block_ep_emulate(ColiMoe *const *ranks, int world, 
     }
   }
   const int H = ranks[0]->L.H, k = ranks[0]->L.k;
+  if (ranks[0]->ep->direct) {  // the slabs of the other handles are plain pointers in this process
+    for (int r = 0; r < world; ++r) {
+      if (!ranks[r]->ep->direct || ranks[r]->max_tokens != ranks[0]->max_tokens) {
+        coli_set_error("moe_block_ep_emulate: all handles must use the same transport and max_tokens");
+        return 0;
+      }
+      for (int j = 0; j < world; ++j) ranks[r]->ep->peer_slab[j] = ranks[j]->ep->slab;
+    }
+    for (int r = 0; r < world; ++r)
+      if (!ep_phase_a(ranks[r], x_dev[r], T_local[r], st)) return 0;
+    for (int r = 0; r < world; ++r) {  // stream order is the barrier here
+      ColiEp *ep = ranks[r]->ep;
+      if (ep->timing) CK(cudaEventRecord(ep->ev_t[3], st), "stage event");
+      if (!ep_direct_phase_b(ranks[r], st)) return 0;
+    }
+    for (int r = 0; r < world; ++r) {
+      if (!ep_phase_c(ranks[r], out_dev[r], T_local[r], st)) return 0;
+      if (!ep_finish_timing(ranks[r])) return 0;
+    }
+    return 1;
+  }
   for (int r = 0; r < world; ++r)
     if (!ep_phase_a(ranks[r], x_dev[r], T_local[r], st)) return 0;
   for (int r = 0; r < world; ++r)

@@ -107,3 +107,4 @@ void coli_ep_destroy(ColiMoe *m);
 // Allocate the expert-parallel state of a handle created with ep_world > 1 (idempotent); `comm` is an
 // ncclComm_t or null (a handle without a communicator can only take part in the one-GPU emulation).
 int coli_ep_ensure(ColiMoe *m, void *comm);
+int coli_ep_check(ColiMoe *m);

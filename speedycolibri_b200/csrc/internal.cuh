@@ -149,7 +149,24 @@ struct PermuteParams {
   __half *xg;                  // [T*k (+T),H] gathered rows as f16 (null = skip)
   int gather_shared;           // also copy the shared expert's T identity rows into xg
   __half *x16;                 // [T,H] f16 copy of x in token order (null = skip)
+  // Virtual batch (expert parallelism): the tokens are the concatenation of up to 8 segments that
+  // sit at fixed places of a larger buffer, with their lengths known on the device only.  When
+  // `virt` is set, T above is an upper bound used for grid sizes, the token count is virt->total, and
+  // token j lives in row virt->phys[s] * virt->stride + (j - virt->off[s]) of x / topk_idx, s being its segment.
+  const struct VirtualBatch *virt;
+  int rows_cap;                // rows xg / row_token hold; a pair beyond it gets no row and raises *overflow
+  int *overflow;               // device word (may be null)
 };
+struct VirtualBatch {
+  int32_t nseg, stride, total, pad;
+  int32_t off[9];   // first token of each segment (off[nseg] = total)
+  int32_t phys[8];  // buffer slot of each segment
+};
+__device__ __forceinline__ int coli_virt_row(const VirtualBatch *v, int j) {
+  int s = 0;
+  while (s + 1 < v->nseg && j >= v->off[s + 1]) ++s;
+  return v->phys[s] * v->stride + (j - v->off[s]);
+}
 int launch_permute(const PermuteParams &p, cudaStream_t st);
 // Router + top-k + permutation of a decode-sized batch (T <= 8) in one launch.  Returns 1 on
 // success, 0 on error, -1 when the shapes do not qualify (run launch_router + launch_permute).

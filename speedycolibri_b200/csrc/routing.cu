@@ -652,11 +652,12 @@ __global__ void __launch_bounds__(128) k_seg_count(PermuteParams p, int nchunk) 
   int *cnt = cnt_sm + (size_t)warp * p.E;
   for (int e = lane; e < p.E; e += 32) cnt[e] = 0;
   __syncwarp();
-  if (chunk >= nchunk) return;
-  const int t0 = chunk * 32, t1 = min(p.T, t0 + 32);
+  const int T = p.virt ? p.virt->total : p.T;
+  if (chunk >= nchunk || chunk * 32 >= T) return;
+  const int t0 = chunk * 32, t1 = min(T, t0 + 32);
   for (int t = t0; t < t1; ++t) {
     int e = -1;
-    if (lane < p.k) e = p.topk_idx[(size_t)t * p.k + lane];
+    if (lane < p.k) e = p.topk_idx[(size_t)(p.virt ? coli_virt_row(p.virt, t) : t) * p.k + lane];
     const bool valid = e >= 0 && e < p.E;
     const unsigned same = __match_any_sync(0xffffffffu, valid ? e : -1 - lane);  // invalid lanes match nobody
     int base = 0;
@@ -728,6 +729,7 @@ __global__ void __launch_bounds__(1024) k_seg_scan(PermuteParams p, int nchunk, 
   __shared__ int seg_off[1024 + 2];
   __shared__ int seg_ibase[1024 + 2];
   const int E = p.E;
+  if (p.virt) nchunk = min(nchunk, (p.virt->total + 31) / 32);
   const int nrt = p.nseg_routed;  // routed segments: E, or the experts resident on this rank
   const int nseg = nrt + (p.has_shared ? 1 : 0);
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
@@ -747,8 +749,21 @@ __global__ void __launch_bounds__(1024) k_seg_scan(PermuteParams p, int nchunk, 
     }
     seg_cnt[pos] = run;
   }
-  if (threadIdx.x == 0 && p.has_shared) seg_cnt[nrt] = p.T;
+  if (threadIdx.x == 0 && p.has_shared) seg_cnt[nrt] = p.virt ? p.virt->total : p.T;
   __syncthreads();
+  if (p.rows_cap != 0x7fffffff) {  // a batch that does not fit the row buffers is not run at all (and reported)
+    __shared__ int too_many;
+    if (threadIdx.x == 0) {
+      long total = 0;
+      for (int s = 0; s < nseg; ++s) total += seg_cnt[s];
+      too_many = total > (long)p.rows_cap ? 1 : 0;
+      if (too_many && p.overflow) atomicExch(p.overflow, 1);
+    }
+    __syncthreads();
+    if (too_many)
+      for (int s = threadIdx.x; s < nseg; s += blockDim.x) seg_cnt[s] = 0;
+    __syncthreads();
+  }
   build_work_list(p, seg_cnt, nseg, max_items, seg_off, seg_ibase);
   for (int s = threadIdx.x; s <= nseg; s += blockDim.x) p.seg_off[s] = seg_off[s];
   for (int s = threadIdx.x; s < nrt; s += blockDim.x) p.seg_count[s] = seg_cnt[s];
@@ -758,11 +773,12 @@ __global__ void __launch_bounds__(256) k_permute(PermuteParams p) {
   // one warp per (t, kk) row; rows T*k .. T*k+T-1 are the shared expert's identity rows; when a
   // token-order f16 copy of x is wanted, T more warps write it
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  const int nrouted = p.T * p.k;
-  const int total = nrouted + (p.has_shared ? p.T : 0);
+  const int T = p.virt ? p.virt->total : p.T;
+  const int nrouted = T * p.k;
+  const int total = nrouted + (p.has_shared ? T : 0);
   if (warp >= total) {
     const int t = warp - total;
-    if (p.x16 && t < p.T) {
+    if (p.x16 && t < T) {
       const int vec = p.H / 8;
       const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (size_t)t * p.H);
       uint4 *dst = reinterpret_cast<uint4 *>(p.x16 + (size_t)t * p.H);
@@ -771,24 +787,34 @@ __global__ void __launch_bounds__(256) k_permute(PermuteParams p) {
     return;
   }
   int t, pos;
+  int trow;  // row of the token in x / topk_idx
   if (warp < nrouted) {
     t = warp / p.k;
-    const int e = p.topk_idx[warp];
+    trow = p.virt ? coli_virt_row(p.virt, t) : t;
+    const int e = p.topk_idx[(size_t)trow * p.k + (warp - t * p.k)];
     const int s = (e < 0 || e >= p.E) ? -1 : (p.expert_slot ? p.expert_slot[e] : e);
     if (s < 0) {  // not resident here (or not an expert id): no row, the combine skips negative slots
       if (lane == 0) p.slot[warp] = -1;
       return;
     }
     pos = p.seg_off[s] + p.chunk_cnt[(size_t)(t >> 5) * p.E + e] + p.local_rank[warp];
+    if (pos >= p.rows_cap) {  // more rows than the buffers hold: drop the pair and report it
+      if (lane == 0) {
+        p.slot[warp] = -1;
+        if (p.overflow) atomicExch(p.overflow, 1);
+      }
+      return;
+    }
     if (lane == 0) p.slot[warp] = pos;
   } else {
     t = warp - nrouted;
+    trow = t;
     pos = p.seg_off[p.nseg_routed] + t;
   }
   if (lane == 0) p.row_token[pos] = t;
   if (p.xg && (warp < nrouted || p.gather_shared)) {
     const int vec = p.H / 8;
-    const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (size_t)t * p.H);
+    const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (size_t)trow * p.H);
     uint4 *dst = reinterpret_cast<uint4 *>(p.xg + (size_t)pos * p.H);
     for (int c = lane; c < vec; c += 32) dst[c] = coli_bf16x8_to_f16x8(src[c]);
   }
@@ -945,8 +971,8 @@ int launch_permute(const PermuteParams &p, cudaStream_t st) {
   }
   const int nchunk = (p.T + 31) / 32;
   const int max_items = permute_max_items(p);
-  // the one-CTA form also gathers the rows: fine for a decode batch, far too slow for hundreds of rows
-  if (permute_small_ok(p) && (!p.xg || p.T * (p.k + 1) <= 96)) {
+  // the one-CTA form also gathers the rows: fine up to ~128 KB of them, far too slow for a megabyte
+  if (!p.virt && permute_small_ok(p) && (!p.xg || (size_t)p.T * (p.k + 1) * p.H * 2 <= 128 * 1024)) {
     int conv = 0;
     if (p.x16) {
       const size_t n = (size_t)p.T * p.H / 8;

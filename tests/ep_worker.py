@@ -24,7 +24,9 @@ def main():
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     backend.init([local])
-    for name, T, balanced in (("tiny_sig", 40 * world, False), ("mid", 256 * world, False), ("tiny_zipf", 64 * world, True)):
+    for name, T, balanced, transport in (("tiny_sig", 40 * world, False, "direct"), ("mid", 256 * world, False, "direct"),
+                                         ("tiny_zipf", 64 * world, True, "direct"), ("mid", 256 * world, True, "nccl")):
+        os.environ["COLI_EP_TRANSPORT"] = transport  # read when the handle's expert-parallel state is created
         shape = CONFIGS[name].with_tokens(T)
         L, packed = host_layer(shape)
         x_all = synth.host_tokens(shape, T)
@@ -53,7 +55,7 @@ def main():
         assert tab[:, 1, :].sum() == T * shape.k
         if rank == 0:
             assert max(errs) <= 1e-2, (name, errs)
-            print(f"EP_OK {name} world={world} rel_l2={max(errs):.2e} rows_per_rank={tab[:, 1, :].sum(axis=0).tolist()}", flush=True)
+            print(f"EP_OK {name} {transport} world={world} rel_l2={max(errs):.2e} rows_per_rank={tab[:, 1, :].sum(axis=0).tolist()}", flush=True)
         sm.close()
         dist.barrier()
     dist.destroy_process_group()

@@ -26,4 +26,4 @@ def test_expert_parallel_matches_oracle(world):
                         "--master-addr", "127.0.0.1", "--master-port", port, os.path.join(ROOT, "tests", "ep_worker.py")],
                        capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    assert r.stdout.count("EP_OK") == 3, r.stdout
+    assert r.stdout.count("EP_OK") == 4, r.stdout

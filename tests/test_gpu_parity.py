@@ -388,18 +388,21 @@ def test_stage_calls_emulate_expert_parallel(gpu_backend, orc, world, name):
         b.close()
 
 
+@pytest.mark.parametrize("transport", ["direct", "nccl"])
 @pytest.mark.parametrize("world,name,T,balanced", [(2, "tiny_sig", 37, False), (4, "tiny_sig", 150, False), (3, "tiny_zipf", 70, True),
                                                     (2, "mid", 512, False), (8, "mid", 1000, True), (2, "tiny", 5, False)])
-def test_expert_parallel_call_emulated_on_one_gpu(gpu_backend, orc, world, name, T, balanced):
+def test_expert_parallel_call_emulated_on_one_gpu(gpu_backend, orc, monkeypatch, world, name, T, balanced, transport):
     """The expert-parallel block call with `world` handles on ONE GPU (coli_b200_moe_block_ep_emulate:
-    same kernels, same offsets, the two exchanges done as device copies): ragged token shards (one
-    of them empty), contiguous and LPT expert maps, a rank that owns no expert of some tokens.
-    Routing must be exact and every rank's output within the bar against the oracle; and because
-    result rows return unweighted and the home rank combines, the output must equal the single-GPU
-    block's bit for bit when both take the same kernel family."""
+    same kernels, same offsets; the peers' buffers are plain pointers, the barriers stream order):
+    ragged token shards (one of them empty), contiguous and LPT expert maps, a rank that owns no
+    expert of some tokens; both transports (rows stored straight into the peers' receive slabs, or
+    packed and copied as the ncclSend / ncclRecv form lays them out).  Routing must be exact and
+    every rank's output within the bar against the oracle."""
     import ctypes as C
 
     import torch
+
+    monkeypatch.setenv("COLI_EP_TRANSPORT", transport)  # read when a handle's expert-parallel state is created
 
     from speedycolibri_b200 import _lib
     from speedycolibri_b200.cluster import ExpertSharding, ep_layout, rows_per_rank
