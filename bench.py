@@ -333,13 +333,15 @@ class Ctx:
             # shorter than that, the same step keeps running (untimed, same count on every rank) so
             # that the clock record still describes the GPU under this load
             spent_ms = ms_step * steps
+            if self.args.profile_run:
+                spent_ms = 1e9  # under a profiler: no extra steps
             if spent_ms < 800.0:
                 extra = int(min(20000, max(1, (800.0 - spent_ms) / max(ms_step, 1e-3))))
                 for _ in range(extra):
                     fn()
                 torch.cuda.synchronize()
         clocks = clk.summary()
-        if spent_ms < 800.0:
+        if spent_ms < 800.0 and not self.args.profile_run:
             clocks["note"] = "timed region shorter than the sampler's start-up; samples include the same step repeated after it"
         return ms_step, launches, clocks
 
@@ -432,7 +434,7 @@ def bench_single(ctx, shape, layer, steps, warmup, headline):
     res["phase_ms"] = phases
     res["roofline"] = roofline_of(ctx, shape, phases, ms_step, active, clocks)
     # parity: sampled tokens against the CPU oracle, with the experts exported from the GPU
-    if not ctx.args.no_parity:
+    if not ctx.args.no_parity and not ctx.args.profile_run:
         blk.forward(x, out)
         torch.cuda.synchronize()
         toks = sample_tokens(shape.T, ctx.args.parity_tokens)
@@ -440,6 +442,10 @@ def bench_single(ctx, shape, layer, steps, warmup, headline):
         tt = torch.from_numpy(toks).to(ctx.dev)
         res["parity"] = compare_with_oracle(L, bits(x[tt]), bits(out[tt]), idx[toks], w[toks])
         del L
+    if ctx.args.profile_run:  # a run made to be profiled: the timed and the per-phase steps only
+        blk.close()
+        res["e2e"] = None
+        return res
     # end to end: pinned host buffers, host-pointer call (H2D + block + D2H inside the timed region)
     xh = torch.empty((shape.T, shape.H), dtype=torch.bfloat16).pin_memory()
     oh = torch.empty((shape.T, shape.H), dtype=torch.bfloat16).pin_memory()
@@ -590,6 +596,8 @@ def run_ours(args):
     ctx = Ctx(args)
     world = ctx.world
     head_shape = shape_named(args.workload, args.tokens)
+    if args.profile_run:
+        args.workloads = "none"
     if args.workloads == "all":
         extra = ["c0", "c1_t1", "c1_t4", "c1_t8", "c2", "c4"] if world == 1 else ["c4"]
         extra = [w for w in extra if w != args.workload]
@@ -650,6 +658,9 @@ def main():
     ap.add_argument("--ref-tokens", type=int, default=0, help="tokens per step of the reference arm (0 = auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
+    ap.add_argument("--profile-run", action="store_true",
+                    help="for runs under ncu: only the warm-up, timed and per-phase steps of the headline workload (no clock-sample "
+                         "extension, parity, end-to-end or CPU legs); implies --workloads none")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
