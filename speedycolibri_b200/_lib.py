@@ -33,7 +33,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     objdir = os.path.join(_HERE, "build")
     os.makedirs(objdir, exist_ok=True)
-    flags = [f for f in NVCC_FLAGS if f != "-shared"]
+    flags = [f for f in NVCC_FLAGS if f != "-shared"] + os.environ.get("COLI_NVCC_EXTRA", "").split()
 
     def compile_one(src):
         obj = os.path.join(objdir, src.replace(".cu", ".o"))

@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
         const uint32_t buf = big ? 0u : (small_units++ & 1u);
         bool ok = true;
         for (uint32_t b = big ? 0u : buf; ok && b <= (big ? 1u : buf); ++b) {
-          ok = mbar_wait(acc_empty + 8 * b, (waits[b] & 1u) ^ 1u, abort_flag, p.status, TC_ERR_MMA_WAIT);
+          ok = mbar_wait(acc_empty + 8 * b, (waits[b] & 1u) ^ 1u, abort_flag, p.status, TC_ERR_MMA_WAIT, 1);
           waits[b]++;
         }
         if (!ok) break;
@@ -237,19 +237,33 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
         tmem_ld16(tbase + c0, g);
         tmem_ld16(tbase + acc1_off + c0, u);
         tmem_ld_wait();
+        // all 16 columns are computed first, branch-free, so that their dependent chains (scale,
+        // exponential, reciprocal, two roundings) overlap; a branch per column would run them one
+        // after the other.  Columns beyond the item's rows hold zeros and are simply not stored.
+        if (GATED) {
+          __half hv[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int col = c0 + j;
-          if (col < nrows) {
-            const float v0 = __uint_as_float(g[j]) * s0, v1 = __uint_as_float(u[j]) * s1;
-            if (GATED) {
-              if (f < Oout) out_h[(size_t)col * Oout] = coli_f32_to_f16_via_bf16(coli_act_fast(v0, v1, p.act));
-            } else {
-              __nv_bfloat16 *dst = out_y + (size_t)col * Oout;
-              if (f < Oout) *dst = __float2bfloat16_rn(v0);
-              if (f + TC_BM < Oout) dst[TC_BM] = __float2bfloat16_rn(v1);
-            }
+          for (int j = 0; j < 16; ++j)
+            hv[j] = coli_f32_to_f16_via_bf16(coli_act_fast(__uint_as_float(g[j]) * s0, __uint_as_float(u[j]) * s1, p.act));
+          if (f < Oout) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (c0 + j < nrows) out_h[(size_t)(c0 + j) * Oout] = hv[j];
           }
+        } else {
+          __nv_bfloat16 y0[16], y1[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            y0[j] = __float2bfloat16_rn(__uint_as_float(g[j]) * s0);
+            y1[j] = __float2bfloat16_rn(__uint_as_float(u[j]) * s1);
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (c0 + j < nrows) {
+              __nv_bfloat16 *dst = out_y + (size_t)(c0 + j) * Oout;
+              if (f < Oout) *dst = y0[j];
+              if (f + TC_BM < Oout) dst[TC_BM] = y1[j];
+            }
         }
       }
       tc_fence_before();

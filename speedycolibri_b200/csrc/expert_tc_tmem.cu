@@ -29,6 +29,22 @@
 // waits for its own copies and frees its TMEM before returning.
 #include "tc_common.cuh"
 
+#ifdef COLI_TT_TRACE
+// Measurement aid (never compiled into the library as shipped): clock stamps of CTA 0's first stages.
+__device__ long long g_tt_trace[256 * 8];
+extern "C" int coli_debug_tt_trace(long long *host) {
+  return cudaMemcpyFromSymbol(host, g_tt_trace, sizeof(g_tt_trace)) == cudaSuccess ? 1 : 0;
+}
+#define TT_TRACE(it, k)                                                                 \
+  do {                                                                                  \
+    if (GATED && blockIdx.x == 0 && (it) < 256u) g_tt_trace[(it) * 8 + (k)] = clock64(); \
+  } while (0)
+#else
+#define TT_TRACE(it, k) \
+  do {                  \
+  } while (0)
+#endif
+
 namespace colib {
 
 // TMEM budget (512 columns): two accumulators of ACC columns (= the most token rows of a tile) and a
@@ -112,6 +128,15 @@ __device__ __forceinline__ TtPacked tt_load_packed(const WeightRef &w, int Op, i
     asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(r.sc) : "l"(w.s + base * 8 + (kb & 1) * 4));
   }
   return r;
+}
+// Ask L2 for the bytes tt_load_packed will read `ahead` stages later (the weights of a tile come from
+// DRAM exactly once; the register loads two stages ahead then find them in L2).
+__device__ __forceinline__ void tt_prefetch_packed(const WeightRef &w, int Op, int row, int kb, int KB) {
+  if (row < Op && kb < KB) {
+    const size_t base = (size_t)(kb >> 1) * Op + row;
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(w.q + base * 64 + (kb & 1) * 32));
+    if ((kb & 1) == 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(w.s + base * 8));
+  }
 }
 // Convert one stage of one row and hand it to the tensor core through 32 TMEM columns.
 __device__ __forceinline__ void tt_emit_stage(const TtPacked &pk, uint32_t taddr) {
@@ -283,6 +308,7 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
             alive = false;
             break;
           }
+          TT_TRACE(it, 6);
           const uint32_t dst = smem_u32(smem + s * TT_B_BYTES);
           mbar_expect_tx(full_s + 8 * s, (uint32_t)N * TC_BK * 2);
           for (int j = 0; j < N / TC_BOXN; ++j)
@@ -311,23 +337,44 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
         const int nrows = p.item_nrows[item];
         const int N = (nrows + TC_BOXN - 1) / TC_BOXN * TC_BOXN;
         const uint32_t idesc = umma_idesc(N);
+        if (which == 0) TT_TRACE(240 + tix, 3);
         if (!mbar_wait(acc_empty, (tix & 1u) ^ 1u, abort_flag, p.status, TC_ERR_MMA_WAIT, 1)) break;
+        if (which == 0) TT_TRACE(240 + tix, 4);
         tc_fence_after();
-        for (int kb = 0; kb < KB; ++kb) {
-          if (!mbar_wait(full_s + 8 * sb, phb, abort_flag, p.status, TC_ERR_MMA_WAIT, 1)) {
+        // Two stages per visit (KB is even): both "filled" barriers are awaited first and the eight MMAs
+        // go out back to back.  A wait plus the loop around it keeps this thread away from the tensor
+        // core for several hundred cycles; with one stage per visit the queue behind it (four MMAs of
+        // each issuer) ran dry in that time.
+        for (int kb = 0; kb < KB; kb += 2) {
+          if (which == 0) TT_TRACE(tix * KB + kb, 0);
+          const uint32_t sb0 = sb, ph0 = phb;
+          uint32_t sb1 = sb + 1, ph1 = phb;
+          if (sb1 == TT_B_STAGES) {
+            sb1 = 0;
+            ph1 ^= 1u;
+          }
+          if (!mbar_wait(full_s + 8 * sb0, ph0, abort_flag, p.status, TC_ERR_MMA_WAIT, 1) ||
+              !mbar_wait(full_s + 8 * sb1, ph1, abort_flag, p.status, TC_ERR_MMA_WAIT, 1)) {
             alive = false;
             break;
           }
+          if (which == 0) TT_TRACE(tix * KB + kb, 1);
           tc_fence_after();
+          const uint32_t sa1 = sa == TT_A_STAGES - 1 ? 0u : sa + 1;
           // both issuers commit: the rings are refilled once both accumulators have read them
-          tt_issue_stage(acc, a_ring + sa * 64, bdesc_ring + (uint64_t)(sb * (TT_B_BYTES >> 4)), idesc, kb ? 1u : 0u, empty_s + 8 * sb);
-          sa = sa == TT_A_STAGES - 1 ? 0u : sa + 1;
-          if (++sb == TT_B_STAGES) {
+          tt_issue_stage(acc, a_ring + sa * 64, bdesc_ring + (uint64_t)(sb0 * (TT_B_BYTES >> 4)), idesc, kb ? 1u : 0u, empty_s + 8 * sb0);
+          tt_issue_stage(acc, a_ring + sa1 * 64, bdesc_ring + (uint64_t)(sb1 * (TT_B_BYTES >> 4)), idesc, 1u, empty_s + 8 * sb1);
+          if (which == 0) TT_TRACE(tix * KB + kb, 2);
+          sa = sa1 == TT_A_STAGES - 1 ? 0u : sa1 + 1;
+          sb = sb1 + 1;
+          phb = ph1;
+          if (sb == TT_B_STAGES) {
             sb = 0;
             phb ^= 1u;
           }
         }
         if (alive) umma_commit(acc_full);
+        if (which == 0) TT_TRACE(240 + tix, 5);
       }
     }
   } else if (warp < 2 + TC_EPI_WARPS) {
@@ -354,7 +401,9 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
         s1 = f1 < Oout ? __ldg(reinterpret_cast<const float *>(w1.s) + f1) : 0.0f;
       }
       bool ok = true;
+      if (lg == 0 && lane == 0) TT_TRACE(240 + tix, 0);
       if (lane == 0) ok = mbar_wait(acc_full, tix & 1u, abort_flag, p.status, TC_ERR_EPI_WAIT, 256);
+      if (lg == 0 && lane == 0) TT_TRACE(240 + tix, 1);
       ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
       if (!ok) break;
       tc_fence_after();
@@ -363,26 +412,52 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
       __nv_bfloat16 *out_y = p.y + (size_t)row0 * Oout + f;
       for (int c0 = 0; c0 < N; c0 += 16) {
         uint32_t g[16], u[16];
+#ifdef COLI_TT_TRACE
+        if (GATED && blockIdx.x == 0 && lg == 0 && lane == 0 && tix == 2) g_tt_trace[(200 + c0 / 16) * 8 + 0] = clock64();
+#endif
         tmem_ld16(tbase + c0, g);
         tmem_ld16(tbase + TT_ACC_COLS + c0, u);
         tmem_ld_wait();
+#ifdef COLI_TT_TRACE
+        if (GATED && blockIdx.x == 0 && lg == 0 && lane == 0 && tix == 2) g_tt_trace[(200 + c0 / 16) * 8 + 1] = clock64();
+        if (GATED && blockIdx.x == 0 && lg == 0 && lane == 0 && tix == 2)
+          g_tt_trace[(200 + c0 / 16) * 8 + 3] = clock64() + (long long)(g[0] == 0x12345u) + (long long)(u[15] == 0x12345u) + (long long)(g[7] == 0x12345u);
+#endif
+        // all 16 columns are computed first, branch-free, so that their dependent chains (scale,
+        // exponential, reciprocal, two roundings) overlap; a branch per column would run them one
+        // after the other.  Columns beyond the item's rows hold other rows' sums and are not stored.
+        if (GATED) {
+          __half hv[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int col = c0 + j;
-          if (col < nrows) {
-            const float v0 = __uint_as_float(g[j]) * s0, v1 = __uint_as_float(u[j]) * s1;
-            if (GATED) {
-              if (f < Oout) out_h[(size_t)col * Oout] = coli_f32_to_f16_via_bf16(coli_act_fast(v0, v1, p.act));
-            } else {
-              __nv_bfloat16 *dst = out_y + (size_t)col * Oout;
-              if (f < Oout) *dst = __float2bfloat16_rn(v0);
-              if (f + TC_BM < Oout) dst[TC_BM] = __float2bfloat16_rn(v1);
-            }
+          for (int j = 0; j < 16; ++j)
+            hv[j] = coli_f32_to_f16_via_bf16(coli_act_fast(__uint_as_float(g[j]) * s0, __uint_as_float(u[j]) * s1, p.act));
+#ifdef COLI_TT_TRACE
+          if (blockIdx.x == 0 && lg == 0 && lane == 0 && tix == 2) g_tt_trace[(200 + c0 / 16) * 8 + 2] = clock64() + (long long)(__half2float(hv[0]) == 123.0f) + (long long)(__half2float(hv[15]) == 123.0f);
+#endif
+          if (f < Oout) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (c0 + j < nrows) out_h[(size_t)(c0 + j) * Oout] = hv[j];
           }
+        } else {
+          __nv_bfloat16 y0[16], y1[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            y0[j] = __float2bfloat16_rn(__uint_as_float(g[j]) * s0);
+            y1[j] = __float2bfloat16_rn(__uint_as_float(u[j]) * s1);
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (c0 + j < nrows) {
+              __nv_bfloat16 *dst = out_y + (size_t)(c0 + j) * Oout;
+              if (f < Oout) *dst = y0[j];
+              if (f + TC_BM < Oout) dst[TC_BM] = y1[j];
+            }
         }
       }
       tc_fence_before();
       __syncwarp();
+      if (lg == 0 && lane == 0) TT_TRACE(240 + tix, 2);
       if (lane == 0) mbar_arrive(acc_empty);
     }
   } else {
@@ -399,6 +474,7 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
     auto stage = [&](const auto &pk, uint32_t it) -> bool {
       const uint32_t sa = it % TT_A_STAGES;
       bool ok = true;
+      if (mtx == 0 && quarter == 0 && lane == 0) TT_TRACE(it, 3);
       if (it >= (uint32_t)TT_A_STAGES) {  // the weight slot was last read by stage it - TT_A_STAGES
         const uint32_t u = it - TT_A_STAGES;
         if (lane == 0) ok = mbar_wait(empty_s + 8 * (u % TT_B_STAGES), (u / TT_B_STAGES) & 1u, abort_flag, p.status, TC_ERR_PROD_WAIT, 1);
@@ -406,12 +482,17 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
         if (!ok) return false;
         tc_fence_after();
       }
+      if (mtx == 0 && quarter == 0 && lane == 0) TT_TRACE(it, 4);
       if constexpr (FMT == COLI_FMT_NVFP4)
         tt_emit_stage(pk, taddr + sa * 64);
       else
         tt_emit_stage<FMT>(pk, taddr + sa * 64);
+      if (mtx == 0 && quarter == 0 && lane == 0) TT_TRACE(it, 5);
       tc_fence_before();
       __syncwarp();
+#ifdef COLI_TT_TRACE
+      if (GATED && blockIdx.x == 0 && lane == 0 && it < 256u) atomicMax((unsigned long long *)&g_tt_trace[it * 8 + 7], (unsigned long long)clock64());
+#endif
       if (lane == 0) mbar_arrive(full_s + 8 * (it % TT_B_STAGES));
       return true;
     };
@@ -433,7 +514,12 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
         pb = pa;
         if (kb0 < KB) pa = tt_load_packed(wr, Op, grow, kb0);
         if (kb0 + 2 < KB) pb = tt_load_packed(wr, Op, grow, kb0 + 2);
+        const int pf = p.pf_stages;
         for (int kb = kb0; kb < KB && alive; kb += 4) {
+          if (pf > 0) {
+            tt_prefetch_packed(wr, Op, grow, kb + pf, KB);
+            tt_prefetch_packed(wr, Op, grow, kb + pf + 2, KB);
+          }
           alive = stage(pa, it0 + kb);
           if (kb + 4 < KB) pa = tt_load_packed(wr, Op, grow, kb + 4);
           if (alive && kb + 2 < KB) alive = stage(pb, it0 + kb + 2);

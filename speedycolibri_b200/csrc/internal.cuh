@@ -219,6 +219,7 @@ struct TcParams {
   __nv_bfloat16 *y;  // [rows, H]
   int *status;       // device word: 0, or the code of the first bounded wait that gave up
   ActParams act;
+  int pf_stages;     // tensor-memory kernel: weight bytes are requested into L2 this many 64-k stages ahead (0 = off)
 };
 // x_rows: f16 [rows_cap, H] expert-contiguous rows (row index = position in the work list)
 int launch_gate_up_tc(const TcParams &p, const void *x_rows, int rows_cap, int sm_count, cudaStream_t st);
@@ -297,18 +298,19 @@ __device__ __forceinline__ uint4 coli_bf16x8_to_f16x8(uint4 v) {
   return make_uint4(coli_bf16x2_to_f16x2(v.x), coli_bf16x2_to_f16x2(v.y), coli_bf16x2_to_f16x2(v.z),
                     coli_bf16x2_to_f16x2(v.w));
 }
-// coli_act_combine with the fast exponential: silu(g) * u, or its clamped / OpenAI forms
+// coli_act_combine with the fast exponential: silu(g) * u, or its clamped / OpenAI forms.
+// Written with selects on the (uniform) mode instead of branches: inlined sixteen times in an
+// unrolled epilogue, a branch per call turns the sixteen independent chains (exp, reciprocal, two
+// roundings: ~150 cycles each) into sixteen basic blocks that run one after the other.
 __device__ __forceinline__ float coli_act_fast(float g, float u, const ActParams &a) {
-  if (a.oai) {
-    g = fminf(g, a.limit);
-    u = fminf(fmaxf(u, -a.limit), a.limit);
-    return __fdividef(g, 1.0f + __expf(-a.alpha * g)) * (u + 1.0f);
-  }
-  if (a.limit > 0.0f) {
-    g = fminf(g, a.limit);
-    u = fminf(fmaxf(u, -a.limit), a.limit);
-  }
-  return __fdividef(g, 1.0f + __expf(-g)) * u;
+  const bool oai = a.oai != 0;
+  const bool clamp = oai || a.limit > 0.0f;
+  const float gl = fminf(g, a.limit), ul = fminf(fmaxf(u, -a.limit), a.limit);
+  g = clamp ? gl : g;
+  u = clamp ? ul : u;
+  const float al = oai ? a.alpha : 1.0f;
+  const float add = oai ? 1.0f : 0.0f;
+  return __fdividef(g, 1.0f + __expf(-al * g)) * (u + add);
 }
 // f32 -> (rounded to bf16) -> f16 bits, saturating
 __device__ __forceinline__ __half coli_f32_to_f16_via_bf16(float v) {

@@ -655,9 +655,19 @@ __global__ void __launch_bounds__(128) k_seg_count(PermuteParams p, int nchunk) 
   const int T = p.virt ? p.virt->total : p.T;
   if (chunk >= nchunk || chunk * 32 >= T) return;
   const int t0 = chunk * 32, t1 = min(T, t0 + 32);
-  for (int t = t0; t < t1; ++t) {
-    int e = -1;
-    if (lane < p.k) e = p.topk_idx[(size_t)(p.virt ? coli_virt_row(p.virt, t) : t) * p.k + lane];
+  // all of the chunk's expert ids are requested before the ordered walk: a load per step would put a
+  // memory round trip on each of the 32 steps
+  int ids[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    ids[i] = -1;
+    if (lane < p.k && t0 + i < t1) ids[i] = p.topk_idx[(size_t)(p.virt ? coli_virt_row(p.virt, t0 + i) : t0 + i) * p.k + lane];
+  }
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int t = t0 + i;
+    if (t >= t1) break;  // uniform across the warp
+    const int e = ids[i];
     const bool valid = e >= 0 && e < p.E;
     const unsigned same = __match_any_sync(0xffffffffu, valid ? e : -1 - lane);  // invalid lanes match nobody
     int base = 0;

@@ -36,6 +36,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait with a suspend-time hint: the thread stays suspended in hardware (taking no issue slots)
+// until the phase completes or about `ns` nanoseconds have passed
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -46,16 +57,18 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false when the barrier did not flip in time or another role gave up.
-// sleep_ns = 0 polls with test_wait (never suspends); 1 polls with try_wait, which the hardware
-// may suspend for a short while (stage-ring waits: no hot spin next to the producer warps, and
-// measured no slower); > 1 additionally sleeps between polls (waits that normally last a whole
-// main loop).
+// sleep_ns = 0 polls with test_wait (never suspends); otherwise every poll is a try_wait that the
+// hardware suspends for up to max(sleep_ns, 1000) ns or until the phase completes.  A waiting warp
+// must not spin: the trace of the tensor-memory kernel showed twenty polling warps taking four
+// fifths of the issue slots from the one warp per scheduler that had work (the epilogue ran at a
+// tenth of an instruction per cycle, the MMA-issuing threads lost ~500 cycles per stage).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code,
                                           uint32_t sleep_ns = 0) {
-  for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
-    if (sleep_ns ? mbar_try_wait(bar, parity) : mbar_test_wait(bar, parity)) return true;
-    if (sleep_ns > 1 && i >= 8) __nanosleep(sleep_ns);
-    if ((i & 63u) == 63u && *abort_flag) return false;
+  const uint32_t hint = sleep_ns > 1000u ? sleep_ns : 1000u;
+  const uint32_t limit = sleep_ns ? (TC_SPIN_LIMIT >> 4) : TC_SPIN_LIMIT;  // at most ~0.3 s of suspended polls
+  for (uint32_t i = 0; i < limit; ++i) {
+    if (sleep_ns ? mbar_try_wait_hint(bar, parity, hint) : mbar_test_wait(bar, parity)) return true;
+    if ((i & 7u) == 7u && *abort_flag) return false;
   }
   *abort_flag = 1;
   atomicCAS(status, TC_OK, code);
