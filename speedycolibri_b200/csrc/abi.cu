@@ -501,11 +501,6 @@ extern "C" void *coli_b200_moe_stream(ColiMoe *m) { return m ? (void *)m->ctx->s
 // 160 tokens and wins while segments are about that long; longer NVFP4 segments amortise the
 // shared-memory weight tiles of the other kernel over 256 tokens.  The FP8 formats exist in the
 // tensor-memory kernel only (longer segments are cut into several of its tiles).
-// Stages of L2 look-ahead of the tensor-memory kernel's weight stream (COLI_TCT_PF overrides, a measurement aid).
-int coli_tct_prefetch_stages() {
-  const char *e = getenv("COLI_TCT_PF");
-  return e ? atoi(e) : 0;
-}
 bool coli_use_tct(int fmt, int rows, int nseg) {
   return fmt != COLI_FMT_NVFP4 || rows <= 160 * (nseg > 0 ? nseg : 1);
 }
@@ -843,7 +838,6 @@ static int moe_block_impl(ColiMoe *m, const void *x_dev, void *out_dev, float *r
     tp.y = m->y;
     tp.status = m->status;
     tp.act = m->act;
-    tp.pf_stages = coli_tct_prefetch_stages();
     if (!(tct ? colib::launch_gate_up_tct(tp, m->xg, rows, m->sm_count, st) : colib::launch_gate_up_tc(tp, m->xg, rows, m->sm_count, st)))
       return 0;
     COLI_MARK(3);
@@ -1077,7 +1071,6 @@ int coli_run_segments(ColiMoe *m, SegScratch &sc, const WeightRef *g, const Weig
     tp.y = (__nv_bfloat16 *)y_dev;
     tp.status = m->status;
     tp.act = m->act;
-    tp.pf_stages = coli_tct_prefetch_stages();
     if (tct) return colib::launch_gate_up_tct(tp, rows_dev, rows_cap, m->sm_count, st) && colib::launch_down_tct(tp, rows_cap, m->sm_count, st);
     return colib::launch_gate_up_tc(tp, rows_dev, rows_cap, m->sm_count, st) && colib::launch_down_tc(tp, rows_cap, m->sm_count, st);
   }
@@ -1299,7 +1292,6 @@ static int run_host_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *u
     tp.y = (__nv_bfloat16 *)ctx->buf[4];
     tp.status = d_status;
     tp.act = current_activation();
-    tp.pf_stages = coli_tct_prefetch_stages();
     const int sms = ctx->sm_count;
     const int ok = tct ? colib::launch_gate_up_tct(tp, ctx->buf[1], (int)total, sms, st) && colib::launch_down_tct(tp, (int)total, sms, st)
                        : colib::launch_gate_up_tc(tp, ctx->buf[1], (int)total, sms, st) && colib::launch_down_tc(tp, (int)total, sms, st);

@@ -64,6 +64,13 @@ struct TtBudget {
   static constexpr int NBARS = 2 * B_STAGES + 2;
   static_assert(B_STAGES % A_STAGES == 0 && B_BYTES % 1024 == 0, "a stage barrier serves both rings");
 };
+// The token tile of a stage arrives as ONE box of N rows: the copy engine of an SM takes about 64
+// cycles per box plus 4 per 128-byte row (measured: 21 B/clk with 32-row boxes, 31 B/clk with
+// 160-row ones, on 8 SMs as on 148), and at 21 B/clk the 20 KB tile of a 160-token stage takes
+// longer than the stage's MMAs.  One tensor map per box height (32, 64, ... rows).
+struct TtMaps {
+  CUtensorMap m[TCT_MAX_TOKENS / TC_BOXN];
+};
 constexpr int TT_PROD_WARPS = 16;
 constexpr int TT_MMA2_WARP = 2 + TC_EPI_WARPS + TT_PROD_WARPS;       // the second MMA-issuing warp
 constexpr int TT_THREADS = 32 * (TT_MMA2_WARP + 1);                  // 736
@@ -129,18 +136,8 @@ __device__ __forceinline__ TtPacked tt_load_packed(const WeightRef &w, int Op, i
   }
   return r;
 }
-// Ask L2 for the bytes tt_load_packed will read `ahead` stages later (the weights of a tile come from
-// DRAM exactly once; the register loads two stages ahead then find them in L2).
-__device__ __forceinline__ void tt_prefetch_packed(const WeightRef &w, int Op, int row, int kb, int KB) {
-  if (row < Op && kb < KB) {
-    const size_t base = (size_t)(kb >> 1) * Op + row;
-    asm volatile("prefetch.global.L2 [%0];" ::"l"(w.q + base * 64 + (kb & 1) * 32));
-    if ((kb & 1) == 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(w.s + base * 8));
-  }
-}
 // Convert one stage of one row and hand it to the tensor core through 32 TMEM columns.
-__device__ __forceinline__ void tt_emit_stage(const TtPacked &pk, uint32_t taddr) {
-  uint32_t r[32];
+__device__ __forceinline__ void tt_convert(const TtPacked &pk, uint32_t (&r)[32]) {
   uint32_t m0, m1, m2, m3;
   tc_scales(pk.sc, m0, m1);
   tc_scales(pk.sc >> 16, m2, m3);
@@ -154,8 +151,6 @@ __device__ __forceinline__ void tt_emit_stage(const TtPacked &pk, uint32_t taddr
     r[4 * j + 2] = o.z;
     r[4 * j + 3] = o.w;
   }
-  tmem_st32(taddr, r);
-  tmem_st_wait();
 }
 
 // 16 consecutive columns of this thread's lane
@@ -219,26 +214,20 @@ __device__ __forceinline__ void tt_cvt_e4m3x4(uint32_t w, uint32_t &p0, uint32_t
       : "r"(w));
 }
 template <int FMT>
-__device__ __forceinline__ void tt_emit_stage(const TtPacked8 &pk, uint32_t taddr) {
+__device__ __forceinline__ void tt_convert8(const TtPacked8 &pk, uint32_t (&r)[32]) {
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    uint32_t r[16];
+  for (int j = 0; j < 4; ++j) {
+    const uint4 v = pk.q[j];
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const uint4 v = pk.q[2 * half + j];
-      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        tt_cvt_e4m3x4(w[i], r[8 * j + 2 * i], r[8 * j + 2 * i + 1]);
-        if (FMT == COLI_FMT_FP8_B128) {
-          r[8 * j + 2 * i] = tc_hmul2(r[8 * j + 2 * i], pk.mult);
-          r[8 * j + 2 * i + 1] = tc_hmul2(r[8 * j + 2 * i + 1], pk.mult);
-        }
+    for (int i = 0; i < 4; ++i) {
+      tt_cvt_e4m3x4(w[i], r[8 * j + 2 * i], r[8 * j + 2 * i + 1]);
+      if (FMT == COLI_FMT_FP8_B128) {
+        r[8 * j + 2 * i] = tc_hmul2(r[8 * j + 2 * i], pk.mult);
+        r[8 * j + 2 * i + 1] = tc_hmul2(r[8 * j + 2 * i + 1], pk.mult);
       }
     }
-    tmem_st16(taddr + 16 * half, r);
   }
-  tmem_st_wait();
 }
 // Largest scale of one row block over all k-tiles (every thread of a tile computes the same value).
 __device__ __forceinline__ float tt_block_scale_max(const float *srow, int KT) {
@@ -250,7 +239,7 @@ __device__ __forceinline__ float tt_block_scale_max(const float *srow, int KT) {
 // GATED: the two weight tiles of a stage are gate and up of the same 128 features, result
 // h = act(g, u).  Otherwise: two adjacent 128-feature tiles of the down projection, result y.
 template <bool GATED, int FMT, int ACC>
-__global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant__ CUtensorMap tmap, TcParams p) {
+__global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant__ TtMaps maps, TcParams p) {
   constexpr int TT_A_STAGES = TtBudget<ACC>::A_STAGES, TT_A_COL0 = TtBudget<ACC>::A_COL0, TT_ACC_COLS = ACC;
   constexpr int TT_B_STAGES = TtBudget<ACC>::B_STAGES, TT_B_BYTES = TtBudget<ACC>::B_BYTES, TT_NBARS = TtBudget<ACC>::NBARS;
   extern __shared__ uint8_t smem_raw[];
@@ -302,6 +291,7 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
         const int item = w / n_ftiles;
         const int row0 = p.item_row0[item], nrows = p.item_nrows[item];
         const int N = (nrows + TC_BOXN - 1) / TC_BOXN * TC_BOXN;
+        const CUtensorMap *tmap = &maps.m[N / TC_BOXN - 1];  // the map whose box is N rows
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const uint32_t s = it % TT_B_STAGES, ph = (it / TT_B_STAGES) & 1u;
           if (!mbar_wait(empty_s + 8 * s, ph ^ 1u, abort_flag, p.status, TC_ERR_TMA_WAIT, 32)) {
@@ -311,8 +301,7 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
           TT_TRACE(it, 6);
           const uint32_t dst = smem_u32(smem + s * TT_B_BYTES);
           mbar_expect_tx(full_s + 8 * s, (uint32_t)N * TC_BK * 2);
-          for (int j = 0; j < N / TC_BOXN; ++j)
-            tma_load_2d(dst + j * (TC_BOXN * TC_BK * 2), &tmap, kb * TC_BK, row0 + j * TC_BOXN, full_s + 8 * s);
+          tma_load_2d(dst, tmap, kb * TC_BK, row0, full_s + 8 * s);
         }
       }
       if (!alive) {
@@ -322,6 +311,9 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
     }
   } else if (warp == 1 || warp == TT_MMA2_WARP) {
     // ---------------- MMA issue: warp 1 feeds accumulator 0, the extra warp accumulator 1 ----------------
+    // One thread per accumulator keeps the order of its additions fixed, so results repeat bit for
+    // bit from run to run.  (Two threads per accumulator taking alternate stages were measured: the
+    // additions then interleave differently each run and the time per stage does not change.)
     if (lane == 0) {
       const uint32_t which = warp == 1 ? 0u : 1u;
       uint32_t tix = 0;
@@ -329,7 +321,7 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
       const uint64_t bdesc_ring = umma_smem_desc(smem_u32(smem));  // token-tile stage 0; stages are TT_B_BYTES apart
       const uint32_t acc = tmem_base + which * TT_ACC_COLS;
       const uint32_t a_ring = tmem_base + TT_A_COL0 + which * 32;
-      // ring positions as counters: this thread's instruction stream is the critical path of the
+      // ring positions as counters: this thread's instruction stream is on the critical path of the
       // kernel, so no division or modulo per stage
       uint32_t sa = 0, sb = 0, phb = 0;
       for (int w = blockIdx.x; w < n_work && alive; w += gridDim.x, ++tix) {
@@ -337,44 +329,26 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
         const int nrows = p.item_nrows[item];
         const int N = (nrows + TC_BOXN - 1) / TC_BOXN * TC_BOXN;
         const uint32_t idesc = umma_idesc(N);
-        if (which == 0) TT_TRACE(240 + tix, 3);
         if (!mbar_wait(acc_empty, (tix & 1u) ^ 1u, abort_flag, p.status, TC_ERR_MMA_WAIT, 1)) break;
-        if (which == 0) TT_TRACE(240 + tix, 4);
         tc_fence_after();
-        // Two stages per visit (KB is even): both "filled" barriers are awaited first and the eight MMAs
-        // go out back to back.  A wait plus the loop around it keeps this thread away from the tensor
-        // core for several hundred cycles; with one stage per visit the queue behind it (four MMAs of
-        // each issuer) ran dry in that time.
-        for (int kb = 0; kb < KB; kb += 2) {
+        for (int kb = 0; kb < KB; ++kb) {
           if (which == 0) TT_TRACE(tix * KB + kb, 0);
-          const uint32_t sb0 = sb, ph0 = phb;
-          uint32_t sb1 = sb + 1, ph1 = phb;
-          if (sb1 == TT_B_STAGES) {
-            sb1 = 0;
-            ph1 ^= 1u;
-          }
-          if (!mbar_wait(full_s + 8 * sb0, ph0, abort_flag, p.status, TC_ERR_MMA_WAIT, 1) ||
-              !mbar_wait(full_s + 8 * sb1, ph1, abort_flag, p.status, TC_ERR_MMA_WAIT, 1)) {
+          if (!mbar_wait(full_s + 8 * sb, phb, abort_flag, p.status, TC_ERR_MMA_WAIT, 1)) {
             alive = false;
             break;
           }
           if (which == 0) TT_TRACE(tix * KB + kb, 1);
           tc_fence_after();
-          const uint32_t sa1 = sa == TT_A_STAGES - 1 ? 0u : sa + 1;
           // both issuers commit: the rings are refilled once both accumulators have read them
-          tt_issue_stage(acc, a_ring + sa * 64, bdesc_ring + (uint64_t)(sb0 * (TT_B_BYTES >> 4)), idesc, kb ? 1u : 0u, empty_s + 8 * sb0);
-          tt_issue_stage(acc, a_ring + sa1 * 64, bdesc_ring + (uint64_t)(sb1 * (TT_B_BYTES >> 4)), idesc, 1u, empty_s + 8 * sb1);
+          tt_issue_stage(acc, a_ring + sa * 64, bdesc_ring + (uint64_t)(sb * (TT_B_BYTES >> 4)), idesc, kb ? 1u : 0u, empty_s + 8 * sb);
           if (which == 0) TT_TRACE(tix * KB + kb, 2);
-          sa = sa1 == TT_A_STAGES - 1 ? 0u : sa1 + 1;
-          sb = sb1 + 1;
-          phb = ph1;
-          if (sb == TT_B_STAGES) {
+          if (++sa == TT_A_STAGES) sa = 0;
+          if (++sb == TT_B_STAGES) {
             sb = 0;
             phb ^= 1u;
           }
         }
         if (alive) umma_commit(acc_full);
-        if (which == 0) TT_TRACE(240 + tix, 5);
       }
     }
   } else if (warp < 2 + TC_EPI_WARPS) {
@@ -471,7 +445,14 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + TT_A_COL0 + mtx * 32;
     uint32_t it0 = 0;
     bool alive = true;
+    // The conversion runs BEFORE the wait for the slot, so that only the store stands between the
+    // slot's release and the barrier that hands it to the issuing threads.
     auto stage = [&](const auto &pk, uint32_t it) -> bool {
+      uint32_t r[32];
+      if constexpr (FMT == COLI_FMT_NVFP4)
+        tt_convert(pk, r);
+      else
+        tt_convert8<FMT>(pk, r);
       const uint32_t sa = it % TT_A_STAGES;
       bool ok = true;
       if (mtx == 0 && quarter == 0 && lane == 0) TT_TRACE(it, 3);
@@ -483,10 +464,8 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
         tc_fence_after();
       }
       if (mtx == 0 && quarter == 0 && lane == 0) TT_TRACE(it, 4);
-      if constexpr (FMT == COLI_FMT_NVFP4)
-        tt_emit_stage(pk, taddr + sa * 64);
-      else
-        tt_emit_stage<FMT>(pk, taddr + sa * 64);
+      tmem_st32(taddr + sa * 64, r);
+      tmem_st_wait();
       if (mtx == 0 && quarter == 0 && lane == 0) TT_TRACE(it, 5);
       tc_fence_before();
       __syncwarp();
@@ -514,12 +493,7 @@ __global__ void __launch_bounds__(TT_THREADS, 1) k_ffn_tct(const __grid_constant
         pb = pa;
         if (kb0 < KB) pa = tt_load_packed(wr, Op, grow, kb0);
         if (kb0 + 2 < KB) pb = tt_load_packed(wr, Op, grow, kb0 + 2);
-        const int pf = p.pf_stages;
         for (int kb = kb0; kb < KB && alive; kb += 4) {
-          if (pf > 0) {
-            tt_prefetch_packed(wr, Op, grow, kb + pf, KB);
-            tt_prefetch_packed(wr, Op, grow, kb + pf + 2, KB);
-          }
           alive = stage(pa, it0 + kb);
           if (kb + 4 < KB) pa = tt_load_packed(wr, Op, grow, kb + 4);
           if (alive && kb + 2 < KB) alive = stage(pb, it0 + kb + 2);
@@ -562,14 +536,15 @@ static int launch_tct(const TcParams &p, const void *rows_base, int rows_cap, in
   const size_t smem = (size_t)TtBudget<ACC>::B_STAGES * TtBudget<ACC>::B_BYTES + 1024 /*align*/ + 8 * TtBudget<ACC>::NBARS + 16 + 64;
   static ColiPerDeviceOnce attr_once;
   if (!coli_set_smem_limit(attr_once, k_ffn_tct<GATED, FMT, ACC>, smem, "tcgen05 kernel shared-memory attribute")) return 0;
-  CUtensorMap map;
-  if (!make_rows_map(&map, rows_base, rows_cap, GATED ? p.H : p.I)) return 0;
+  TtMaps maps;
+  for (int j = 0; j < TCT_MAX_TOKENS / TC_BOXN; ++j)
+    if (!make_rows_map(&maps.m[j], rows_base, rows_cap, GATED ? p.H : p.I, (j + 1) * TC_BOXN)) return 0;
   const int FT = GATED ? TC_BM : 2 * TC_BM;
   const int n_ftiles = ((GATED ? p.I : p.H) + FT - 1) / FT;
   const long max_work = (long)p.max_items * n_ftiles;
   const int grid = (int)(max_work < sm_count ? max_work : sm_count);
   if (grid <= 0) return 1;
-  k_ffn_tct<GATED, FMT, ACC><<<grid, TT_THREADS, smem, st>>>(map, p);
+  k_ffn_tct<GATED, FMT, ACC><<<grid, TT_THREADS, smem, st>>>(maps, p);
   coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "tcgen05 expert ffn launch") ? 1 : 0;
 }

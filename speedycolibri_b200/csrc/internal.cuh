@@ -219,7 +219,6 @@ struct TcParams {
   __nv_bfloat16 *y;  // [rows, H]
   int *status;       // device word: 0, or the code of the first bounded wait that gave up
   ActParams act;
-  int pf_stages;     // tensor-memory kernel: weight bytes are requested into L2 this many 64-k stages ahead (0 = off)
 };
 // x_rows: f16 [rows_cap, H] expert-contiguous rows (row index = position in the work list)
 int launch_gate_up_tc(const TcParams &p, const void *x_rows, int rows_cap, int sm_count, cudaStream_t st);

@@ -171,8 +171,8 @@ static inline EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// f16 [rows, K] row-major; box = 64 k x 32 rows; 128-byte swizzle; out-of-range reads give zeros
-static inline bool make_rows_map(CUtensorMap *map, const void *base, int rows, int K) {
+// f16 [rows, K] row-major; box = 64 k x box_rows rows; 128-byte swizzle; out-of-range reads give zeros
+static inline bool make_rows_map(CUtensorMap *map, const void *base, int rows, int K, int box_rows = TC_BOXN) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   if ((reinterpret_cast<uintptr_t>(base) & 15) || (K % 8)) {
@@ -181,7 +181,7 @@ static inline bool make_rows_map(CUtensorMap *map, const void *base, int rows, i
   }
   const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)TC_BOXN};
+  const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
