@@ -85,8 +85,14 @@ __device__ __forceinline__ void tc_store_tile(uint8_t *tile, int row, int c, con
   *reinterpret_cast<uint4 *>(rbase + (((c * 4 + 3) ^ sw) << 4)) = tc_dequant_word(pk.q.w, m1);
 }
 
+// The token tile of a stage arrives as ONE box of N rows (the copy engine of an SM takes about 64
+// cycles per box plus 4 per 128-byte row, so eight 32-row boxes per 256-token stage cost a third
+// more than one): one tensor map per box height.
+struct TcMaps {
+  CUtensorMap m[TC_MAX_TOKENS / TC_BOXN];
+};
 template <bool GATED>
-__global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __grid_constant__ CUtensorMap tmap, TcParams p) {
+__global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __grid_constant__ TcMaps maps, TcParams p) {
   constexpr int MATS = 2;    // gate + up of the same 128 features, or two adjacent 128-feature tiles of down
   constexpr int STAGES = 3;
   constexpr int STAGE_BYTES = MATS * TC_A_BYTES + TC_B_BYTES;
@@ -141,6 +147,7 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
         const int item = w / n_ftiles;
         const int row0 = p.item_row0[item], nrows = p.item_nrows[item];
         const int N = (nrows + TC_BOXN - 1) / TC_BOXN * TC_BOXN;
+        const CUtensorMap *tmap = &maps.m[N / TC_BOXN - 1];  // the map whose box is N rows
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
           if (!mbar_wait(empty + 8 * s, ph ^ 1u, abort_flag, p.status, TC_ERR_TMA_WAIT, 64)) {
@@ -149,8 +156,7 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
           }
           const uint32_t dst = smem_u32(smem + s * STAGE_BYTES + MATS * TC_A_BYTES);
           mbar_expect_tx(full_b + 8 * s, (uint32_t)N * TC_BK * 2);
-          for (int j = 0; j < N / TC_BOXN; ++j)
-            tma_load_2d(dst + j * (TC_BOXN * TC_BK * 2), &tmap, kb * TC_BK, row0 + j * TC_BOXN, full_b + 8 * s);
+          tma_load_2d(dst, tmap, kb * TC_BK, row0, full_b + 8 * s);
         }
       }
       if (!alive) {
@@ -343,14 +349,15 @@ static int launch_tc(const TcParams &p, const void *rows_base, int rows_cap, int
   const size_t smem = (size_t)STAGES * (MATS * TC_A_BYTES + TC_B_BYTES) + 1024 /*align*/ + 8 * (3 * STAGES + 4) + 16 + 64;
   static ColiPerDeviceOnce attr_once;
   if (!coli_set_smem_limit(attr_once, k_ffn_tc<GATED>, smem, "tcgen05 kernel shared-memory attribute")) return 0;
-  CUtensorMap map;
-  if (!make_rows_map(&map, rows_base, rows_cap, GATED ? p.H : p.I)) return 0;
+  TcMaps maps;
+  for (int j = 0; j < TC_MAX_TOKENS / TC_BOXN; ++j)
+    if (!make_rows_map(&maps.m[j], rows_base, rows_cap, GATED ? p.H : p.I, (j + 1) * TC_BOXN)) return 0;
   const int FT = GATED ? TC_BM : 2 * TC_BM;
   const int n_ftiles = ((GATED ? p.I : p.H) + FT - 1) / FT;
   const long max_work = (long)p.max_items * n_ftiles;
   const int grid = (int)(max_work < sm_count ? max_work : sm_count);
   if (grid <= 0) return 1;
-  k_ffn_tc<GATED><<<grid, TcCfg<GATED>::THREADS, smem, st>>>(map, p);
+  k_ffn_tc<GATED><<<grid, TcCfg<GATED>::THREADS, smem, st>>>(maps, p);
   coli_count_launch(1);
   return coli_cuda_check(cudaGetLastError(), "tcgen05 expert ffn launch") ? 1 : 0;
 }

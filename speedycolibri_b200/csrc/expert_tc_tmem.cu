@@ -8,9 +8,9 @@
 //   per stage straight into a ring of 32-column TMEM slots with tcgen05.st.  A stage holds two
 //   weight tiles (gate + up of the same 128 features, or two adjacent 128-feature tiles of down);
 //   the ring is three stages deep beside 160-column accumulators, six beside 64-column ones.
-// * B operand: up to 160 token rows x 64 k of f16 activations per stage, copied by TMA
-//   (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a 6-deep shared-memory ring and
-//   shared by both weight tiles of the stage.
+// * B operand: up to 160 token rows x 64 k of f16 activations per stage, copied by TMA as ONE box
+//   (cp.async.bulk.tensor, 128-byte swizzle, no multicast; one tensor map per box height) into a
+//   6-deep shared-memory ring and shared by both weight tiles of the stage.
 // * tcgen05.mma kind::f16 with A from tensor memory and B through a shared-memory descriptor,
 //   two accumulators of 160 columns, each fed by its own issuing thread (the instruction stream
 //   of a single issuing thread, not the tensor core, bounded the first version of this kernel);
@@ -151,15 +151,6 @@ __device__ __forceinline__ void tt_convert(const TtPacked &pk, uint32_t (&r)[32]
     r[4 * j + 2] = o.z;
     r[4 * j + 3] = o.w;
   }
-}
-
-// 16 consecutive columns of this thread's lane
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
 }
 
 // FP8 (e4m3 codes, one byte per weight): the 64 codes of one row for one 64-k stage and the
