@@ -51,8 +51,20 @@ def measured_peaks():
 # and the first 12 hex digits of that file's sha256 at capture time: when the file has changed
 # since, the figure is stale and the bench prints null instead.  The c3 figures are the c3s capture
 # (same matrices, 1/8 of the experts and tokens, so 1/8 of every stream) times 8: a full c3 launch
-# holds too much on the device for a multi-pass capture.  The captures are summarised under profiles/.
+# holds too much on the device for a multi-pass capture.  c4 has no figure: its skewed routing leaves
+# a different share of the experts active than the small case c4s, so the streams do not scale by a
+# constant.  The captures are summarised under profiles/.
 NCU_TRAFFIC = {
+    ("c3s", 512, "gate_up"): (636922112, "profiles/k_ffn_tct_c3s_full.md", "expert_tc_tmem.cu", "9a233a922ce9"),
+    ("c3s", 512, "down"): (338477824, "profiles/k_ffn_tct_c3s_full.md", "expert_tc_tmem.cu", "9a233a922ce9"),
+    ("c3", 4096, "gate_up"): (5095376896, "profiles/k_ffn_tct_c3s_full.md (c3s capture x 8)", "expert_tc_tmem.cu", "9a233a922ce9"),
+    ("c3", 4096, "down"): (2707822592, "profiles/k_ffn_tct_c3s_full.md (c3s capture x 8)", "expert_tc_tmem.cu", "9a233a922ce9"),
+    ("c2", 512, "gate_up"): (442167552, "profiles/k_ffn_tct_c2_full.md", "expert_tc_tmem.cu", "9a233a922ce9"),
+    ("c2", 512, "down"): (226135295, "profiles/k_ffn_tct_c2_full.md", "expert_tc_tmem.cu", "9a233a922ce9"),
+    ("c1", 8, "gate_up"): (95071232, "profiles/k_ffn_mm_c1_full.md", "expert_small.cu", "e50bd732c27b"),
+    ("c1", 8, "down"): (46234624, "profiles/k_ffn_mm_c1_full.md", "expert_small.cu", "e50bd732c27b"),
+    ("c4s", 2048, "gate_up"): (1290228976, "profiles/k_ffn_tc_c4s_full.md", "expert_tc.cu", "828fcd761060"),
+    ("c4s", 2048, "down"): (738659936, "profiles/k_ffn_tc_c4s_full.md", "expert_tc.cu", "828fcd761060"),
 }
 
 
@@ -650,7 +662,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="c3", help="headline workload: c0 c1 c1_t1 c1_t4 c1_t8 c2 c3 c3s c4")
+    ap.add_argument("--workload", default="c3", help="headline workload: c0 c1 c1_t1 c1_t4 c1_t8 c2 c3 c3s c4 c4s")
     ap.add_argument("--workloads", default="all", help="other workloads reported under 'workloads': all, none, or a comma list")
     ap.add_argument("--tokens", type=int, default=0, help="override the headline workload's token count")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])

@@ -669,7 +669,8 @@ __global__ void __launch_bounds__(128) k_seg_count(PermuteParams p, int nchunk) 
     if (t >= t1) break;  // uniform across the warp
     const int e = ids[i];
     const bool valid = e >= 0 && e < p.E;
-    const unsigned same = __match_any_sync(0xffffffffu, valid ? e : -1 - lane);  // invalid lanes match nobody
+    // invalid lanes share one key: the instruction takes a pass per distinct key, and their group is never read
+    const unsigned same = __match_any_sync(0xffffffffu, valid ? e : -1);
     int base = 0;
     if (valid) base = cnt[e];
     __syncwarp();
@@ -855,7 +856,7 @@ __device__ __forceinline__ void permute_small_body(const PermuteParams &p, int m
     const int ln = (int)threadIdx.x;
     for (int t = 0; t < p.T; ++t) {  // lanes holding the same segment (a degenerate routing) rank among themselves
       const int s = ln < p.k ? idx_sm[t * p.k + ln] : -1;
-      const unsigned same = __match_any_sync(0xffffffffu, s >= 0 ? s : -1 - ln);
+      const unsigned same = __match_any_sync(0xffffffffu, s >= 0 ? s : -1);  // one key for all lanes without a row
       int base = 0;
       if (s >= 0) base = cnt[s];
       __syncwarp();
