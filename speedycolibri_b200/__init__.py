@@ -6,8 +6,9 @@ interface for that path:
 
 * :mod:`.backend`  — safe wrappers over the C ABI (the role of crates/colibri-backend/src/cuda.rs)
 * :mod:`.moe`      — ``Config`` / ``Expert`` / ``Layer`` / ``moe`` / ``route`` (crates/colibri-engine/src/moe.rs)
-* :mod:`.cluster`  — ``ExpertSharding`` and the expert-parallel ``moe_sharded``
-  (crates/colibri-cluster/src/sharding.rs, moe.rs:1620-1794) over NCCL all-to-all
+* :mod:`.cluster`  — ``ExpertSharding`` and ``ShardedMoe``, the expert-parallel block
+  (crates/colibri-cluster/src/sharding.rs, moe.rs:1620-1794): one library call per rank that
+  dispatches token rows to the experts' owners and brings the result rows back
 * :mod:`.configs`, :mod:`.synth` — the benchmark shapes and their seeded synthetic tensors
 
 There is no CPU fallback: importing :mod:`.backend` without the built library raises.
