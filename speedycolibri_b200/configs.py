@@ -79,6 +79,10 @@ CONFIGS = {
     # c4 with 48 experts and 2048 tokens: same matrices, skew and rows/expert (1 GB of weights)
     "c4s": MoeShape("c4s", H=6144, E=48, k=8, I=2048, T=2048, shared=False, zipf_s=1.2,
                     note="c4 shapes at 1/8 of the experts and tokens (profiling case)"),
+    # c3's router (H, E, routing rule, T) over experts of 1/16 of the width: the profiling case of the router kernels
+    "c3r": MoeShape("c3r", H=7168, E=256, k=8, I=128, T=4096, score=SCORE_SIGMOID, norm_topk=True,
+                    routed_scale=2.5, n_group=8, topk_group=4, select_bias_std=0.01,
+                    note="c3's router with thin experts (profiling case)"),
     # small shapes for tests
     "tiny": MoeShape("tiny", H=64, E=8, k=2, I=32, T=5, norm_topk=True),
     "tiny_sig": MoeShape("tiny_sig", H=128, E=16, k=4, I=64, T=37, score=SCORE_SIGMOID, norm_topk=True,

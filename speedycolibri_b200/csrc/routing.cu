@@ -87,6 +87,19 @@ __global__ void __launch_bounds__(256) k_router_gemm(RouteParams p) {
 // output is one thread's k-ascending fmaf chain.  Needs H % 8 == 0.  The chain makes the kernel
 // issue-bound with a fixed time per CTA, so the variants trade work per thread against the number
 // of CTAs: the launcher takes the largest tile that still covers the SMs.
+// Two independent f32 FMAs in one instruction (sm_100): c.x = fma(a.x, b, c.x), c.y = fma(a.y, b, c.y),
+// each rounded as a scalar fmaf, so an output's k-ascending chain is unchanged.  It halves the FMA
+// instructions of k_router_gemm_big (0.51 -> 0.475 ms at 4096 tokens x 256 experts x 7168); the 8 x 8
+// register-tiled kernel below measured the same with and without it and keeps scalar FMAs.
+__device__ __forceinline__ void coli_ffma2(float2 &c, const float2 a, const float b) {
+  unsigned long long cc, aa, bb;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(cc) : "f"(c.x), "f"(c.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(aa) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(bb) : "f"(b));
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(cc) : "l"(aa), "l"(bb));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(c.x), "=f"(c.y) : "l"(cc));
+}
+
 template <int BM, int NT>
 __global__ void __launch_bounds__(NT) k_router_gemm_big(RouteParams p) {
   constexpr int TMR = BM * 16 / NT;  // token rows per thread
@@ -101,11 +114,12 @@ __global__ void __launch_bounds__(NT) k_router_gemm_big(RouteParams p) {
   float(*ws)[BK][LDW] = reinterpret_cast<float(*)[BK][LDW]>(rsm + 2 * BK * LDX);   // [2][BK][LDW]
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // tx -> 4 experts, ty -> TMR tokens
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  float acc[TMR][4];
+  static_assert(TMR % 2 == 0, "token rows are accumulated in pairs");
+  float2 acc[TMR / 2][4];  // .x = token row 2i, .y = row 2i + 1
 #pragma unroll
-  for (int i = 0; i < TMR; ++i)
+  for (int i = 0; i < TMR / 2; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    for (int j = 0; j < 4; ++j) acc[i][j] = make_float2(0.0f, 0.0f);
   // staging assignment: the threads of a warp take consecutive rows of one 8-k chunk, so their
   // transposed stores fall into consecutive banks
   const int sr = threadIdx.x % SR, sc = threadIdx.x / SR;
@@ -175,9 +189,9 @@ __global__ void __launch_bounds__(NT) k_router_gemm_big(RouteParams p) {
       const float4 b = *reinterpret_cast<const float4 *>(&ws[buf][kk][tx * 4]);
       const float bb[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-      for (int i = 0; i < TMR; ++i)
+      for (int i = 0; i < TMR / 2; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = __fmaf_rn(a[i], bb[j], acc[i][j]);
+        for (int j = 0; j < 4; ++j) coli_ffma2(acc[i][j], make_float2(a[2 * i], a[2 * i + 1]), bb[j]);
     }
     if (k0 + BK < p.H) {
       stage(buf ^ 1);  // chunk k0 + BK, fetched while this one was multiplied; that buffer was last read one barrier ago
@@ -191,7 +205,7 @@ __global__ void __launch_bounds__(NT) k_router_gemm_big(RouteParams p) {
     for (int j = 0; j < 4; ++j) {
       const int m = m0 + ty * TMR + i, n = n0 + tx * 4 + j;
       if (m < p.T && n < p.E) {
-        float v = acc[i][j];
+        float v = (i & 1) ? acc[i >> 1][j].y : acc[i >> 1][j].x;
         if (p.logit_bias) v = __fadd_rn(v, p.logit_bias[n]);
         p.logits[(size_t)m * p.E + n] = v;
       }
