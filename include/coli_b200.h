@@ -293,7 +293,10 @@ int coli_b200_moe_finish_dev(ColiMoe *moe, const float *partial_dev, const void 
  * Transport.  By default ("direct") every rank keeps its receive buffers in one slab that the other
  * ranks map at create time (cudaIpc handles, all-gathered over nccl_comm); the pack kernels store
  * rows, expert ids and the per-rank counts straight into the destination's slab over NVLink, and a
- * one-word NCCL all-gather after the stores is the barrier that tells a rank its senders are done.
+ * barrier after the stores tells a rank that its senders are done: every rank publishes a growing
+ * count in a flag row of each peer's slab and waits, for about two seconds at most, until all peers'
+ * counts in its own row have caught up (a wait that runs out fails the call: coli_b200_moe_check).
+ * COLI_EP_BARRIER=nccl at create replaces it with a one-word NCCL all-gather.
  * Nothing needs the host: the call only queues work on `stream`.  With COLI_EP_TRANSPORT=nccl in
  * the environment when the handle is created, rows are packed into send buffers and exchanged with
  * grouped ncclSend / ncclRecv instead; the host then waits once per call for the counts those need.

@@ -218,13 +218,23 @@ class ShardedMoe:
         return self.block.forward_ep(x, out)
 
     def stage_ms(self, x, steps: int):
-        """Per-stage milliseconds averaged over `steps` extra calls (every rank must take part)."""
+        """Per-stage milliseconds, the median over `steps` extra calls (every rank must take part).
+
+        The stages that end in a barrier also hold the time this rank waited for the slowest peer to
+        reach it, so one stalled host anywhere in the job shows up in every rank's figure for that
+        call; the median keeps a single such call from setting the figure."""
+        import numpy as np
+
         self.block.ep_profile(True)
+        per_call, prev = [], None
         for _ in range(steps):
             self.block.forward_ep(x)
-        ms, calls = self.block.ep_stage_ms()
+            ms, calls = self.block.ep_stage_ms()  # cumulative since profiling was switched on
+            cur = dict(ms)
+            per_call.append({k: cur[k] - (prev[k] if prev else 0.0) for k in cur})
+            prev = cur
         self.block.ep_profile(False)
-        return {k: v / max(calls, 1) for k, v in ms.items()}
+        return {k: float(np.median([c[k] for c in per_call])) for k in per_call[0]} if per_call else {}
 
     def close(self):
         import torch

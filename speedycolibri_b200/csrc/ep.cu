@@ -139,7 +139,10 @@ struct ColiEp {
   uint8_t *slab = nullptr;         // table + recv_meta + recv_x + ret_recv of THIS rank; peers write into it
   uint8_t *peer_slab[EP_MAX_WORLD] = {};  // the same slab of every rank as mapped into this process (own entry = slab)
   bool peer_mapped[EP_MAX_WORLD] = {};    // opened with cudaIpcOpenMemHandle (to be closed)
-  size_t table_off = 0, meta_off = 0, x_off = 0, ret_off = 0, slab_bytes = 0;
+  size_t table_off = 0, flag_off = 0, meta_off = 0, x_off = 0, ret_off = 0, slab_bytes = 0;
+  bool flag_barrier = true;  // direct transport: barrier by flags in the peers' slabs (else a one-word NCCL all-gather)
+  int32_t epoch = 0;         // barriers passed so far; every rank runs the same sequence
+  int32_t *bar_status = nullptr;  // device word: set when a barrier wait gave up
   int tl_cap = 0;                  // rows per source segment of recv_x / recv_meta
   struct EpRecvInfo *info = nullptr;  // device: what this rank received, derived from the table
   int32_t *bar_src = nullptr, *bar_dst = nullptr;  // operands of the tiny collective used as a barrier
@@ -391,6 +394,32 @@ __global__ void __launch_bounds__(256) k_ep_ret_pack(const __nv_bfloat16 *y, con
 }
 
 __global__ void k_set_i32(int32_t *p, int32_t v) { *p = v; }
+
+// Barrier of the direct transport.  Every thread that stored into a peer's slab has run
+// __threadfence_system() behind its stores and its kernel has ended (stream order) before this one
+// starts; thread d then publishes this rank's barrier count in peer d's flag row, and thread s waits
+// until rank s's count in the own row has reached it.  Counts only grow, so a peer that is already
+// one barrier ahead satisfies the wait as well.  The wait is bounded (about two seconds): a rank
+// whose peer never arrives sets the status word and goes on, and the call is reported as failed.
+// Ranks are separate processes on separate GPUs; one GPU never runs two ranks of this kernel (the
+// single-GPU emulation orders the ranks' phases by the stream instead).
+__global__ void k_ep_flag_barrier(EpPeers peers, size_t flag_off, int rank, int world, int32_t epoch, int32_t *status) {
+  const int t = threadIdx.x;
+  if (t >= world) return;
+  __threadfence_system();
+  int32_t *dst = reinterpret_cast<int32_t *>(peers.slab[t] + flag_off) + rank;
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(dst), "r"(epoch) : "memory");
+  const int32_t *src = reinterpret_cast<const int32_t *>(peers.slab[rank] + flag_off) + t;
+  bool ok = false;
+  for (uint32_t i = 0; i < (1u << 23) && !ok; ++i) {
+    int32_t v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(src) : "memory");
+    ok = v - epoch >= 0;
+    if (!ok) __nanosleep(200);
+  }
+  if (!ok) atomicExch(status, 1);
+  __threadfence_system();
+}
 
 // ---- direct transport -----------------------------------------------------------------------------------
 // Receive buffers have one fixed segment of tl_cap rows per source rank, so a sender needs nobody
@@ -866,7 +895,8 @@ int coli_ep_ensure(ColiMoe *m, void *comm) {
     auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
     ep->tl_cap = m->max_tokens;
     ep->table_off = 0;
-    ep->meta_off = up(sizeof(int32_t) * 2 * world * world);
+    ep->flag_off = up(sizeof(int32_t) * 2 * world * world);
+    ep->meta_off = ep->flag_off + 256;  // one row of barrier counts, [world] int32
     ep->x_off = ep->meta_off + up(sizeof(int32_t) * (size_t)world * ep->tl_cap * k);
     ep->ret_off = ep->x_off + up(sizeof(__nv_bfloat16) * (size_t)world * ep->tl_cap * H);
     ep->slab_bytes = ep->ret_off + up(sizeof(__nv_bfloat16) * (size_t)ep->tl_cap * k * H);
@@ -876,7 +906,10 @@ int coli_ep_ensure(ColiMoe *m, void *comm) {
       m->ws_bytes += ep->slab_bytes;
       ep->peer_slab[rank] = ep->slab;
       ok = coli_cuda_check(cudaMemset(ep->slab, 0, ep->meta_off), "table clear") && ws_alloc(m, &ep->info, 1) &&
-           ws_alloc(m, &ep->bar_src, 1) && ws_alloc(m, &ep->bar_dst, (size_t)world);
+           ws_alloc(m, &ep->bar_src, 1) && ws_alloc(m, &ep->bar_dst, (size_t)world) && ws_alloc(m, &ep->bar_status, 1) &&
+           coli_cuda_check(cudaMemset(ep->bar_status, 0, sizeof(int32_t)), "flag clear");
+      const char *bk = getenv("COLI_EP_BARRIER");
+      ep->flag_barrier = !(bk && strcmp(bk, "nccl") == 0);
     }
     if (ok && comm && !ep_connect_direct(m)) ok = false;
   } else if (ok) {
@@ -932,6 +965,14 @@ int coli_ep_check(ColiMoe *m) {
     cudaMemset(m->ep->overflow, 0, sizeof(int));
     coli_set_error("an expert-parallel call brought more tokens than the handle's max_tokens=%d holds; its results are invalid", m->max_tokens);
     return 0;
+  }
+  if (m->ep->bar_status) {
+    CK(cudaMemcpy(&v, m->ep->bar_status, sizeof(int), cudaMemcpyDeviceToHost), "flag read");
+    if (v != 0) {
+      cudaMemset(m->ep->bar_status, 0, sizeof(int));
+      coli_set_error("an expert-parallel call gave up waiting for a peer rank at a barrier; its results are invalid");
+      return 0;
+    }
   }
   return 1;
 }
@@ -1028,10 +1069,19 @@ extern "C" int coli_b200_moe_block_ep_dev(ColiMoe *m, const void *x_dev, void *o
   if (ep->direct) {
     // the rows and counts were stored straight into the peers' slabs; a tiny collective after the stores
     // is the barrier that tells every rank that all of its senders are done (and nothing needs the host)
-    if (!nccl_ok(api, api->AllGather(ep->bar_src, ep->bar_dst, 1, COLI_NCCL_INT32, ep->comm, st), "dispatch barrier")) return 0;
+    auto barrier = [&](const char *what) -> bool {
+      if (!ep->flag_barrier) return nccl_ok(api, api->AllGather(ep->bar_src, ep->bar_dst, 1, COLI_NCCL_INT32, ep->comm, st), what);
+      colib::EpPeers peers;
+      for (int d = 0; d < EP_MAX_WORLD; ++d) peers.slab[d] = d < world ? ep->peer_slab[d] : nullptr;
+      ++ep->epoch;
+      colib::k_ep_flag_barrier<<<1, 32, 0, st>>>(peers, ep->flag_off, rank, world, ep->epoch, ep->bar_status);
+      coli_count_launch(1);
+      return coli_cuda_check(cudaGetLastError(), what);
+    };
+    if (!barrier("dispatch barrier")) return 0;
     EP_MARK(3);
     if (!ep_direct_phase_b(m, st)) return 0;
-    if (!nccl_ok(api, api->AllGather(ep->bar_src, ep->bar_dst, 1, COLI_NCCL_INT32, ep->comm, st), "return barrier")) return 0;
+    if (!barrier("return barrier")) return 0;
     if (!ep_phase_c(m, out_dev, T_local, st)) return 0;
     return ep_finish_timing(m);
   }
