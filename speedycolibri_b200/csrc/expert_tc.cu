@@ -236,8 +236,6 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
       const int f = ft * FT + lg * 32 + lane;  // accumulator 0; accumulator 1 is feature f + 128 of down
       const uint32_t tbase = tmem_base + buf * TC_MAX_TOKENS + ((uint32_t)(lg * 32) << 16);
       const uint32_t acc1_off = big ? TC_MAX_TOKENS : TC_MAX_TOKENS / 2;
-      __half *out_h = p.h + (size_t)row0 * Oout + f;
-      __nv_bfloat16 *out_y = p.y + (size_t)row0 * Oout + f;
       for (int c0 = 0; c0 < N; c0 += 16) {
         uint32_t g[16], u[16];
         tmem_ld16(tbase + c0, g);
@@ -246,30 +244,25 @@ __global__ void __launch_bounds__(TcCfg<GATED>::THREADS, 1) k_ffn_tc(const __gri
         // all 16 columns are computed first, branch-free, so that their dependent chains (scale,
         // exponential, reciprocal, two roundings) overlap; a branch per column would run them one
         // after the other.  Columns beyond the item's rows hold zeros and are simply not stored.
+        const int fq = f & ~3;  // first feature of this lane's quad
+        const int cols_valid = nrows - c0;
         if (GATED) {
-          __half hv[16];
+          uint32_t pk[8];
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            hv[j] = coli_f32_to_f16_via_bf16(coli_act_fast(__uint_as_float(g[j]) * s0, __uint_as_float(u[j]) * s1, p.act));
-          if (f < Oout) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (c0 + j < nrows) out_h[(size_t)(c0 + j) * Oout] = hv[j];
-          }
+          for (int j = 0; j < 8; ++j)
+            pk[j] = tc_pack_f16x2_via_bf16(coli_act_fast(__uint_as_float(g[2 * j]) * s0, __uint_as_float(u[2 * j]) * s1, p.act),
+                                           coli_act_fast(__uint_as_float(g[2 * j + 1]) * s0, __uint_as_float(u[2 * j + 1]) * s1, p.act));
+          tc_store_cols16(pk, p.h + (size_t)(row0 + c0) * Oout + fq, (size_t)Oout, cols_valid, fq < Oout, lane);
         } else {
-          __nv_bfloat16 y0[16], y1[16];
+          uint32_t pk0[8], pk1[8];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            y0[j] = __float2bfloat16_rn(__uint_as_float(g[j]) * s0);
-            y1[j] = __float2bfloat16_rn(__uint_as_float(u[j]) * s1);
+          for (int j = 0; j < 8; ++j) {
+            pk0[j] = tc_pack_bf16x2(__uint_as_float(g[2 * j]) * s0, __uint_as_float(g[2 * j + 1]) * s0);
+            pk1[j] = tc_pack_bf16x2(__uint_as_float(u[2 * j]) * s1, __uint_as_float(u[2 * j + 1]) * s1);
           }
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (c0 + j < nrows) {
-              __nv_bfloat16 *dst = out_y + (size_t)(c0 + j) * Oout;
-              if (f < Oout) *dst = y0[j];
-              if (f + TC_BM < Oout) dst[TC_BM] = y1[j];
-            }
+          __nv_bfloat16 *yq = p.y + (size_t)(row0 + c0) * Oout + fq;
+          tc_store_cols16(pk0, yq, (size_t)Oout, cols_valid, fq < Oout, lane);
+          tc_store_cols16(pk1, yq + TC_BM, (size_t)Oout, cols_valid, fq + TC_BM < Oout, lane);
         }
       }
       tc_fence_before();

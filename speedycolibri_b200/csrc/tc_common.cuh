@@ -151,6 +151,53 @@ __device__ __forceinline__ void tc_scales(uint32_t sc, uint32_t &m0, uint32_t &m
   m1 = __byte_perm(v, v, 0x3232);
 }
 
+// ---- epilogue stores ------------------------------------------------------------------------------------
+// An epilogue lane owns ONE feature (its TMEM lane) and 16 token columns of it, while the result
+// matrices are token-major: written lane by lane, every value is a 2-byte store of its own, and
+// those store instructions (32 per 16-column chunk of the down kernel) were what the epilogue
+// spent its time on.  Instead the four lanes of a quad (features 4q .. 4q+3) exchange their values
+// with two shuffles per four columns, so that lane r of the quad holds the four features of column
+// 4g + r and writes them with one 8-byte store: a quarter of the store instructions.
+__device__ __forceinline__ uint32_t tc_pack_bf16x2(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+// two f32 -> each rounded to bf16, then held as f16 (saturating): the pair form of coli_f32_to_f16_via_bf16
+__device__ __forceinline__ uint32_t tc_pack_f16x2_via_bf16(float lo, float hi) {
+  const uint32_t b = tc_pack_bf16x2(lo, hi);
+  const float rl = fminf(fmaxf(__uint_as_float(b << 16), -65504.0f), 65504.0f);
+  const float rh = fminf(fmaxf(__uint_as_float(b & 0xffff0000u), -65504.0f), 65504.0f);
+  uint32_t d;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(rh), "f"(rl));
+  return d;
+}
+// pk[i] = the lane's values of columns 2i (low half) and 2i + 1 (high half), 16-bit each.
+// quad_base = &out[first column of the chunk][feature of the quad's first lane], ld = elements
+// per token row, cols_valid = how many of the 16 columns are rows of the item, feat_ok = the quad's
+// features exist (feature counts are multiples of 8, so a quad is whole or absent).  Every lane of
+// the warp must call this (shuffles).
+template <typename T16>
+__device__ __forceinline__ void tc_store_cols16(const uint32_t (&pk)[8], T16 *quad_base, size_t ld, int cols_valid, bool feat_ok,
+                                                int lane) {
+  static_assert(sizeof(T16) == 2, "16-bit elements");
+  const bool odd = (lane & 1) != 0, hi2 = (lane & 2) != 0;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const uint32_t p01 = pk[2 * g], p23 = pk[2 * g + 1];
+    // lanes 2j and 2j+1: the even lane keeps columns 0 and 2 of the group, the odd one 1 and 3
+    const uint32_t send1 = odd ? __byte_perm(p01, p23, 0x5410) : __byte_perm(p01, p23, 0x7632);
+    const uint32_t r1 = __shfl_xor_sync(0xffffffffu, send1, 1);
+    const uint32_t xa = odd ? __byte_perm(p01, r1, 0x3254) : __byte_perm(p01, r1, 0x5410);  // features (even, odd) of column odd / 0
+    const uint32_t xb = odd ? __byte_perm(p23, r1, 0x3276) : __byte_perm(p23, r1, 0x7610);  // ... of column 2 + odd
+    // lanes j and j+2: the lower pair keeps column xa and takes the upper pair's features of it
+    const uint32_t r2 = __shfl_xor_sync(0xffffffffu, hi2 ? xa : xb, 2);
+    const uint32_t o0 = hi2 ? r2 : xa, o1 = hi2 ? xb : r2;
+    const int col = 4 * g + (odd ? 1 : 0) + (hi2 ? 2 : 0);
+    if (feat_ok && col < cols_valid) *reinterpret_cast<uint2 *>(quad_base + (size_t)col * ld) = make_uint2(o0, o1);
+  }
+}
+
 // ---- host side ----------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
