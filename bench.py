@@ -55,16 +55,16 @@ def measured_peaks():
 # a different share of the experts active than the small case c4s, so the streams do not scale by a
 # constant.  The captures are summarised under profiles/.
 NCU_TRAFFIC = {
-    ("c3s", 512, "gate_up"): (636922112, "profiles/k_ffn_tct_c3s_full.md", "expert_tc_tmem.cu", "9a233a922ce9"),
-    ("c3s", 512, "down"): (338477824, "profiles/k_ffn_tct_c3s_full.md", "expert_tc_tmem.cu", "9a233a922ce9"),
-    ("c3", 4096, "gate_up"): (5095376896, "profiles/k_ffn_tct_c3s_full.md (c3s capture x 8)", "expert_tc_tmem.cu", "9a233a922ce9"),
-    ("c3", 4096, "down"): (2707822592, "profiles/k_ffn_tct_c3s_full.md (c3s capture x 8)", "expert_tc_tmem.cu", "9a233a922ce9"),
-    ("c2", 512, "gate_up"): (442167552, "profiles/k_ffn_tct_c2_full.md", "expert_tc_tmem.cu", "9a233a922ce9"),
-    ("c2", 512, "down"): (226135295, "profiles/k_ffn_tct_c2_full.md", "expert_tc_tmem.cu", "9a233a922ce9"),
-    ("c1", 8, "gate_up"): (95071232, "profiles/k_ffn_mm_c1_full.md", "expert_small.cu", "e50bd732c27b"),
-    ("c1", 8, "down"): (46234624, "profiles/k_ffn_mm_c1_full.md", "expert_small.cu", "e50bd732c27b"),
-    ("c4s", 2048, "gate_up"): (1290228976, "profiles/k_ffn_tc_c4s_full.md", "expert_tc.cu", "828fcd761060"),
-    ("c4s", 2048, "down"): (738659936, "profiles/k_ffn_tc_c4s_full.md", "expert_tc.cu", "828fcd761060"),
+    ("c3s", 512, "gate_up"): (634600000, "profiles/k_ffn_tct_c3s_full.md", "expert_tc_tmem.cu", "2356b26d8fea"),
+    ("c3s", 512, "down"): (338200000, "profiles/k_ffn_tct_c3s_full.md", "expert_tc_tmem.cu", "2356b26d8fea"),
+    ("c3", 4096, "gate_up"): (5076800000, "profiles/k_ffn_tct_c3s_full.md (c3s capture x 8)", "expert_tc_tmem.cu", "2356b26d8fea"),
+    ("c3", 4096, "down"): (2705600000, "profiles/k_ffn_tct_c3s_full.md (c3s capture x 8)", "expert_tc_tmem.cu", "2356b26d8fea"),
+    ("c2", 512, "gate_up"): (442300000, "profiles/k_ffn_tct_c2_full.md", "expert_tc_tmem.cu", "2356b26d8fea"),
+    ("c2", 512, "down"): (224100000, "profiles/k_ffn_tct_c2_full.md", "expert_tc_tmem.cu", "2356b26d8fea"),
+    ("c1", 8, "gate_up"): (95500000, "profiles/k_ffn_mm_c1_full.md", "expert_small.cu", "3f21c1937e43"),
+    ("c1", 8, "down"): (46400000, "profiles/k_ffn_mm_c1_full.md", "expert_small.cu", "3f21c1937e43"),
+    ("c4s", 2048, "gate_up"): (1264600000, "profiles/k_ffn_tc_c4s_full.md", "expert_tc.cu", "454ac79fc581"),
+    ("c4s", 2048, "down"): (715900000, "profiles/k_ffn_tc_c4s_full.md", "expert_tc.cu", "454ac79fc581"),
 }
 
 
