@@ -61,8 +61,8 @@ NCU_TRAFFIC = {
     ("c3", 4096, "down"): (2705600000, "profiles/k_ffn_tct_c3s_full.md (c3s capture x 8)", "expert_tc_tmem.cu", "2356b26d8fea"),
     ("c2", 512, "gate_up"): (442300000, "profiles/k_ffn_tct_c2_full.md", "expert_tc_tmem.cu", "2356b26d8fea"),
     ("c2", 512, "down"): (224100000, "profiles/k_ffn_tct_c2_full.md", "expert_tc_tmem.cu", "2356b26d8fea"),
-    ("c1", 8, "gate_up"): (95500000, "profiles/k_ffn_mm_c1_full.md", "expert_small.cu", "3f21c1937e43"),
-    ("c1", 8, "down"): (46400000, "profiles/k_ffn_mm_c1_full.md", "expert_small.cu", "3f21c1937e43"),
+    ("c1", 8, "gate_up"): (94800128, "profiles/k_ffn_mm_c1_full.md", "expert_small.cu", "e50bd732c27b"),
+    ("c1", 8, "down"): (46207488, "profiles/k_ffn_mm_c1_full.md", "expert_small.cu", "e50bd732c27b"),
     ("c4s", 2048, "gate_up"): (1264600000, "profiles/k_ffn_tc_c4s_full.md", "expert_tc.cu", "454ac79fc581"),
     ("c4s", 2048, "down"): (715900000, "profiles/k_ffn_tc_c4s_full.md", "expert_tc.cu", "454ac79fc581"),
 }

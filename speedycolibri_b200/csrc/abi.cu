@@ -937,10 +937,6 @@ extern "C" int coli_b200_moe_check(ColiMoe *m) {
     cudaMemset(m->status, 0, sizeof(int));
     return 0;
   }
-  if (colib::coli_ffn_small_status() != 0) {
-    coli_set_error("the register-level expert kernel abandoned a bounded wait for its weight ring; results of that call are invalid");
-    return 0;
-  }
   return coli_ep_check(m);
 }
 

@@ -45,39 +45,6 @@ __device__ __forceinline__ uint4 ldg_nc_v4(const void *p) {
   return v;
 }
 
-// ---- shared-memory weight ring of the tile-per-warp form: mbarrier + bulk copies -------------------
-// The packed slab of a (16-row tile, k-tile) is one contiguous run of bytes (1 KB of nibbles + 128 B
-// of block scales for NVFP4, 2 KB of codes for FP8), so one lane fetches it with cp.async.bulk and
-// the bytes in flight cost no registers: with the ring in registers a warp kept one k-tile ahead
-// and an SM held about 37 KB in flight, short of what the HBM latency needs for the bandwidth.
-__device__ int g_ffn_ring_status;  // 0, or 1 after a ring wait gave up (read by coli_ffn_small_status)
-__device__ __forceinline__ uint32_t ffn_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void ffn_mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void ffn_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void ffn_bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
-// Bounded: about a second of suspended polls, then the warp reports and gives up.
-__device__ __forceinline__ bool ffn_mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < (1u << 20); ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(1000u)
-        : "memory");
-    if (ok) return true;
-  }
-  atomicExch(&g_ffn_ring_status, 1);
-  return false;
-}
-
 // Two bytes of a NVFP4 word (each byte = two consecutive k, low nibble first) -> two f16x2.
 // HI selects bytes 2,3 of the word, otherwise bytes 0,1.
 template <bool HI>
@@ -130,40 +97,6 @@ __device__ __forceinline__ void load_a(AFrag<FMT> &f, const WeightRef &w, int Op
     f.lo[1] = ldg_nc_v4(slab + lane * 32 + 16);
     f.hi[0] = ldg_nc_v4(slab + 1024 + lane * 32);
     f.hi[1] = ldg_nc_v4(slab + 1024 + lane * 32 + 16);
-    f.sc = 0;
-  }
-}
-
-// Bytes of one ring stage per matrix, and the copies that fill it (one lane).
-template <int FMT>
-struct RingStage {
-  static constexpr int Q = FMT == COLI_FMT_NVFP4 ? 1024 : 2048;
-  static constexpr int S = FMT == COLI_FMT_NVFP4 ? 128 : 0;
-  static constexpr int BYTES = Q + S;
-};
-template <int FMT>
-__device__ __forceinline__ void ring_issue(uint32_t dst, const WeightRef &w, int Op, int r0, int kt, uint32_t bar) {
-  if (FMT == COLI_FMT_NVFP4) {
-    ffn_bulk_load(dst, w.q + ((size_t)kt * Op + r0) * 64, 1024, bar);
-    ffn_bulk_load(dst + 1024, w.s + ((size_t)kt * Op + r0) * 8, 128, bar);
-  } else {
-    ffn_bulk_load(dst, w.q + ((size_t)kt * Op + r0) * 128, 2048, bar);
-  }
-}
-// The same fragment load_a takes from global memory, from a ring stage.
-template <int FMT>
-__device__ __forceinline__ void load_a_smem(AFrag<FMT> &f, const uint8_t *st, int lane) {
-  if (FMT == COLI_FMT_NVFP4) {
-    f.lo[0] = *reinterpret_cast<const uint4 *>(st + lane * 16);
-    f.hi[0] = *reinterpret_cast<const uint4 *>(st + 512 + lane * 16);
-    const uint32_t s0 = *reinterpret_cast<const uint16_t *>(st + 1024 + lane * 2);
-    const uint32_t s1 = *reinterpret_cast<const uint16_t *>(st + 1024 + 64 + lane * 2);
-    f.sc = s0 | (s1 << 16);
-  } else {
-    f.lo[0] = *reinterpret_cast<const uint4 *>(st + lane * 32);
-    f.lo[1] = *reinterpret_cast<const uint4 *>(st + lane * 32 + 16);
-    f.hi[0] = *reinterpret_cast<const uint4 *>(st + 1024 + lane * 32);
-    f.hi[1] = *reinterpret_cast<const uint4 *>(st + 1024 + lane * 32 + 16);
     f.sc = 0;
   }
 }
@@ -229,24 +162,10 @@ __global__ void __launch_bounds__(SPLITK ? 256 : 64, SPLITK                  ? 1
   constexpr int D = 2;
   constexpr int R = NB <= 2 ? 4 : 2;
   constexpr int PF = R - 1;
-  // ring depth (k-tiles) of the tile-per-warp form's shared-memory weight ring
-  constexpr int S = FMT == COLI_FMT_NVFP4 ? 4 : 3;
-  constexpr int STAGE = MATS * RingStage<FMT>::BYTES;
-  extern __shared__ __align__(128) float red[];  // SPLITK: [W][MATS*NB*4][32]; otherwise the rings, [W][S][STAGE] bytes
-  __shared__ uint64_t ring_bar[2][4];            // tile-per-warp form: two warps, S <= 4 stages each
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
-  uint8_t *ring_sm = reinterpret_cast<uint8_t *>(red) + (size_t)warp * S * STAGE;
-  uint32_t fill = 0, use = 0;  // stages issued / consumed by this warp since the kernel began
-  if (!SPLITK) {
-    if (lane == 0) {
-      for (int j = 0; j < S; ++j) ffn_mbar_init(ffn_smem_u32(&ring_bar[warp][j]), 1);
-      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    __syncwarp();
-  }
+  extern __shared__ __align__(16) float red[];  // [W][MATS*NB*4][32]
   coli_grid_dependency_sync();
   const int n_items = *p.n_items;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int K = GATED ? p.H : p.I;     // contraction length
   const int Oout = GATED ? p.I : p.H;  // output features
@@ -300,131 +219,79 @@ __global__ void __launch_bounds__(SPLITK ? 256 : 64, SPLITK                  ? 1
       }
     };
 
-    // Token fragments ride a register ring R quarter-k-tiles deep (unrolled, so every slot is a
-    // fixed set of registers); four quarters per k-tile and 4 % R == 0, so the slot of quarter c
-    // does not depend on the k-tile.
+    // Register rings, both unrolled so that every slot is a fixed set of registers (rotating
+    // slots with copies would make each iteration wait for the youngest load): packed weight
+    // fragments D k-tiles deep, token fragments R quarter-k-tiles deep.
+    AFrag<FMT> ring[D][MATS];
     uint4 xq[R][NB];
+#pragma unroll
+    for (int j = 0; j < D - 1; ++j) {
+      const int ktl = kt_first + j * kstep;
+      if (ktl < KT) {
+        load_a<FMT>(ring[j][0], w0, Op, r0, ktl, lane);
+        if (GATED) load_a<FMT>(ring[j][MATS - 1], w1, Op, r0, ktl, lane);
+      }
+    }
 #pragma unroll
     for (int f = 0; f < PF; ++f) load_x(xq[f % R], kt_first + (f / 4) * kstep, f % 4);
 
-    // one k-tile: 8 MMA steps per matrix and token block from the packed fragments `fr`
-    auto ktile = [&](const AFrag<FMT>(&fr)[MATS], int kt) {
-      AScale asc[MATS];
+    for (int kt0 = kt_first; kt0 < KT; kt0 += D * kstep) {
 #pragma unroll
-      for (int mtx = 0; mtx < MATS; ++mtx) asc[mtx] = decode_scales<FMT>(fr[mtx]);
-      float part[MATS][NB][4];
-      if (FMT == COLI_FMT_FP8_B128) {
+      for (int slot = 0; slot < D; ++slot) {
+        const int kt = kt0 + slot * kstep;
+        if (kt >= KT) break;
+        const int ktn = kt + (D - 1) * kstep;
+        if (ktn < KT) {
+          load_a<FMT>(ring[(slot + D - 1) % D][0], w0, Op, r0, ktn, lane);
+          if (GATED) load_a<FMT>(ring[(slot + D - 1) % D][MATS - 1], w1, Op, r0, ktn, lane);
+        }
+        AScale asc[MATS];
 #pragma unroll
-        for (int mtx = 0; mtx < MATS; ++mtx)
+        for (int mtx = 0; mtx < MATS; ++mtx) asc[mtx] = decode_scales<FMT>(ring[slot][mtx]);
+        float part[MATS][NB][4];
+        if (FMT == COLI_FMT_FP8_B128) {
 #pragma unroll
-          for (int j = 0; j < NB; ++j)
+          for (int mtx = 0; mtx < MATS; ++mtx)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) part[mtx][j][c] = 0.0f;
-      }
+            for (int j = 0; j < NB; ++j)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        load_x(xq[(c + PF) % R], kt + ((c + PF) / 4) * kstep, (c + PF) % 4);
-        const uint4(&xb)[NB] = xq[c % R];
+              for (int c = 0; c < 4; ++c) part[mtx][j][c] = 0.0f;
+        }
 #pragma unroll
-        for (int mm = 0; mm < 2; ++mm) {
-          const int m = 2 * c + mm;
+        for (int c = 0; c < 4; ++c) {
+          const int f = slot * 4 + c;  // position in the unrolled body; 4*D is a multiple of R
+          load_x(xq[(f + PF) % R], kt + ((c + PF) / 4) * kstep, (c + PF) % 4);
+          const uint4(&xb)[NB] = xq[f % R];
 #pragma unroll
-          for (int mtx = 0; mtx < MATS; ++mtx) {
-            uint32_t a[4];
-            decode_a<FMT>(fr[mtx], asc[mtx], m, a);
+          for (int mm = 0; mm < 2; ++mm) {
+            const int m = 2 * c + mm;
 #pragma unroll
-            for (int j = 0; j < NB; ++j) {
-              const uint32_t b0 = mm ? xb[j].z : xb[j].x, b1 = mm ? xb[j].w : xb[j].y;
-              if (FMT == COLI_FMT_FP8_B128)
-                mma_f16_16816(part[mtx][j], a, b0, b1);
-              else
-                mma_f16_16816(acc[mtx][j], a, b0, b1);
+            for (int mtx = 0; mtx < MATS; ++mtx) {
+              uint32_t a[4];
+              decode_a<FMT>(ring[slot][mtx], asc[mtx], m, a);
+#pragma unroll
+              for (int j = 0; j < NB; ++j) {
+                const uint32_t b0 = mm ? xb[j].z : xb[j].x, b1 = mm ? xb[j].w : xb[j].y;
+                if (FMT == COLI_FMT_FP8_B128)
+                  mma_f16_16816(part[mtx][j], a, b0, b1);
+                else
+                  mma_f16_16816(acc[mtx][j], a, b0, b1);
+              }
             }
           }
         }
-      }
-      if (FMT == COLI_FMT_FP8_B128) {
-        // one f32 scale per (128-row block, k-tile): convert.rs:731-741
+        if (FMT == COLI_FMT_FP8_B128) {
+          // one f32 scale per (128-row block, k-tile): convert.rs:731-741
 #pragma unroll
-        for (int mtx = 0; mtx < MATS; ++mtx) {
-          const float *sc = reinterpret_cast<const float *>(mtx == 0 ? w0.s : w1.s);
-          const float s = sc[(size_t)(r0 >> 7) * KT + kt];
+          for (int mtx = 0; mtx < MATS; ++mtx) {
+            const float *sc = reinterpret_cast<const float *>(mtx == 0 ? w0.s : w1.s);
+            const float s = sc[(size_t)(r0 >> 7) * KT + kt];
 #pragma unroll
-          for (int j = 0; j < NB; ++j)
+            for (int j = 0; j < NB; ++j)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) acc[mtx][j][c] = fmaf(s, part[mtx][j][c], acc[mtx][j][c]);
-        }
-      }
-    };
-
-    if (SPLITK) {
-      // packed weight fragments in a register ring D k-tiles deep (unrolled: rotating slots with
-      // copies would make each iteration wait for the youngest load)
-      AFrag<FMT> ring[D][MATS];
-#pragma unroll
-      for (int j = 0; j < D - 1; ++j) {
-        const int ktl = kt_first + j * kstep;
-        if (ktl < KT) {
-          load_a<FMT>(ring[j][0], w0, Op, r0, ktl, lane);
-          if (GATED) load_a<FMT>(ring[j][MATS - 1], w1, Op, r0, ktl, lane);
-        }
-      }
-      for (int kt0 = kt_first; kt0 < KT; kt0 += D * kstep) {
-#pragma unroll
-        for (int slot = 0; slot < D; ++slot) {
-          const int kt = kt0 + slot * kstep;
-          if (kt >= KT) break;
-          const int ktn = kt + (D - 1) * kstep;
-          if (ktn < KT) {
-            load_a<FMT>(ring[(slot + D - 1) % D][0], w0, Op, r0, ktn, lane);
-            if (GATED) load_a<FMT>(ring[(slot + D - 1) % D][MATS - 1], w1, Op, r0, ktn, lane);
+              for (int c = 0; c < 4; ++c) acc[mtx][j][c] = fmaf(s, part[mtx][j][c], acc[mtx][j][c]);
           }
-          ktile(ring[slot], kt);
         }
-      }
-    } else {
-      // packed weights through the shared-memory ring: S - 1 k-tiles are in flight ahead of the one
-      // being multiplied.  One lane issues the copies of a stage and arms its barrier; every lane
-      // waits on the barrier and takes its fragment.  The slot a new copy lands in is the one read
-      // in the previous iteration: the warp has converged since, and a proxy fence orders those
-      // reads before the copy engine's writes.
-      auto issue = [&](int kt) {
-        if (lane == 0) {
-          const uint32_t slot = fill % S;
-          const uint32_t bar = ffn_smem_u32(&ring_bar[warp][slot]);
-          const uint32_t dst = ffn_smem_u32(ring_sm + (size_t)slot * STAGE);
-          ffn_mbar_expect_tx(bar, STAGE);
-          ring_issue<FMT>(dst, w0, Op, r0, kt, bar);
-          if (GATED) ring_issue<FMT>(dst + RingStage<FMT>::BYTES, w1, Op, r0, kt, bar);
-        }
-        ++fill;
-      };
-      __syncwarp();
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#pragma unroll
-      for (int j = 0; j < S - 1; ++j)
-        if (j < KT) issue(j);
-      bool alive = true;
-      for (int kt = 0; kt < KT; ++kt) {
-        __syncwarp();
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        if (kt + S - 1 < KT) issue(kt + S - 1);
-        const uint32_t slot = use % S;
-        if (!ffn_mbar_wait(ffn_smem_u32(&ring_bar[warp][slot]), (use / S) & 1u)) {
-          alive = false;
-          break;
-        }
-        ++use;
-        AFrag<FMT> fr[MATS];
-        const uint8_t *st = ring_sm + (size_t)slot * STAGE;
-        load_a_smem<FMT>(fr[0], st, lane);
-        if (GATED) load_a_smem<FMT>(fr[MATS - 1], st + RingStage<FMT>::BYTES, lane);
-        ktile(fr, kt);
-      }
-      if (!alive) {
-        // copies already issued still land in this CTA's shared memory: give them time before the exit
-        for (int i2 = 0; i2 < 1000; ++i2) __nanosleep(1000);
-        return;
       }
     }
 
@@ -527,25 +394,19 @@ static int launch_one(const FfnParams &p, bool gated, cudaStream_t st) {
     if (!coli_cuda_check(cudaGetDevice(&dev), "device query")) return 0;
     int uncached = 0;
     int &resident_slot = (dev >= 0 && dev < 32) ? resident_tab[gated ? 1 : 0][dev] : uncached;
-    // the weight rings: W warps x S stages x (1 or 2 matrices) of packed slab bytes
-    const size_t ring_sm = (size_t)W * (FMT == COLI_FMT_NVFP4 ? 4 : 3) * (gated ? 2 : 1) * RingStage<FMT>::BYTES;
     if (resident_slot == 0) {
       int sms = 0, per_sm = 0;
       if (!coli_cuda_check(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "device query")) return 0;
-      // ask for the largest shared-memory carve-out: ten CTAs per SM hold 180 KB of rings
-      cudaError_t e = gated ? cudaFuncSetAttribute(k_ffn_mm<FMT, NB, true, false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100)
-                            : cudaFuncSetAttribute(k_ffn_mm<FMT, NB, false, false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-      if (!coli_cuda_check(e, "expert ffn carve-out attribute")) return 0;
-      e = gated ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_ffn_mm<FMT, NB, true, false>, W * 32, ring_sm)
-                : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_ffn_mm<FMT, NB, false, false>, W * 32, ring_sm);
+      const cudaError_t e = gated ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_ffn_mm<FMT, NB, true, false>, W * 32, 0)
+                                  : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_ffn_mm<FMT, NB, false, false>, W * 32, 0);
       if (!coli_cuda_check(e, "occupancy query")) return 0;
       resident_slot = sms * (per_sm > 0 ? per_sm : 1);
     }
     const int resident_ctas = resident_slot;
     const long max_ctas = ((long)row_tiles * p.max_items + W - 1) / W;
     const int grid = (int)(max_ctas < resident_ctas ? max_ctas : resident_ctas);
-    const cudaError_t e = gated ? launch_dependent(k_ffn_mm<FMT, NB, true, false>, dim3(grid), dim3(W * 32), ring_sm, st, p)
-                                : launch_dependent(k_ffn_mm<FMT, NB, false, false>, dim3(grid), dim3(W * 32), ring_sm, st, p);
+    const cudaError_t e = gated ? launch_dependent(k_ffn_mm<FMT, NB, true, false>, dim3(grid), dim3(W * 32), 0, st, p)
+                                : launch_dependent(k_ffn_mm<FMT, NB, false, false>, dim3(grid), dim3(W * 32), 0, st, p);
     coli_count_launch(1);
     return coli_cuda_check(e, "expert ffn launch") ? 1 : 0;
   }
@@ -577,18 +438,6 @@ static int launch_ffn_stage(const FfnParams &p, bool gated, cudaStream_t st) {
       return 0;
   }
 #undef COLI_DISPATCH
-}
-
-// 0, or 1 when a weight-ring wait of k_ffn_mm gave up on the current device since the last call
-// (the word is cleared by the read).
-int coli_ffn_small_status() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_ffn_ring_status, sizeof(int)) != cudaSuccess) return -1;
-  if (v != 0) {
-    const int zero = 0;
-    cudaMemcpyToSymbol(g_ffn_ring_status, &zero, sizeof(int));
-  }
-  return v;
 }
 
 int launch_gate_up_small(const FfnParams &p, cudaStream_t st) { return launch_ffn_stage(p, true, st); }

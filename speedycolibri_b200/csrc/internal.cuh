@@ -204,7 +204,6 @@ struct FfnParams {
 int launch_gate_up_small(const FfnParams &p, cudaStream_t st);  // h = silu(gate x) * (up x)
 int launch_down_small(const FfnParams &p, cudaStream_t st);     // y = down h
 int launch_ffn_small(const FfnParams &p, cudaStream_t st);      // both
-int coli_ffn_small_status();  // 0, 1 = a bounded wait inside k_ffn_mm gave up (clears the word), -1 = read failed
 
 // expert_tc.cu — tcgen05 path for prefill-sized segments
 constexpr int TC_MAX_TOKENS = 256;  // token rows per tile = rows per work item on this path
