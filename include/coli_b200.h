@@ -310,6 +310,12 @@ int coli_b200_moe_block_ep_dev(ColiMoe *moe, const void *x_dev, void *out_dev, i
  * per rank. */
 int coli_b200_moe_block_ep_emulate(ColiMoe *const *ranks, int world, const void *const *x_dev, void *const *out_dev,
                                    const int *T_local, void *stream);
+/* Test aid for the bounded wait of the direct transport's barrier: one barrier on this handle alone,
+ * with a wait of about 13 ms.  peers_arrive != 0 writes the peers' counts into the own flag row
+ * first (the wait succeeds); with 0 nothing sets them, the wait runs out and coli_b200_moe_check
+ * reports the abandoned barrier (and clears the report).  The handle must have made an
+ * expert-parallel or emulated call before. */
+int coli_b200_ep_barrier_probe(ColiMoe *moe, int peers_arrive, void *stream);
 /* For callers without a communicator of their own: rank 0 obtains a 128-byte id, passes it to the
  * other ranks by any means, and every rank creates its end (ncclGetUniqueId / ncclCommInitRank of
  * the NCCL library already in the process, else libnccl.so.2).  `device` must be initialised. */

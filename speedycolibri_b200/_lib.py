@@ -134,6 +134,7 @@ SIGNATURES = {
     "coli_b200_moe_finish_dev": (_i, [_P, _P, _P, _P, _i, _P]),
     "coli_b200_moe_block_ep_dev": (_i, [_P, _P, _P, _i, _P]),
     "coli_b200_moe_block_ep_emulate": (_i, [_PP, _i, _PP, _PP, C.POINTER(_i), _P]),
+    "coli_b200_ep_barrier_probe": (_i, [_P, _i, _P]),
     "coli_b200_nccl_unique_id": (_i, [_P]),
     "coli_b200_nccl_comm_create": (_i, [_PP, _P, _i, _i, _i]),
     "coli_b200_nccl_comm_destroy": (None, [_P]),

@@ -108,6 +108,7 @@ bool nccl_ok(NcclApi *api, ncclResult_t r, const char *what) {
 }  // namespace
 
 constexpr int EP_MAX_WORLD = 8;  // the GPUs of one NVSwitch box
+constexpr uint32_t EP_BARRIER_POLLS = 1u << 23;  // x 200 ns of sleep between polls: about two seconds
 constexpr int EP_MAX_K = 16;     // a token's destination ranks are packed 4 bits per kk
 
 // Stages timed when profiling is on (coli_b200_ep_stage_ms).
@@ -394,6 +395,9 @@ __global__ void __launch_bounds__(256) k_ep_ret_pack(const __nv_bfloat16 *y, con
 }
 
 __global__ void k_set_i32(int32_t *p, int32_t v) { *p = v; }
+__global__ void k_fill_i32(int32_t *p, int n, int32_t v) {
+  if ((int)threadIdx.x < n) p[threadIdx.x] = v;
+}
 
 // Barrier of the direct transport.  Every thread that stored into a peer's slab has run
 // __threadfence_system() behind its stores and its kernel has ended (stream order) before this one
@@ -403,7 +407,7 @@ __global__ void k_set_i32(int32_t *p, int32_t v) { *p = v; }
 // whose peer never arrives sets the status word and goes on, and the call is reported as failed.
 // Ranks are separate processes on separate GPUs; one GPU never runs two ranks of this kernel (the
 // single-GPU emulation orders the ranks' phases by the stream instead).
-__global__ void k_ep_flag_barrier(EpPeers peers, size_t flag_off, int rank, int world, int32_t epoch, int32_t *status) {
+__global__ void k_ep_flag_barrier(EpPeers peers, size_t flag_off, int rank, int world, int32_t epoch, uint32_t max_polls, int32_t *status) {
   const int t = threadIdx.x;
   if (t >= world) return;
   __threadfence_system();
@@ -411,7 +415,7 @@ __global__ void k_ep_flag_barrier(EpPeers peers, size_t flag_off, int rank, int 
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(dst), "r"(epoch) : "memory");
   const int32_t *src = reinterpret_cast<const int32_t *>(peers.slab[rank] + flag_off) + t;
   bool ok = false;
-  for (uint32_t i = 0; i < (1u << 23) && !ok; ++i) {
+  for (uint32_t i = 0; i < max_polls && !ok; ++i) {
     int32_t v;
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(src) : "memory");
     ok = v - epoch >= 0;
@@ -1074,7 +1078,7 @@ extern "C" int coli_b200_moe_block_ep_dev(ColiMoe *m, const void *x_dev, void *o
       colib::EpPeers peers;
       for (int d = 0; d < EP_MAX_WORLD; ++d) peers.slab[d] = d < world ? ep->peer_slab[d] : nullptr;
       ++ep->epoch;
-      colib::k_ep_flag_barrier<<<1, 32, 0, st>>>(peers, ep->flag_off, rank, world, ep->epoch, ep->bar_status);
+      colib::k_ep_flag_barrier<<<1, 32, 0, st>>>(peers, ep->flag_off, rank, world, ep->epoch, EP_BARRIER_POLLS, ep->bar_status);
       coli_count_launch(1);
       return coli_cuda_check(cudaGetLastError(), what);
     };
@@ -1121,6 +1125,34 @@ extern "C" int coli_b200_moe_block_ep_dev(ColiMoe *m, const void *x_dev, void *o
   if (!ok) return 0;
   if (!ep_phase_c(m, out_dev, T_local, st)) return 0;
   return ep_finish_timing(m);
+}
+
+// One barrier of the direct transport on this handle alone, for the test of the bounded wait: the
+// handle signals its peers and waits for them exactly as inside the expert-parallel call, with a wait
+// of about 13 ms instead of two seconds.  With `peers_arrive` the peers' counts are written into the own
+// flag row first (the wait succeeds); without it nothing ever sets them, the wait runs out, and
+// coli_b200_moe_check reports the abandoned barrier.  Needs a handle of the direct transport whose peer
+// slabs are known (any expert-parallel or emulated call made before).
+extern "C" int coli_b200_ep_barrier_probe(ColiMoe *m, int peers_arrive, void *stream) {
+  if (!m || !m->ep || !m->ep->direct || !m->ep->slab || !coli_select_ctx(m->ctx)) {
+    coli_set_error("ep_barrier_probe: the handle has no direct-transport expert-parallel state");
+    return 0;
+  }
+  ColiEp *ep = m->ep;
+  cudaStream_t st = (cudaStream_t)stream;
+  colib::EpPeers peers;
+  for (int d = 0; d < EP_MAX_WORLD; ++d) {
+    peers.slab[d] = d < ep->world ? ep->peer_slab[d] : nullptr;
+    if (d < ep->world && !peers.slab[d]) {
+      coli_set_error("ep_barrier_probe: the slab of rank %d is not known to this handle yet", d);
+      return 0;
+    }
+  }
+  ++ep->epoch;
+  if (peers_arrive)
+    colib::k_fill_i32<<<1, 32, 0, st>>>(reinterpret_cast<int32_t *>(ep->slab + ep->flag_off), ep->world, ep->epoch);
+  colib::k_ep_flag_barrier<<<1, 32, 0, st>>>(peers, ep->flag_off, ep->rank, ep->world, ep->epoch, 1u << 16, ep->bar_status);
+  return coli_cuda_check(cudaGetLastError(), "barrier probe launch") ? 1 : 0;
 }
 
 // The same call for `world` handles that live on ONE device in ONE process (ranks[r] created with

@@ -479,6 +479,53 @@ def test_expert_parallel_call_emulated_on_one_gpu(gpu_backend, orc, monkeypatch,
         b.close()
 
 
+def test_expert_parallel_barrier_wait_is_bounded(gpu_backend, monkeypatch):
+    """The barrier of the direct transport waits for its peers with a limit: when nothing ever sets the
+    peers' counts the kernel returns, the context stays usable and the handle's check reports the
+    abandoned barrier once; when the counts are there the barrier passes.  One handle, one kernel at
+    a time: no kernel here waits for another launch."""
+    import ctypes as C
+
+    import torch
+
+    monkeypatch.setenv("COLI_EP_TRANSPORT", "direct")
+    from speedycolibri_b200 import _lib
+    from speedycolibri_b200.backend import CudaError
+    from speedycolibri_b200.cluster import ExpertSharding
+
+    lib = _lib.load()
+    world, shape = 2, CONFIGS["tiny_sig"].with_tokens(16)
+    _, packed = host_layer(shape)
+    sh = ExpertSharding.new(world, shape.E)
+    blocks = [make_block(shape, upload_layer(shape, packed, local=set(sh.local_experts(r))), max_tokens=16, ep_rank=r, ep_world=world)
+              for r in range(world)]
+    x_all = synth.host_tokens(shape, 16)
+    xs = [torch.from_numpy(x_all[8 * r:8 * r + 8].view(np.int16).copy()).cuda().view(torch.bfloat16).reshape(-1, shape.H) for r in range(world)]
+    outs = [torch.zeros_like(t) for t in xs]
+    hp = (C.c_void_p * world)(*[b.handle for b in blocks])
+    xp = (C.c_void_p * world)(*[t.data_ptr() for t in xs])
+    op = (C.c_void_p * world)(*[t.data_ptr() for t in outs])
+    tl = (C.c_int * world)(8, 8)
+    assert lib.coli_b200_moe_block_ep_emulate(hp, world, xp, op, tl, None) == 1, lib.coli_cuda_last_error().decode()
+    torch.cuda.synchronize()
+    blocks[0].check()
+    # peers present: passes
+    assert lib.coli_b200_ep_barrier_probe(blocks[0].handle, 1, None) == 1, lib.coli_cuda_last_error().decode()
+    torch.cuda.synchronize()
+    blocks[0].check()
+    # rank 1 never arrives: the wait runs out (about 13 ms), is reported once, and the handle keeps working
+    assert lib.coli_b200_ep_barrier_probe(blocks[0].handle, 0, None) == 1
+    torch.cuda.synchronize()
+    with pytest.raises(CudaError, match="barrier"):
+        blocks[0].check()
+    blocks[0].check()
+    assert lib.coli_b200_moe_block_ep_emulate(hp, world, xp, op, tl, None) == 1
+    torch.cuda.synchronize()
+    for b in blocks:
+        b.check()
+        b.close()
+
+
 def test_tracing_phases_and_launch_count(gpu_backend):
     import torch
     from speedycolibri_b200 import _lib
