@@ -331,7 +331,19 @@ __global__ void __launch_bounds__(256) k_ep_pack(EpPackParams p) {
   }
   const uint4 *src = reinterpret_cast<const uint4 *>(p.x + (size_t)t * p.H);
   const int vec = p.H / 8;
-  for (int c = lane; c < vec; c += 32) {
+  int c = lane;
+  for (; c + 96 < vec; c += 128) {  // four loads in flight per lane before their stores
+    const uint4 v0 = src[c], v1 = src[c + 32], v2 = src[c + 64], v3 = src[c + 96];
+#pragma unroll
+    for (int d = 0; d < EP_MAX_WORLD; ++d)
+      if (row[d]) {
+        row[d][c] = v0;
+        row[d][c + 32] = v1;
+        row[d][c + 64] = v2;
+        row[d][c + 96] = v3;
+      }
+  }
+  for (; c < vec; c += 32) {
     const uint4 v = src[c];
 #pragma unroll
     for (int d = 0; d < EP_MAX_WORLD; ++d)
@@ -563,7 +575,16 @@ __global__ void __launch_bounds__(256) k_ep_ret_pack_direct(const __nv_bfloat16 
   const uint4 *src = reinterpret_cast<const uint4 *>(y + (size_t)slot[i] * H);
   uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(peers.slab[info->src_rank[s]] + ret_off) + (size_t)row * H);
   const int vec = H / 8;
-  for (int c = lane; c < vec; c += 32) dst[c] = src[c];
+  // four loads in flight per lane before their stores: a row is one warp's serial copy otherwise
+  int c = lane;
+  for (; c + 96 < vec; c += 128) {
+    const uint4 v0 = src[c], v1 = src[c + 32], v2 = src[c + 64], v3 = src[c + 96];
+    dst[c] = v0;
+    dst[c + 32] = v1;
+    dst[c + 64] = v2;
+    dst[c + 96] = v3;
+  }
+  for (; c < vec; c += 32) dst[c] = src[c];
   __threadfence_system();
 }
 
