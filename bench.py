@@ -276,6 +276,10 @@ class Ctx:
             import torch.distributed as dist
 
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            # the exchange stores into peer memory with plain stores and uses NCCL only for one-word and handle
+            # all-gathers at set-up: in-switch reduction buys nothing here, and a rank that dies while its
+            # memory is bound to a multicast object takes its peers with it
+            os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
             if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "WARN"):
                 os.environ.pop("NCCL_DEBUG")  # its banner goes to stdout, which carries the one JSON line
             dist.init_process_group("nccl", device_id=self.dev)
