@@ -526,6 +526,26 @@ def test_expert_parallel_barrier_wait_is_bounded(gpu_backend, monkeypatch):
         b.close()
 
 
+@pytest.mark.parametrize("name", ["tiny", "tiny_sig", "tiny_fp8", "tiny_mx", "tiny_zipf", "mid_ragged"])
+def test_block_against_committed_fixture(gpu_backend, name):
+    """The device block against the committed fixtures of tests/golden (made by make_golden.py from the
+    pinned oracle): routing bits exact, output within the bar.  The digests tie the fixture to the inputs."""
+    import hashlib
+    import os
+
+    want = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", f"block_{name}.npz"))
+    shape = CONFIGS[name]
+    _, packed = host_layer(shape)
+    x = synth.host_tokens(shape)
+    assert hashlib.sha256(np.ascontiguousarray(x).tobytes()).hexdigest() == str(want["x_sha"])
+    blk = make_block(shape, upload_layer(shape, packed))
+    out, idx, w = blk.moe(x, want_routing=True)
+    blk.check()
+    assert np.array_equal(idx, want["idx"]) and np.array_equal(w.view(np.uint32), want["w_bits"])
+    assert rel_l2(np.asarray(out).view(np.uint16), want["out_bits"]) <= REL_L2_TOL
+    blk.close()
+
+
 def test_tracing_phases_and_launch_count(gpu_backend):
     import torch
     from speedycolibri_b200 import _lib
