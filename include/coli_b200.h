@@ -264,7 +264,8 @@ int coli_b200_moe_gather_local_dev(ColiMoe *moe, const void *x_dev, const int32_
                                    int32_t *seg_count_dev, int32_t *slot_dev, void *stream);
 /* Grouped SwiGLU FFN of the resident experts over those rows -> y_dev (bf16 [rows, H]); the
  * device-pointer form of coli_cuda_expert_group_nvfp4.  rows_cap = rows the two buffers hold;
- * rows_expected (e.g. T*k/world) only selects the kernel family. */
+ * rows_expected (e.g. T*k/world) only selects the kernel family.  rows_dev and y_dev must be
+ * 16-byte aligned (TMA reads the rows; the tcgen05 kernels write result rows 8 bytes at a time). */
 int coli_b200_moe_experts_dev(ColiMoe *moe, const void *rows_dev, const int32_t *seg_count_dev, int rows_cap,
                               int rows_expected, void *y_dev, void *stream);
 /* Shared expert over x_dev[T,H] -> y_dev[T,H] (bf16). */

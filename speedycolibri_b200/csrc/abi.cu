@@ -1111,6 +1111,10 @@ extern "C" int coli_b200_moe_experts_dev(ColiMoe *m, const void *rows_dev, const
     coli_set_error("moe_experts_dev: bad row bounds or null pointer");
     return 0;
   }
+  if ((reinterpret_cast<uintptr_t>(rows_dev) | reinterpret_cast<uintptr_t>(y_dev)) & 15) {
+    coli_set_error("moe_experts_dev: rows_dev and y_dev must be 16-byte aligned");
+    return 0;
+  }
   return run_segments(m, m->gate, m->up, m->down, m->seg_expert + m->first_local_seg, rows_dev, seg_count_dev, m->n_local_seg,
                       rows_cap, rows_expected < rows_cap ? rows_expected : rows_cap, y_dev, pick_stream(m, stream));
 }
@@ -1122,6 +1126,10 @@ extern "C" int coli_b200_moe_shared_dev(ColiMoe *m, const void *x_dev, int T, vo
     return 0;
   }
   if (T == 0) return 1;
+  if (!y_dev || (reinterpret_cast<uintptr_t>(y_dev) & 15)) {
+    coli_set_error("moe_shared_dev: y_dev must be a 16-byte aligned device buffer");
+    return 0;
+  }
   cudaStream_t st = pick_stream(m, stream);
   // one segment of T rows; its count lives in seg_count[E]
   if (!coli_cuda_check(cudaMemcpyAsync(m->seg_count + m->L.E, &T, sizeof(int32_t), cudaMemcpyHostToDevice, st), "shared count"))
