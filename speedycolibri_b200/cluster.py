@@ -1,7 +1,8 @@
 """Expert parallelism: the ownership map of crates/colibri-cluster/src/sharding.rs and the
 sharded block of crates/colibri-engine/src/moe.rs:1620-1794, with the reference's TCP
-request/response (crates/colibri-cluster/src/net.rs) replaced by an all-to-all of token rows over
-NCCL send/recv inside one library call.
+request/response (crates/colibri-cluster/src/net.rs) replaced by an all-to-all of token rows inside
+one library call: rows stored straight into the peers' receive buffers over NVLink (default), or
+exchanged with NCCL send/recv.
 
 What is kept from the reference: the expert -> rank map (contiguous ``e*N/E`` or an explicit
 LPT table), the FNV-1a fingerprint every rank compares before exchanging anything, "move

@@ -25,6 +25,12 @@
 // The result rows travel unweighted and the home rank applies the routing weights, so the f32
 // accumulation (moe.rs:1549-1553) is the single-GPU block's, whatever the number of ranks.
 //
+// That is the NCCL transport.  The default ("direct") transport keeps the same plan, layouts and
+// kernels downstream but moves the rows itself: every rank's receive buffers sit in one slab that the
+// peers map through CUDA IPC, the pack kernels store rows, ids and counts straight into it over
+// NVLink, and a flag barrier with a bounded wait (k_ep_flag_barrier) stands where the collectives
+// stood, so the host never waits.
+//
 // NCCL is bound at run time (dlopen of libnccl.so.2, the copy already in the process if there is
 // one), so the library loads and runs single-GPU without it.
 #include <dlfcn.h>
